@@ -1,0 +1,12 @@
+"""Typed configurations, the architecture registry and the model structure data."""
+from .registry import (ConfigError, architecture_name, load_config, read_config_json,
+                       register_architecture, registered_architectures, resolve_architecture)
+from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
+
+__all__ = [
+    "ConfigError", "architecture_name", "load_config", "read_config_json",
+    "register_architecture", "registered_architectures", "resolve_architecture",
+    "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
+    "LlamaConfig", "build_llama_spec", "llama_config_from_dict",
+]

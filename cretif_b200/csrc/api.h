@@ -1,0 +1,58 @@
+// The C interface of the kernel library.
+//
+// Every launcher takes raw device pointers, sizes and the CUDA stream to launch on, and
+// returns 0 when the kernel was launched, a negative cretif::Status for arguments it does
+// not take, or a positive cudaError_t.  Element types are passed as codes: 0 = float32,
+// 1 = bfloat16.  Nothing here allocates device memory.
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// out[t, :] = table[ids[t], :] widened to float32.  An id outside [0, V) sets bit 1 of
+// *fault and writes zeros.
+int cretif_embed_rows(const void* table, int table_dt, const int* ids, float* out, int T, int H,
+                      int V, unsigned int* fault, void* stream);
+
+// v = h[src] (+ delta[src]); if write_h, h[src] = v; out[r] = v * weight * rsqrt(mean(v^2)+eps).
+// src = rows ? rows[r] : r.  delta may be null.  rows and write_h exclude each other.
+int cretif_add_rmsnorm(float* h, const void* delta, int delta_dt, const float* weight, void* out,
+                       int out_dt, const int* rows, int R, int H, float eps, int write_h,
+                       void* stream);
+
+// act[t, i] = silu(gu[t, i]) * gu[t, I + i]
+int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, void* stream);
+
+// Rotate q and k of every token by its position's angles (pairing 0: (j, j+rot/2),
+// 1: (2j, 2j+1)); q in place, rotated k and v into the block cache.
+int cretif_rope_kv_append(void* qkv, int ld, int dt, const float* cos_t, const float* sin_t,
+                          int pairing, int rot_dim, int nh, int nkv, int hd, const int* tok_pos,
+                          const int* tok_seq, const int* seq_slot, const int* table,
+                          int table_stride, void* kc, void* vc, int bt, int write_cache, int T,
+                          unsigned int* fault, void* stream);
+
+// After a decode step: ids <- sampled (if given), positions and lengths + 1.
+int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int* sampled, int B,
+                          void* stream);
+
+// C[M,N] (= or +=) A[M,K] · W[N,K]^T, 32-bit FMA on the CUDA cores.
+int cretif_gemm_simt(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt, int M,
+                     int N, int K, int lda, int ldw, int ldc, int accumulate, void* stream);
+
+// Causal grouped-query attention over the block cache, any step shape.
+int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
+                     const void* vc, const int* table, int table_stride, const int* tok_pos,
+                     const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
+                     int window, int bt, int T, void* stream);
+
+// One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.
+int cretif_sample(const float* logits, int ld, int rows, int V, float temperature, int top_k,
+                  unsigned long long seed, const long long* request, int* draw, int* out,
+                  void* stream);
+float cretif_uniform01(unsigned long long seed, long long request, int draw);
+int cretif_max_top_k(void);
+
+#ifdef __cplusplus
+}
+#endif

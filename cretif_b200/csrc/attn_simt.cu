@@ -1,0 +1,124 @@
+// Causal grouped-query attention over the block cache, one warp per (token, query head).
+//
+// The plain attention kernel: it serves prefill and decode alike, in 32-bit and in
+// bfloat16 storage, for any number of heads and groups, head sizes in steps of 8 up to
+// 256, an optional sliding window, and it is the kernel the faster ones are checked
+// against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
+// dot (src/attention.cu:690-692), keys after the query's position are masked (:60-77),
+// softmax with running maximum and sum in 32-bit as in the reference's decode kernel
+// (:451-493), query head h reads key/value head h / (heads / kv_heads) (:421-422).
+// A (token, head) is always reduced in the same order, so its output does not depend on
+// what else is in the batch or on how the tokens were cut into steps.
+#include "api.h"
+#include "common.cuh"
+
+namespace cretif {
+
+constexpr int kWarps = 4;
+constexpr int kMaxHd = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
+                 const T* __restrict__ kc, const T* __restrict__ vc,
+                 const int* __restrict__ table, int table_stride,
+                 const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                 const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
+                 int window, int bt, int T_tokens) {
+  __shared__ float qs[kWarps][kMaxHd];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * kWarps + warp;
+  if (item >= (long long)T_tokens * nh) return;
+  const int t = (int)(item / nh), h = (int)(item - (long long)t * nh);
+  const int kvh = h / (nh / nkv);
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  const int* tab = table + (size_t)slot * table_stride;
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+
+  const T* qrow = q + (size_t)t * ldq + (size_t)h * hd;
+  for (int d = lane; d < hd; d += 32) qs[warp][d] = to_float(qrow[d]);
+  __syncwarp();
+
+  float m = -INFINITY, l = 0.f;
+  float acc[kMaxHd / 32];
+#pragma unroll
+  for (int i = 0; i < kMaxHd / 32; ++i) acc[i] = 0.f;
+
+  for (int base = first; base <= pos; base += 32) {
+    const int key = base + lane;
+    bool valid = key <= pos;
+    float s = -INFINITY;
+    unsigned long long row = 0;
+    const int blk = valid ? tab[key / bt] : -1;
+    valid = blk >= 0;                 // a position without a block counts as masked
+    if (valid) {
+      row = ((unsigned long long)blk * nkv + kvh) * bt + (key % bt);
+      const T* kp = kc + row * hd;
+      float dot = 0.f;
+      for (int d = 0; d < hd; d += 8) {
+        float kv[8];
+        load8(kp + d, kv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+      }
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = valid ? expf(s - m_new) : 0.f;
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);   // nothing summed yet
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < kMaxHd / 32; ++i) acc[i] *= corr;
+    m = m_new;
+    const int n_valid = min(32, pos + 1 - base);
+    for (int j = 0; j < n_valid; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const unsigned long long rj = __shfl_sync(0xffffffffu, row, j);
+      if (pj == 0.f) continue;        // masked, or underflowed: adds nothing
+      const T* vp = vc + rj * hd;
+#pragma unroll
+      for (int i = 0; i < kMaxHd / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) acc[i] = fmaf(pj, to_float(vp[d]), acc[i]);
+      }
+    }
+  }
+  const float inv = 1.0f / l;
+  T* orow = out + (size_t)t * ldo + (size_t)h * hd;
+#pragma unroll
+  for (int i = 0; i < kMaxHd / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < hd) orow[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+}  // namespace cretif
+
+using namespace cretif;
+
+extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
+                                const void* vc, const int* table, int table_stride,
+                                const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                int nh, int nkv, int hd, float scale, int window, int bt, int T,
+                                void* stream) {
+  if (T <= 0) return kOk;
+  if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd % 8 || hd > kMaxHd || bt <= 0 ||
+      window < 0)
+    return kBadArgument;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long items = (long long)T * nh;
+  const unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
+  if (dt == kF32)
+    attn_simt_kernel<float><<<blocks, kWarps * 32, 0, st>>>(
+        (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, table,
+        table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T);
+  else if (dt == kBF16)
+    attn_simt_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, st>>>(
+        (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
+        (const __nv_bfloat16*)vc, table, table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd,
+        scale, window, bt, T);
+  else
+    return kBadDType;
+  return launch_status();
+}

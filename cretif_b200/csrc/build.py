@@ -1,0 +1,159 @@
+"""Building and loading the kernel library.
+
+The ``.cu`` files beside this module are compiled with ``nvcc`` for sm_100a into one
+shared library that is loaded with ``ctypes``.  The library's file name carries a hash
+of the sources and flags, so an edited source is never served by a stale build.  The
+library is looked for, and built at first need, in ``_build/`` beside the sources; if
+that folder cannot be written (a read-only installation) a per-user folder under the
+system's temporary directory is used instead.  While compiling, a line is printed to
+stderr for every file so that a first call does not look hung.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from typing import List, Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+_NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+
+_lib: Optional[ctypes.CDLL] = None
+_lib_path: Optional[str] = None
+
+
+class KernelBuildError(RuntimeError):
+    """The kernel library could not be built or loaded."""
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+
+
+def _headers() -> List[str]:
+    return sorted(f for f in os.listdir(_HERE) if f.endswith((".h", ".cuh")))
+
+
+def _find_nvcc() -> str:
+    for cand in (os.environ.get("CRETIF_NVCC"), shutil.which("nvcc"),
+                 "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise KernelBuildError("nvcc was not found (looked at $CRETIF_NVCC, PATH and "
+                           "/usr/local/cuda/bin); the kernels cannot be compiled")
+
+
+def source_hash() -> str:
+    h = hashlib.sha256()
+    for name in sources() + _headers():
+        h.update(name.encode())
+        with open(os.path.join(_HERE, name), "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(_ARCH_FLAGS + _NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def _build_dirs() -> List[str]:
+    dirs = []
+    env = os.environ.get("CRETIF_BUILD_DIR")
+    if env:
+        dirs.append(env)
+    dirs.append(os.path.join(_HERE, "_build"))
+    dirs.append(os.path.join(tempfile.gettempdir(), f"cretif_b200_build_{os.getuid()}"))
+    return dirs
+
+
+def _writable_dir(path: str) -> bool:
+    try:
+        os.makedirs(path, exist_ok=True)
+        probe = os.path.join(path, f".probe_{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return True
+    except OSError:
+        return False
+
+
+def library_path(build: bool = True, verbose: bool = True) -> str:
+    """Path of the built library for the present sources; builds it if it is missing."""
+    name = f"libcretif_kernels_{source_hash()}.so"
+    for d in _build_dirs():
+        p = os.path.join(d, name)
+        if os.path.isfile(p):
+            return p
+    if not build:
+        raise KernelBuildError(f"{name} has not been built")
+    for d in _build_dirs():
+        if _writable_dir(d):
+            return _compile(d, name, verbose)
+    raise KernelBuildError("no writable folder to build the kernel library in; "
+                           f"tried {_build_dirs()}")
+
+
+def _say(msg: str, verbose: bool) -> None:
+    if verbose:
+        print(f"[cretif_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _compile(build_dir: str, name: str, verbose: bool) -> str:
+    nvcc = _find_nvcc()
+    srcs = sources()
+    tag = name[len("libcretif_kernels_"):-3]
+    obj_dir = os.path.join(build_dir, f"obj_{tag}")
+    os.makedirs(obj_dir, exist_ok=True)
+    _say(f"compiling {len(srcs)} CUDA files for sm_100a into {build_dir} (first use only)",
+         verbose)
+    t0 = time.time()
+
+    def one(src: str):
+        obj = os.path.join(obj_dir, src[:-3] + ".o")
+        cmd = [nvcc, *_ARCH_FLAGS, *_NVCC_FLAGS, "-I", _HERE, "-c",
+               os.path.join(_HERE, src), "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise KernelBuildError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+        with open(os.path.join(obj_dir, src[:-3] + ".ptxas.txt"), "w") as f:
+            f.write(r.stderr)
+        return src, obj
+
+    objs = []
+    workers = max(1, min(len(srcs), os.cpu_count() or 1, 8))
+    with concurrent.futures.ThreadPoolExecutor(workers) as pool:
+        for src, obj in pool.map(one, srcs):
+            objs.append(obj)
+            _say(f"  compiled {src} ({time.time() - t0:.0f} s)", verbose)
+    tmp = os.path.join(build_dir, f".{name}.{os.getpid()}.tmp")
+    cmd = [nvcc, *_ARCH_FLAGS, "-shared", "-o", tmp, *objs]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise KernelBuildError(f"linking the kernel library failed:\n{r.stdout}\n{r.stderr}")
+    out = os.path.join(build_dir, name)
+    os.replace(tmp, out)
+    _say(f"built {name} in {time.time() - t0:.0f} s", verbose)
+    return out
+
+
+def load_library(verbose: bool = True) -> ctypes.CDLL:
+    """The kernel library, built on first use.  Raises KernelBuildError if that fails."""
+    global _lib, _lib_path
+    if _lib is None:
+        path = library_path(build=True, verbose=verbose)
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelBuildError(f"cannot load {path}: {e}") from None
+        _lib_path = path
+    return _lib
+
+
+def loaded_library_path() -> Optional[str]:
+    return _lib_path

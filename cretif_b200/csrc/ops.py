@@ -1,0 +1,227 @@
+"""Python faces of the CUDA launchers: argument checks, then one ctypes call each.
+
+Every function takes CUDA tensors, checks what the kernel assumes (device, dtype,
+contiguity, sizes) and raises ``KernelError`` with a plain message when a kernel
+refuses its arguments.  There is no fallback of any kind: without the compiled
+library, or with a tensor that is not on a CUDA device, the call fails.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_STATUS = {-1: "sizes or options the kernel does not take", -2: "unsupported element type",
+           -3: "pointer or row stride not aligned as the kernel needs"}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = load_library()
+        L.cretif_uniform01.restype = ctypes.c_float
+        L.cretif_uniform01.argtypes = [ctypes.c_ulonglong, ctypes.c_longlong, ctypes.c_int]
+        _lib = L
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_STATUS.get(code, f'status {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"tensors of dtype {t.dtype} have no kernel") from None
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dim=None) -> None:
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} must have {dim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _rows(t: torch.Tensor, name: str) -> int:
+    """Row stride (in elements) of a 2-d tensor whose rows are dense."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-d with dense rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+    return t.stride(0)
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_rows(table, ids, out, fault) -> None:
+    _need(table, "table", dim=2); _need(ids, "ids", torch.int32, 1)
+    _need(out, "out", torch.float32, 2); _need(fault, "fault", torch.int32)
+    T, (V, H) = ids.numel(), table.shape
+    if tuple(out.shape) != (T, H) or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError(f"embed_rows: out must be a contiguous [{T}, {H}] tensor")
+    _check(lib().cretif_embed_rows(_p(table), _dt(table), _p(ids), _p(out), T, H, V, _p(fault),
+                                   _stream()), "embed_rows")
+
+
+def add_rmsnorm(h, delta, weight, out, eps: float, rows=None, write_h: bool = True) -> None:
+    _need(h, "h", torch.float32, 2); _need(weight, "weight", torch.float32, 1)
+    _need(out, "out", dim=2)
+    H = h.shape[1]
+    if not h.is_contiguous() or not out.is_contiguous() or weight.numel() != H:
+        raise KernelError("add_rmsnorm: h and out must be contiguous and weight have H elements")
+    if delta is not None:
+        _need(delta, "delta", dim=2)
+        if tuple(delta.shape) != tuple(h.shape) or not delta.is_contiguous():
+            raise KernelError("add_rmsnorm: delta must match h")
+    R = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        if rows.numel() != R:
+            raise KernelError("add_rmsnorm: one source row per output row")
+        write_h = False
+    elif R != h.shape[0]:
+        raise KernelError("add_rmsnorm: out must have as many rows as h")
+    if out.shape[1] != H:
+        raise KernelError("add_rmsnorm: out has another width than h")
+    _check(lib().cretif_add_rmsnorm(_p(h), _p(delta), _dt(delta) if delta is not None else 0,
+                                    _p(weight), _p(out), _dt(out), _p(rows), R, H,
+                                    ctypes.c_float(eps), int(write_h), _stream()), "add_rmsnorm")
+
+
+def silu_mul(gu, act) -> None:
+    _need(gu, "gu", dim=2); _need(act, "act", gu.dtype, 2)
+    T, I = act.shape
+    if tuple(gu.shape) != (T, 2 * I) or not gu.is_contiguous() or not act.is_contiguous():
+        raise KernelError(f"silu_mul: gu must be contiguous [{T}, {2 * I}]")
+    _check(lib().cretif_silu_mul(_p(gu), _p(act), _dt(gu), T, I, _stream()), "silu_mul")
+
+
+def rope_kv_append(qkv, cos, sin, pairing: int, rot_dim: int, nh: int, nkv: int, hd: int,
+                   tok_pos, tok_seq, seq_slot, table, kc, vc, block_tokens: int,
+                   write_cache: bool, fault) -> None:
+    _need(qkv, "qkv", dim=2)
+    T, ld = qkv.shape[0], _rows(qkv, "qkv")
+    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+    if rot_dim and (cos.shape[1] != rot_dim // 2 or not cos.is_contiguous()
+                    or not sin.is_contiguous()):
+        raise KernelError("rope_kv_append: cos/sin must be contiguous [positions, rot_dim/2]")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (seq_slot, "seq_slot")):
+        _need(t, n, torch.int32, 1)
+    _need(table, "table", torch.int32, 2)
+    if write_cache:
+        _need(kc, "k cache", qkv.dtype, 4); _need(vc, "v cache", qkv.dtype, 4)
+        if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+                or not vc.is_contiguous() or kc.shape != vc.shape):
+            raise KernelError("rope_kv_append: cache must be contiguous "
+                              f"[blocks, {nkv}, {block_tokens}, {hd}], got {tuple(kc.shape)}")
+    _check(lib().cretif_rope_kv_append(
+        _p(qkv), ld, _dt(qkv), _p(cos), _p(sin), pairing, rot_dim, nh, nkv, hd, _p(tok_pos),
+        _p(tok_seq), _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc), block_tokens,
+        int(write_cache), T, _p(fault), _stream()), "rope_kv_append")
+
+
+def advance_decode(tok_ids, tok_pos, seq_start, sampled, B: int) -> None:
+    _check(lib().cretif_advance_decode(_p(tok_ids), _p(tok_pos), _p(seq_start), _p(sampled), B,
+                                       _stream()), "advance_decode")
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_simt(a, w, c, accumulate: bool = False) -> None:
+    """c[M,N] (+)= a[M,K] · w[N,K]ᵀ in 32-bit FMA arithmetic."""
+    _need(a, "a", dim=2); _need(w, "w", dim=2); _need(c, "c", dim=2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(c.shape) != (M, N):
+        raise KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(c.shape)}")
+    _check(lib().cretif_gemm_simt(_p(a), _dt(a), _p(w), _dt(w), _p(c), _dt(c), M, N, K,
+                                  _rows(a, "a"), _rows(w, "w"), _rows(c, "c"), int(accumulate),
+                                  _stream()), "gemm_simt")
+
+
+# ------------------------------------------------------------------ attention
+def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
+              scale: float, window: int, block_tokens: int) -> None:
+    _need(q, "q", dim=2); _need(out, "out", q.dtype, 2)
+    _need(kc, "k cache", q.dtype, 4); _need(vc, "v cache", q.dtype, 4)
+    T = q.shape[0]
+    if out.shape[0] != T or out.shape[1] < nh * hd or q.shape[1] < nh * hd:
+        raise KernelError("attention: q/out must hold [tokens, heads*head_dim]")
+    if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+            or not vc.is_contiguous()):
+        raise KernelError("attention: cache must be contiguous [blocks, kv_heads, block, head_dim]")
+    if hd % 8 or hd > 256:
+        raise KernelError(f"attention: head_dim {hd} is not a multiple of 8 up to 256")
+    _check(lib().cretif_attn_simt(
+        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _dt(q), _p(kc), _p(vc), _p(table),
+        table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
+        ctypes.c_float(scale), window, block_tokens, T, _stream()), "attn_simt")
+
+
+# ------------------------------------------------------------------ sampling
+def sample(logits, out, temperature: float, top_k: int, seed: int, request=None,
+           draw=None) -> None:
+    _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
+    rows, V = logits.shape
+    if out.numel() < rows:
+        raise KernelError("sample: out is shorter than the number of rows")
+    if request is not None:
+        _need(request, "request", torch.int64, 1)
+    if draw is not None:
+        _need(draw, "draw", torch.int32, 1)
+    if temperature > 0 and 0 < top_k < V and top_k > lib().cretif_max_top_k():
+        raise KernelError(f"sample: top_k {top_k} exceeds the kernel's limit "
+                          f"{lib().cretif_max_top_k()}")
+    _check(lib().cretif_sample(_p(logits), _rows(logits, "logits"), rows, V,
+                               ctypes.c_float(temperature), int(top_k),
+                               ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(request),
+                               _p(draw), _p(out), _stream()), "sample")
+
+
+def uniform01(seed: int, request: int, draw: int) -> float:
+    """The uniform number the sampling kernel uses for (seed, request, draw)."""
+    return float(lib().cretif_uniform01(ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF),
+                                        ctypes.c_longlong(request), draw))
+
+
+# ------------------------------------------------------------------ fast products (bfloat16)
+def gemv_supported(x, w, out) -> bool:
+    return False
+
+
+def gemm_tc_supported(x, w, out) -> bool:
+    return False
+
+
+# ------------------------------------------------------------------ fast attention (bfloat16)
+def attn_decode_supported(hd: int, block_tokens: int) -> bool:
+    return False
+
+
+def attn_prefill_supported(hd: int, block_tokens: int) -> bool:
+    return False

@@ -1,0 +1,97 @@
+"""The attention mixer: grouped-query causal attention over the block cache.
+
+Order of work as in the reference's block (src/attention.cu:542-731): q, k, v
+projections without bias (:567-576, here one product with the three matrices
+stacked), position encoding of q and k (:589-597), cache write (:607-608), scores
+scaled after the dot product, causal mask, softmax, weighted sum of values
+(:683-714), output projection (:720-728).  Unlike the reference there is no separate
+score tensor and no transposition of the cache: the attention kernels read the
+cache's blocks directly, for whole prompts and for single tokens alike.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import KVRequest
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part, build_part, register_part
+from .linear import linear
+
+_force_plain = False
+
+
+def force_plain_attention(on: bool) -> None:
+    """Use the one-warp-per-query kernel for every step (the tests' yardstick)."""
+    global _force_plain
+    _force_plain = bool(on)
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``
+    (0 = all keys), ``position`` (a position part's kind and constants), ``names``
+    (tensor names of q, k, v, o relative to the layer's prefix)."""
+
+    def __init__(self, params, hidden_size, dtype, device):
+        super().__init__(params, hidden_size, dtype, device)
+        self.nh = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.hd = int(params["head_dim"])
+        self.scale = float(params["scale"])
+        self.window = int(params.get("window", 0))
+        if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads cannot share {self.nkv} key/value heads")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            raise ValueError(f"attention: head_dim {self.hd} is not a multiple of 16 in [16, 256]; "
+                             "the attention kernels take no other head size")
+        pos = dict(params.get("position") or {"kind": "none"})
+        self.position = build_part("position", PartSpec(pos.pop("kind"), pos), hidden_size,
+                                   dtype, device)
+        self.q_dim, self.kv_dim = self.nh * self.hd, self.nkv * self.hd
+
+    @classmethod
+    def weight_specs(cls, params, hidden_size):
+        q = params["num_heads"] * params["head_dim"]
+        kv = params["num_kv_heads"] * params["head_dim"]
+        n = params["names"]
+        return {"q": (n["q"], WeightSpec((q, hidden_size))),
+                "k": (n["k"], WeightSpec((kv, hidden_size))),
+                "v": (n["v"], WeightSpec((kv, hidden_size))),
+                "o": (n["o"], WeightSpec((hidden_size, q)))}
+
+    def load(self, tensors):
+        # one product for q, k and v: rows [q | k | v] of the stacked matrix
+        self.w_qkv = self._matrix(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0))
+        self.w_o = self._matrix(tensors["o"])
+        self.position.load({})
+
+    def prepare(self, max_positions: int) -> None:
+        self.position.prepare(max_positions)
+
+    def cache_request(self):
+        return KVRequest(self.nkv, self.hd, self.window)
+
+    def forward(self, x, ctx, cache):
+        qkv = linear(x, self.w_qkv)                                   # [T, q + 2 kv]
+        self.position.rotate_and_store(qkv, ctx, cache, self.nh, self.nkv, self.hd)
+        o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
+        self.attend(qkv, o, ctx, cache.kv)
+        return linear(o, self.w_o, out_dtype=torch.float32)
+
+    def attend(self, q, o, ctx, kv):
+        if not _force_plain and self.dtype == torch.bfloat16:
+            if ctx.is_decode and ops.attn_decode_supported(self.hd, kv.block_tokens):
+                ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx, self.nh, self.nkv, self.hd,
+                                self.scale, self.window, kv.block_tokens)
+                return
+            if not ctx.is_decode and ops.attn_prefill_supported(self.hd, kv.block_tokens):
+                ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx, self.nh, self.nkv, self.hd,
+                                 self.scale, self.window, kv.block_tokens)
+                return
+        ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                      self.nh, self.nkv, self.hd, self.scale, self.window, kv.block_tokens)
+
+    def weight_bytes(self):
+        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

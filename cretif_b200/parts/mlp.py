@@ -1,0 +1,46 @@
+"""The gated feed-forward (SwiGLU): ``down(act(gate(x)) ⊙ up(x))`` without bias.
+
+Reference: two products, SiLU, multiply, one product (src/ffn.cu:132-191;
+``silu(z) = z / (1 + exp(−z))``, src/kernels/elementwise.cu:93-99).  Here gate and up
+are one product with the two matrices stacked, and SiLU·mul is one kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part, register_part
+from .linear import linear
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(Part):
+    """params: ``intermediate_size``, ``activation`` ("silu"), ``names`` (gate, up, down)."""
+
+    def __init__(self, params, hidden_size, dtype, device):
+        super().__init__(params, hidden_size, dtype, device)
+        self.inter = int(params["intermediate_size"])
+        if params.get("activation", "silu") != "silu":
+            raise ValueError(f"gated_mlp: activation {params['activation']!r} has no kernel "
+                             "(only 'silu')")
+
+    @classmethod
+    def weight_specs(cls, params, hidden_size):
+        I, n = params["intermediate_size"], params["names"]
+        return {"gate": (n["gate"], WeightSpec((I, hidden_size))),
+                "up": (n["up"], WeightSpec((I, hidden_size))),
+                "down": (n["down"], WeightSpec((hidden_size, I)))}
+
+    def load(self, tensors):
+        self.w_gate_up = self._matrix(torch.cat([tensors["gate"], tensors["up"]], dim=0))
+        self.w_down = self._matrix(tensors["down"])
+
+    def forward(self, x, ctx):
+        gu = linear(x, self.w_gate_up)                                # [T, 2 I]
+        act = torch.empty((x.shape[0], self.inter), dtype=self.dtype, device=x.device)
+        ops.silu_mul(gu, act)
+        return linear(act, self.w_down, out_dtype=torch.float32)
+
+    def weight_bytes(self):
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()

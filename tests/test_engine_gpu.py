@@ -1,0 +1,82 @@
+"""The engine against the plain implementation, in every way of cutting the work."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import tiny
+from replay_cuts import rel_err, run_batch, run_tail_by_one, run_whole
+
+pytestmark = pytest.mark.gpu
+
+# Relative to the largest plain logit.  float32: the library's contract.  bfloat16:
+# activations and cached keys/values are rounded to 8 bits of mantissa (2^-9 relative
+# each) several times a layer; sums and the residual stream stay in 32-bit.
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+LENGTHS = {"A": [5, 9, 13, 70, 100], "B": [1, 17, 40, 130, 200], "C": [3, 33, 64, 65, 300]}
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    from cretif_b200.engine import Engine
+    made = {}
+
+    def get(name, dtype, max_tokens=2048):
+        key = (name, dtype, max_tokens)
+        if key not in made:
+            made[key] = Engine(model_dirs[name], dtype=dtype, max_tokens=max_tokens)
+        return made[key]
+    return get
+
+
+@pytest.fixture(scope="module")
+def plain_logits(plain_models):
+    memo = {}
+
+    def get(name, toks):
+        key = (name, tuple(toks))
+        if key not in memo:
+            cfg, w = plain_models[name]
+            memo[key] = plain_llama.forward(cfg, w, list(toks)).numpy()
+        return memo[key]
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_whole(engines, plain_logits, name, dtype):
+    eng = engines(name, dtype)
+    for n in LENGTHS[name]:
+        toks = tiny.tokens(name, n, 1)
+        got = run_whole(eng, toks)
+        assert got.shape == (n, eng.vocab_size)
+        assert rel_err(got, plain_logits(name, toks)) <= TOL[dtype], (name, n)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_tokens_one_by_one(engines, plain_logits, name, dtype):
+    eng = engines(name, dtype)
+    for n in LENGTHS[name]:
+        toks = tiny.tokens(name, n, 2)
+        got = run_tail_by_one(eng, toks, tail=32)
+        assert rel_err(got, plain_logits(name, toks)) <= TOL[dtype], (name, n)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_reuse_slots(engines, plain_logits, name, dtype):
+    """Batches of unequal lengths, one after another, on a cache too small to hold two
+    batches at once, so that blocks and slots of the first are used again."""
+    eng = engines(name, dtype, max_tokens=512)
+    lens = LENGTHS[name]
+    for round_ in range(3):
+        reqs = [tiny.tokens(name, n + 8 + 3 * i, 10 + round_) for i, n in enumerate(lens[:4])]
+        prompts = [min(lens[i], len(r)) for i, r in enumerate(reqs)]
+        outs = run_batch(eng, reqs, prompts)
+        for r, got in zip(reqs, outs):
+            assert rel_err(got, plain_logits(name, r)) <= TOL[dtype], (name, round_, len(r))
+        eng.cache.check()
+        assert eng.cache.stats()["slots_live"] == 0

@@ -38,8 +38,18 @@ def lib():
     return _lib
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (graph replays are not counted)."""
+    return _launches
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += kernels
         return
     if code < 0:
         raise KernelError(f"{what}: {_STATUS.get(code, f'status {code}')}")

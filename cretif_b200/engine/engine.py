@@ -177,6 +177,14 @@ class Engine:
             what = [msg for bit, msg in _FAULTS.items() if word & bit]
             raise StepError("device fault: " + "; ".join(what or [f"status {word}"]))
 
+    def generate(self, prompts, max_tokens: int = 100, temperature: float = 0.0, top_k: int = 0,
+                 seed: int = 42, stop_ids=None, max_batch: int = 64, use_graph: bool = True):
+        """Generate for a list of prompts (lists of token ids); see engine.generate.generate."""
+        from .generate import generate
+        return generate(self, prompts, max_tokens=max_tokens, temperature=temperature,
+                        top_k=top_k, seed=seed, stop_ids=stop_ids, max_batch=max_batch,
+                        use_graph=use_graph)
+
     def stats(self) -> dict:
         return {"weights_bytes": self.model.weight_bytes(), "cache": self.cache.stats(),
                 "dtype": str(self.dtype).replace("torch.", ""),

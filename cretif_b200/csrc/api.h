@@ -40,11 +40,28 @@ int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int*
 int cretif_gemm_simt(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt, int M,
                      int N, int K, int lda, int ldw, int ldc, int accumulate, void* stream);
 
+// C[M,N] (= or +=) X[M,K] · W[N,K]^T for M <= 64 rows, bfloat16 operands, streaming W once.
+// K and the row strides must be multiples of 8 and the operands 16-byte aligned.
+int cretif_gemm_skinny(const void* X, const void* W, void* C, int c_dt, int M, int N, int K,
+                       int ldx, int ldw, int ldc, int accumulate, void* stream);
+int cretif_gemm_skinny_max_rows(void);
+
 // Causal grouped-query attention over the block cache, any step shape.
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
                      const void* vc, const int* table, int table_stride, const int* tok_pos,
                      const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
                      int window, int bt, int T, void* stream);
+
+// Decode attention (one query token per sequence), bfloat16, keys split into n_splits
+// ranges per (sequence, kv head); part_o/part_ml are float32 scratch of the sizes that
+// cretif_attn_decode_scratch_floats reports.  block tokens must be 64.
+int cretif_attn_decode_scratch_floats(int B, int nh, int hd, int n_splits, long long* part_o,
+                                      long long* part_ml);
+int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc,
+                       const int* table, int table_stride, const int* tok_pos, const int* tok_seq,
+                       const int* seq_slot, int nh, int nkv, int hd, float scale, int window,
+                       int bt, int B, int n_splits, float* part_o, float* part_ml,
+                       unsigned int* fault, void* stream);
 
 // One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.
 int cretif_sample(const float* logits, int ld, int rows, int V, float temperature, int top_k,

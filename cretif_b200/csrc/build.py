@@ -138,6 +138,12 @@ def _compile(build_dir: str, name: str, verbose: bool) -> str:
         raise KernelBuildError(f"linking the kernel library failed:\n{r.stdout}\n{r.stderr}")
     out = os.path.join(build_dir, name)
     os.replace(tmp, out)
+    for old in os.listdir(build_dir):          # builds of earlier sources are of no use
+        path = os.path.join(build_dir, old)
+        if old.startswith("libcretif_kernels_") and old.endswith(".so") and old != name:
+            os.remove(path)
+        elif old.startswith("obj_") and old != f"obj_{tag}":
+            shutil.rmtree(path, ignore_errors=True)
     _say(f"built {name} in {time.time() - t0:.0f} s", verbose)
     return out
 

@@ -221,7 +221,25 @@ def uniform01(seed: int, request: int, draw: int) -> float:
 
 # ------------------------------------------------------------------ fast products (bfloat16)
 def gemv_supported(x, w, out) -> bool:
-    return False
+    """The weight-streaming kernel takes bfloat16 operands with 16-byte aligned rows."""
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= 64
+            and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and out.dtype in (torch.bfloat16, torch.float32))
+
+
+def gemv_bf16(x, w, out, accumulate: bool = False) -> None:
+    """out[M,N] (+)= x[M,K] · w[N,K]ᵀ for M <= 64 (decode), tensor-core FMA, 32-bit sums."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemv: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _check(lib().cretif_gemm_skinny(_p(x), _p(w), _p(out), _dt(out), M, N, K, _rows(x, "x"),
+                                    _rows(w, "w"), _rows(out, "out"), int(accumulate),
+                                    _stream()), "gemm_skinny")
 
 
 def gemm_tc_supported(x, w, out) -> bool:
@@ -229,8 +247,43 @@ def gemm_tc_supported(x, w, out) -> bool:
 
 
 # ------------------------------------------------------------------ fast attention (bfloat16)
-def attn_decode_supported(hd: int, block_tokens: int) -> bool:
-    return False
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _SM_COUNT[key]
+
+
+def attn_decode_supported(hd: int, block_tokens: int, group: int = 1) -> bool:
+    return block_tokens == 64 and hd % 16 == 0 and 16 <= hd <= 256 and group <= 8
+
+
+def decode_splits(B: int, nkv: int, max_context: int, device) -> int:
+    """Ranges per (sequence, kv head): enough CTAs for about four per SM, at most one per
+    cache block of the longest context."""
+    tiles = max(1, -(-max_context // 64))
+    want = -(-4 * sm_count(device) // max(1, B * nkv))
+    return max(1, min(tiles, want))
+
+
+def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
+                scale: float, window: int, block_tokens: int, n_splits: int, fault) -> None:
+    _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
+    B = q.shape[0]
+    if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+            or not vc.is_contiguous()):
+        raise KernelError("attn_decode: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
+    part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib().cretif_attn_decode(
+        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
+        table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
+        ctypes.c_float(scale), window, block_tokens, B, n_splits, _p(part_o), _p(part_ml),
+        _p(fault), _stream()), "attn_decode", kernels=2)
 
 
 def attn_prefill_supported(hd: int, block_tokens: int) -> bool:

@@ -82,9 +82,12 @@ class Attention(Part):
 
     def attend(self, q, o, ctx, kv):
         if not _force_plain and self.dtype == torch.bfloat16:
-            if ctx.is_decode and ops.attn_decode_supported(self.hd, kv.block_tokens):
-                ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx, self.nh, self.nkv, self.hd,
-                                self.scale, self.window, kv.block_tokens)
+            if ctx.is_decode and ops.attn_decode_supported(self.hd, kv.block_tokens,
+                                                           self.nh // self.nkv):
+                splits = ops.decode_splits(ctx.B, self.nkv, ctx.max_context, q.device)
+                ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq,
+                                ctx.seq_slot, self.nh, self.nkv, self.hd, self.scale,
+                                self.window, kv.block_tokens, splits, ctx.fault)
                 return
             if not ctx.is_decode and ops.attn_prefill_supported(self.hd, kv.block_tokens):
                 ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx, self.nh, self.nkv, self.hd,

@@ -20,7 +20,7 @@ import torch
 from ..csrc import ops
 
 # Rows up to which the weight-streaming kernel is used instead of the tensor-core one.
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 64
 
 _force_plain = False
 

@@ -1,0 +1,402 @@
+"""Each kernel alone against a plain float32/float64 torch formula of the same operation,
+at sizes other than the engine's (odd widths, head sizes in steps of 16, tails)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cretif_b200.csrc import ops as _ops
+    _ops.lib()
+    return _ops
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, rel):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-30)
+    assert err <= rel, f"relative error {err:.3e} > {rel:.1e}"
+
+
+# ------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 77), (70, 65, 129), (257, 96, 200)])
+def test_gemm_simt_f32(ops, M, N, K):
+    a, w = rnd(M, K), rnd(N, K, seed=1)
+    c = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(a, w, c)
+    close(c, a.double() @ w.double().T, 2e-6)
+    base = rnd(M, N, seed=2)
+    c2 = base.clone()
+    ops.gemm_simt(a, w, c2, accumulate=True)
+    close(c2, base.double() + a.double() @ w.double().T, 2e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(2, 33, 40), (65, 70, 136)])
+def test_gemm_simt_bf16(ops, M, N, K):
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = a.double() @ w.double().T
+    c32 = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(a, w, c32)
+    close(c32, want, 1e-5)
+    c16 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_simt(a, w, c16)
+    close(c16, want, 5e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 32), (1, 1000, 576), (3, 50, 40), (8, 333, 1544),
+                                   (9, 96, 104), (17, 64, 72), (33, 200, 256), (64, 129, 520)])
+def test_gemm_skinny(ops, M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = x.double() @ w.double().T
+    assert ops.gemv_supported(x, w, torch.empty(M, N, device=DEV))
+    c = torch.empty(M, N, device=DEV)
+    ops.gemv_bf16(x, w, c)
+    close(c, want, 1e-5)
+    base = rnd(M, N, seed=3)
+    c2 = base.clone()
+    ops.gemv_bf16(x, w, c2, accumulate=True)
+    close(c2, base.double() + want, 1e-5)
+    cb = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemv_bf16(x, w, cb)
+    close(cb, want, 5e-3)
+
+
+def test_gemm_skinny_strided_rows(ops):
+    """Rows of x may be a slice of a wider buffer (its row stride a multiple of 8)."""
+    buf = rnd(5, 256, dtype=torch.bfloat16)
+    x = buf[:, 64:64 + 72]
+    w = rnd(40, 72, dtype=torch.bfloat16, seed=1)
+    c = torch.empty(5, 40, device=DEV)
+    ops.gemv_bf16(x, w, c)
+    close(c, x.double() @ w.double().T, 1e-5)
+
+
+def test_gemm_skinny_refuses_unaligned(ops):
+    x, w = rnd(2, 20, dtype=torch.bfloat16), rnd(8, 20, dtype=torch.bfloat16)
+    assert not ops.gemv_supported(x, w, torch.empty(2, 8, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.gemv_bf16(x, w, torch.empty(2, 8, device=DEV))
+
+
+# ------------------------------------------------------------------ row-wise kernels
+@pytest.mark.parametrize("T,H", [(1, 10), (5, 100), (3, 576), (2, 3000)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(ops, T, H, out_dtype):
+    eps = 3e-6
+    h, d, w = rnd(T, H), rnd(T, H, seed=1), rnd(H, seed=2) + 1
+    want_h = h.double() + d.double()
+    want_n = want_h * w.double() / torch.sqrt((want_h ** 2).mean(-1, keepdim=True) + eps)
+    out = torch.empty(T, H, device=DEV, dtype=out_dtype)
+    h2 = h.clone()
+    ops.add_rmsnorm(h2, d, w, out, eps)
+    close(h2, want_h, 1e-7)
+    close(out, want_n, 1e-5 if out_dtype == torch.float32 else 5e-3)
+    # no delta: h untouched
+    h3 = h.clone()
+    ops.add_rmsnorm(h3, None, w, out, eps)
+    assert torch.equal(h3, h)
+    want0 = h.double() * w.double() / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + eps)
+    close(out, want0, 1e-5 if out_dtype == torch.float32 else 5e-3)
+    # gathered rows with a bfloat16 delta: the stream is not written
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    db = d.to(torch.bfloat16)
+    out2 = torch.empty(2, H, device=DEV, dtype=out_dtype)
+    h4 = h.clone()
+    ops.add_rmsnorm(h4, db, w, out2, eps, rows=rows)
+    assert torch.equal(h4, h)
+    wh = h.double() + db.double()
+    wn = (wh * w.double() / torch.sqrt((wh ** 2).mean(-1, keepdim=True) + eps))[[T - 1, 0]]
+    close(out2, wn, 1e-5 if out_dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(ops, dtype):
+    T, I = 5, 173
+    gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
+    act = torch.empty(T, I, device=DEV, dtype=dtype)
+    ops.silu_mul(gu, act)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(ops, dtype):
+    table = rnd(50, 37, dtype=dtype)
+    ids = torch.tensor([3, 49, 0, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, 37, device=DEV)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed_rows(table, ids, out, fault)
+    assert torch.equal(out, table[ids.long()].float())
+    assert fault.item() == 0
+    bad = torch.tensor([3, 50], dtype=torch.int32, device=DEV)
+    out2 = torch.ones(2, 37, device=DEV)
+    ops.embed_rows(table, bad, out2, fault)
+    assert fault.item() & 1 and out2[1].abs().max().item() == 0.0
+
+
+# ------------------------------------------------------------------ cache helpers
+class ToyCache:
+    """A block cache with a shuffled block table, as the kernels see it."""
+
+    def __init__(self, lens, nkv, hd, dtype, bt=64, seed=0, spare=3):
+        self.lens, self.nkv, self.hd, self.bt = lens, nkv, hd, bt
+        B = len(lens)
+        per = [-(-n // bt) for n in lens]
+        n_blocks = sum(per) + spare
+        rng = np.random.default_rng(seed)
+        order = rng.permutation(n_blocks)
+        self.slots = rng.permutation(B + 2)[:B]              # slots are not 0..B-1
+        table = np.full((B + 2, max(per) + 1), -1, dtype=np.int32)
+        o = 0
+        for b in range(B):
+            table[self.slots[b], :per[b]] = order[o:o + per[b]]
+            o += per[b]
+        self.table_host = table
+        self.table = torch.from_numpy(table).to(DEV)
+        self.k = rnd(n_blocks, nkv, bt, hd, dtype=dtype, seed=seed + 1)
+        self.v = rnd(n_blocks, nkv, bt, hd, dtype=dtype, seed=seed + 2)
+        self.seq_slot = torch.from_numpy(self.slots.astype(np.int32)).to(DEV)
+
+    def keys(self, b, n):
+        """K and V of sequence b, positions 0..n-1: [n, nkv, hd] float64."""
+        ks, vs = [], []
+        for p in range(n):
+            blk = self.table_host[self.slots[b], p // self.bt]
+            ks.append(self.k[blk, :, p % self.bt, :])
+            vs.append(self.v[blk, :, p % self.bt, :])
+        return torch.stack(ks).double().cpu(), torch.stack(vs).double().cpu()
+
+
+def plain_attention(q, k, v, scale, qpos, window=0):
+    """q [nq, nh, hd] at positions qpos, k/v [n, nkv, hd] → [nq, nh, hd] (float64)."""
+    nq, nh, hd = q.shape
+    g = nh // k.shape[1]
+    out = torch.zeros(nq, nh, hd, dtype=torch.float64)
+    for i in range(nq):
+        p = qpos[i]
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(nh):
+            s = (k[lo:p + 1, h // g, :] @ q[i, h]) * scale
+            w = torch.softmax(s, dim=0)
+            out[i, h] = w @ v[lo:p + 1, h // g, :]
+    return out
+
+
+ATTN_CASES = [  # nh, nkv, hd, lens
+    (4, 2, 16, [1, 64, 65, 200]),
+    (3, 1, 32, [17, 129]),
+    (5, 5, 48, [70, 3]),
+    (8, 1, 64, [300]),
+    (6, 2, 128, [130, 64]),
+    (2, 2, 256, [90]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,lens", ATTN_CASES)
+@pytest.mark.parametrize("window", [0, 40])
+def test_attn_simt_decode_and_prefill(ops, dtype, nh, nkv, hd, lens, window):
+    scale = 0.37 / math.sqrt(hd)
+    cache = ToyCache(lens, nkv, hd, dtype)
+    B = len(lens)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    # decode shape: one query per sequence at its last position
+    q = rnd(B, nh * hd, dtype=dtype, seed=5)
+    out = torch.empty(B, nh * hd, device=DEV, dtype=dtype)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    ops.attn_simt(q, out, cache.k, cache.v, cache.table, pos, seq, cache.seq_slot, nh, nkv, hd,
+                  scale, window, 64)
+    for b, n in enumerate(lens):
+        k, v = cache.keys(b, n)
+        want = plain_attention(q[b].double().cpu().reshape(1, nh, hd), k, v, scale, [n - 1], window)
+        close(out[b].reshape(1, nh, hd), want, tol)
+    # prefill shape: the last min(n, 20) positions of every sequence as queries
+    qpos, qseq = [], []
+    for b, n in enumerate(lens):
+        for p in range(max(0, n - 20), n):
+            qpos.append(p); qseq.append(b)
+    T = len(qpos)
+    q = rnd(T, nh * hd + 16, dtype=dtype, seed=6)[:, :nh * hd]        # strided rows
+    out = torch.empty(T, nh * hd, device=DEV, dtype=dtype)
+    ops.attn_simt(q, out, cache.k, cache.v, cache.table,
+                  torch.tensor(qpos, dtype=torch.int32, device=DEV),
+                  torch.tensor(qseq, dtype=torch.int32, device=DEV), cache.seq_slot, nh, nkv, hd,
+                  scale, window, 64)
+    for b, n in enumerate(lens):
+        k, v = cache.keys(b, n)
+        idx = [i for i in range(T) if qseq[i] == b]
+        want = plain_attention(q[idx].double().cpu().reshape(len(idx), nh, hd), k, v, scale,
+                               [qpos[i] for i in idx], window)
+        close(out[idx].reshape(len(idx), nh, hd), want, tol)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens", ATTN_CASES + [(9, 3, 64, [2048, 700, 1, 4096])])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
+    scale = 1.0 / math.sqrt(hd)
+    cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=4)
+    B = len(lens)
+    assert ops.attn_decode_supported(hd, 64, nh // nkv)
+    q = rnd(B, nh * hd, dtype=torch.bfloat16, seed=5)
+    out = torch.empty(B, nh * hd, device=DEV, dtype=torch.bfloat16)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attn_decode(q, out, cache.k, cache.v, cache.table, pos, seq, cache.seq_slot, nh, nkv, hd,
+                    scale, window, 64, splits, fault)
+    assert fault.item() == 0
+    for b, n in enumerate(lens):
+        k, v = cache.keys(b, n)
+        want = plain_attention(q[b].double().cpu().reshape(1, nh, hd), k, v, scale, [n - 1], window)
+        close(out[b].reshape(1, nh, hd), want, 1e-2)
+
+
+def test_attn_decode_finds_a_far_key(ops):
+    """One key among thousands is made to dominate; the output must be its value."""
+    nh, nkv, hd, n = 4, 2, 64, 3000
+    cache = ToyCache([n], nkv, hd, torch.bfloat16, seed=9)
+    target = 1234
+    blk = cache.table_host[cache.slots[0], target // 64]
+    q = rnd(1, nh * hd, dtype=torch.bfloat16, seed=5)
+    for kvh in range(nkv):
+        cache.k[blk, kvh, target % 64, :] = (q[0, kvh * 2 * hd:kvh * 2 * hd + hd].float() * 40
+                                             ).to(torch.bfloat16)
+    out = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attn_decode(q, out, cache.k, cache.v, cache.table, pos, seq, cache.seq_slot, nh, nkv, hd,
+                    1.0, 0, 64, 7, fault)
+    for h in (0, 2):       # the heads whose own query was copied into the key
+        close(out[0, h * hd:(h + 1) * hd], cache.v[blk, h // 2, target % 64, :], 2e-2)
+
+
+# ------------------------------------------------------------------ rotary + cache write
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing", [0, 1])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (3, 1, 48, 32), (2, 2, 64, 0)])
+def test_rope_kv_append(ops, dtype, pairing, nh, nkv, hd, rot):
+    lens = [5, 70]
+    cache = ToyCache(lens, nkv, hd, dtype, seed=3)
+    k_before, v_before = cache.k.clone(), cache.v.clone()
+    theta, P = 10000.0, 128
+    half = max(rot // 2, 1)
+    j = torch.arange(half, dtype=torch.float64)
+    ang = torch.arange(P, dtype=torch.float64)[:, None] / theta ** (2 * j / max(rot, 1))[None, :]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    qpos = [3, 4, 64, 65, 69]
+    qseq = [0, 0, 1, 1, 1]
+    T = len(qpos)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=8)
+    orig = qkv.clone()
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_append(qkv, cos, sin, pairing, rot, nh, nkv, hd,
+                       torch.tensor(qpos, dtype=torch.int32, device=DEV),
+                       torch.tensor(qseq, dtype=torch.int32, device=DEV), cache.seq_slot,
+                       cache.table, cache.k, cache.v, 64, True, fault)
+    assert fault.item() == 0
+    tol = 1e-6 if dtype == torch.float32 else 5e-3
+
+    def rotate(x, p):        # x [heads, hd] float64
+        y = x.clone()
+        for jj in range(rot // 2):
+            i0, i1 = (2 * jj, 2 * jj + 1) if pairing else (jj, jj + rot // 2)
+            c, s = math.cos(ang[p, jj]), math.sin(ang[p, jj])
+            y[:, i0] = x[:, i0] * c - x[:, i1] * s
+            y[:, i1] = x[:, i0] * s + x[:, i1] * c
+        return y
+    touched = set()
+    for t in range(T):
+        row = orig[t].double().cpu()
+        q = row[:nh * hd].reshape(nh, hd)
+        k = row[nh * hd:(nh + nkv) * hd].reshape(nkv, hd)
+        v = row[(nh + nkv) * hd:].reshape(nkv, hd)
+        close(qkv[t, :nh * hd].reshape(nh, hd), rotate(q, qpos[t]), tol)
+        blk = cache.table_host[cache.slots[qseq[t]], qpos[t] // 64]
+        close(cache.k[blk, :, qpos[t] % 64, :], rotate(k, qpos[t]), tol)
+        close(cache.v[blk, :, qpos[t] % 64, :], v, tol)
+        touched.add((int(blk), qpos[t] % 64))
+    # nothing else in the cache moved
+    mask = torch.ones_like(cache.k, dtype=torch.bool)
+    for blk, off in touched:
+        mask[blk, :, off, :] = False
+    assert torch.equal(cache.k[mask], k_before[mask]) and torch.equal(cache.v[mask], v_before[mask])
+
+
+# ------------------------------------------------------------------ sampling
+def test_sample_greedy_ties_lowest(ops):
+    V = 1000
+    logits = rnd(4, V)
+    logits[0, 17] = logits[0, 900] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, :] = 1.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, 0.0, 0, 42)
+    want = [17, 999, 0, int(torch.argmax(logits[3]))]
+    assert out.tolist() == want
+
+
+def test_sample_temperature_statistics_and_determinism(ops):
+    V, rows = 16, 4096
+    base = torch.tensor([float(i % 5) for i in range(V)])
+    logits = base[None, :].repeat(rows, 1).to(DEV).contiguous()
+    req = torch.arange(rows, dtype=torch.int64, device=DEV)
+    draw = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, 0.8, 0, 7, req, draw)
+    assert draw.min().item() == 1 and draw.max().item() == 1
+    freq = torch.bincount(out.long().cpu(), minlength=V).double() / rows
+    want = torch.softmax(base.double() / 0.8, dim=0)
+    assert (freq - want).abs().max().item() < 0.03
+    # same (seed, request, draw) → same token, whatever the batch
+    out2 = torch.empty(1, dtype=torch.int32, device=DEV)
+    for r in (0, 5, 4000):
+        ops.sample(logits[r:r + 1], out2, 0.8, 0, 7, req[r:r + 1],
+                   torch.zeros(1, dtype=torch.int32, device=DEV))
+        assert out2.item() == out[r].item()
+    # another draw number changes the stream
+    draw1 = torch.ones(rows, dtype=torch.int32, device=DEV)
+    out3 = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out3, 0.8, 0, 7, req, draw1)
+    assert (out3 != out).float().mean().item() > 0.3
+
+
+def test_sample_top_k(ops):
+    V, rows, k = 5000, 2048, 5
+    row = rnd(V, scale=2.0).cpu()
+    logits = row[None, :].repeat(rows, 1).to(DEV).contiguous()
+    req = torch.arange(rows, dtype=torch.int64, device=DEV)
+    draw = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, 1.3, k, 3, req, draw)
+    vals, idx = torch.topk(row, k)
+    assert set(out.tolist()) <= set(idx.tolist())
+    want = torch.softmax(vals.double() / 1.3, dim=0)
+    freq = torch.tensor([(out.cpu() == i).double().mean() for i in idx])
+    assert (freq - want).abs().max().item() < 0.04
+    # k = 1 is arg-max; a tiny temperature is arg-max
+    ops.sample(logits, out, 1.0, 1, 3, req, draw)
+    assert set(out.tolist()) == {int(idx[0])}
+    ops.sample(logits, out, 1e-4, 0, 3, req, draw)
+    assert set(out.tolist()) == {int(idx[0])}
+    # the host mirror of the generator agrees with the walk along the sorted candidates
+    u = ops.uniform01(3, 11, 0)
+    d0 = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o1 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(logits[:1], o1, 1.3, k, 3, torch.tensor([11], dtype=torch.int64, device=DEV), d0)
+    cum = torch.cumsum(want, 0)
+    pick = int(idx[int((cum >= u).nonzero()[0])]) if (cum >= u).any() else int(idx[-1])
+    assert o1.item() == pick

@@ -46,6 +46,12 @@ int cretif_gemm_skinny(const void* X, const void* W, void* C, int c_dt, int M, i
                        int ldx, int ldw, int ldc, int accumulate, void* stream);
 int cretif_gemm_skinny_max_rows(void);
 
+// C[M,N] (= or +=) A[M,K] · W[N,K]^T on the tcgen05 tensor cores (TMA + TMEM), bfloat16
+// operands, C bfloat16 or float32 (+= only float32).  bn = 64/128/256 picks the tile width,
+// 0 lets the launcher choose.  A wait that expires sets bit 2 of *fault.
+int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda,
+                   int ldw, int ldc, int accumulate, int bn, unsigned int* fault, void* stream);
+
 // Causal grouped-query attention over the block cache, any step shape.
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
                      const void* vc, const int* table, int table_stride, const int* tok_pos,

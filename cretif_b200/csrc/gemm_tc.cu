@@ -1,0 +1,236 @@
+// C[M,N] (= or +=) A[M,K] · W[N,K]^T on the fifth-generation tensor cores (prefill).
+//
+// One CTA computes a 128 x BN tile.  Warp 0 is the producer: it moves 128x64 tiles of A and
+// BNx64 tiles of W from global to shared memory with TMA (128-byte swizzle; rows and
+// columns beyond the matrices are filled with zeros, so any M, N and K % 8 == 0 work)
+// through a ring of stages guarded by full/empty mbarriers.  One thread of warp 1 issues
+// tcgen05.mma (M=128, N=BN, K=16, bf16 in, f32 accumulate) on shared-memory descriptors
+// into a 128 x BN accumulator in tensor memory and commits each stage back to the producer.
+// Warps 2-5 read the accumulator with tcgen05.ld (each thread one row) and store it as
+// bfloat16 or float32, or add it into a float32 matrix (the residual stream).
+// Both operands are K-major exactly as activations [tokens, in] and weights [out, in] lie in
+// memory, so nothing is transposed.
+//
+// The reference runs every product on a 32x32-tile CUDA-core kernel
+// (src/kernels/matmul.cu:74-127); this kernel has no counterpart there.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "api.h"
+#include "tc_common.cuh"
+
+namespace cretif {
+
+constexpr int kTcBM = 128, kTcBK = 64, kTcStages = 4;
+constexpr int kTcThreads = 192;
+
+template <int BN>
+struct TcSmem {
+  static constexpr int kATile = kTcBM * kTcBK * 2;
+  static constexpr int kBTile = BN * kTcBK * 2;
+  static constexpr int kStage = kATile + kBTile;
+  static constexpr int kBars = kTcStages * kStage;          // offset of the barriers
+  static constexpr int kTotal = kBars + (2 * kTcStages + 1) * 8 + 16 + 1024;  // + align slack
+};
+
+template <int BN, typename TC>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               TC* __restrict__ C, int M, int N, int K, int ldc, int accumulate,
+               unsigned int* __restrict__ fault) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using L = TcSmem<BN>;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint64_t* empty = full + kTcStages;
+  uint64_t* acc_full = empty + kTcStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + kTcBK - 1) / kTcBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+    tc::mbar_init(acc_full, 1);
+    *abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_descriptor(&map_a);
+    tc::tma_prefetch_descriptor(&map_w);
+  }
+  if (warp == 1) {                       // one warp allocates the accumulator's columns
+    tc::tmem_alloc(tmem_slot, BN);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kTcStages;
+        if (kb >= kTcStages &&
+            !tc::mbar_wait(&empty[s], (uint32_t)((kb / kTcStages - 1) & 1), abort))
+          break;
+        unsigned char* stage = smem + s * L::kStage;
+        tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
+        tc::tma_load_2d(stage, &map_a, kb * kTcBK, m0, &full[s]);
+        tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc_bf16(kTcBM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kTcStages;
+        ok = tc::mbar_wait(&full[s], (uint32_t)((kb / kTcStages) & 1), abort);
+        if (!ok) break;
+        tc::tc_fence_after();
+        unsigned char* stage = smem + s * L::kStage;
+        const uint64_t a_desc = tc::smem_desc_k_sw128(stage);
+        const uint64_t b_desc = tc::smem_desc_k_sw128(stage + L::kATile);
+#pragma unroll
+        for (int k = 0; k < kTcBK / 16; ++k)       // 16 bf16 = 32 bytes = 2 descriptor units
+          tc::umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+        tc::umma_commit(&empty[s]);                // frees the stage when these MMAs are done
+      }
+      tc::umma_commit(acc_full);                   // accumulator complete
+    }
+  } else {
+    // ---- epilogue: thread = one row of the tile, TMEM lanes 32*(warp%4) ..
+    const int quad = warp & 3;
+    const int m = m0 + quad * 32 + lane;
+    const bool ok = tc::mbar_wait(acc_full, 0u, abort);
+    tc::tc_fence_after();
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc::tmem_load_32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+        tc::tmem_load_wait();
+        if (m < M && n0 + c0 < N) {
+          TC* out = C + (size_t)m * ldc + n0 + c0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+            const int n = n0 + c0 + j;
+            if (n + 8 <= N) {
+              if (accumulate) {
+                float old[8];
+                load8(out + j, old);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += old[e];
+              }
+              store8(out + j, v);
+            } else {
+              for (int e = 0; e < 8 && n + e < N; ++e) {
+                float x = v[e];
+                if (accumulate) x += to_float(out[j + e]);
+                out[j + e] = from_float<TC>(x);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_acc, BN);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] bf16 matrix with row stride ld (elements), tiles of box_rows x 64.
+int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
+                       int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return kBadArgument;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : kBadArgument;
+}
+
+template <int BN, typename TC>
+static int launch_tc(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                     int ldc, int accumulate, unsigned int* fault, cudaStream_t st) {
+  CUtensorMap map_a, map_w;
+  if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
+  if (make_tile_map_bf16(&map_w, W, N, K, ldw, BN)) return kBadArgument;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TcSmem<BN>::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
+  gemm_tc_kernel<BN, TC><<<grid, kTcThreads, TcSmem<BN>::kTotal, st>>>(
+      map_a, map_w, (TC*)C, M, N, K, ldc, accumulate, fault);
+  return launch_status();
+}
+
+}  // namespace cretif
+
+using namespace cretif;
+
+extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K,
+                              int lda, int ldw, int ldc, int accumulate, int bn,
+                              unsigned int* fault, void* stream) {
+  if (M <= 0 || N <= 0) return kOk;
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return kBadArgument;
+  if ((M + kTcBM - 1) / kTcBM > 65535) return kBadArgument;
+  if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return kMisaligned;
+  if ((c_dt == kBF16 && ldc % 8) || (c_dt == kF32 && ldc % 4)) return kMisaligned;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 0) {
+    const long long mt = (M + kTcBM - 1) / kTcBM;
+    bn = (mt * ((N + 255) / 256) >= 148) ? 256 : (mt * ((N + 127) / 128) >= 148 ? 128 : 64);
+  }
+#define CRETIF_TC(BN)                                                                         \
+  (c_dt == kBF16 ? launch_tc<BN, __nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, accumulate,  \
+                                                fault, st)                                    \
+                 : launch_tc<BN, float>(A, W, C, M, N, K, lda, ldw, ldc, accumulate, fault, st))
+  if (c_dt != kBF16 && c_dt != kF32) return kBadDType;
+  if (c_dt == kBF16 && accumulate) return kBadArgument;
+  switch (bn) {
+    case 64: return CRETIF_TC(64);
+    case 128: return CRETIF_TC(128);
+    case 256: return CRETIF_TC(256);
+    default: return kBadArgument;
+  }
+#undef CRETIF_TC
+}

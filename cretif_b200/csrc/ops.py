@@ -242,8 +242,40 @@ def gemv_bf16(x, w, out, accumulate: bool = False) -> None:
                                     _stream()), "gemm_skinny")
 
 
+_FAULT = {}
+
+
+def fault_word(device) -> torch.Tensor:
+    """The int32 status word of a device that kernels OR their fault bits into."""
+    key = str(torch.device(device))
+    if key not in _FAULT:
+        _FAULT[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _FAULT[key]
+
+
 def gemm_tc_supported(x, w, out) -> bool:
-    return False
+    """The tensor-core kernel takes bfloat16 operands whose rows are 16-byte aligned."""
+    K = x.shape[1]
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        return False
+    if out.dtype == torch.bfloat16:
+        return out.stride(0) % 8 == 0
+    return out.dtype == torch.float32 and out.stride(0) % 4 == 0
+
+
+def gemm_tc(x, w, out, accumulate: bool = False, bn: int = 0) -> None:
+    """out[M,N] (+)= x[M,K] · w[N,K]ᵀ with TMA, tcgen05.mma and a TMEM accumulator."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _check(lib().cretif_gemm_tc(_p(x), _p(w), _p(out), _dt(out), M, N, K, _rows(x, "x"),
+                                _rows(w, "w"), _rows(out, "out"), int(accumulate), bn,
+                                _p(fault_word(x.device)), _stream()), "gemm_tc")
 
 
 # ------------------------------------------------------------------ fast attention (bfloat16)

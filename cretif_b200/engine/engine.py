@@ -87,7 +87,7 @@ class Engine:
                                    self.device, block_tokens=block_tokens, max_slots=max_slots,
                                    max_len=longest)
         self.model.prepare(self.cache.max_len)
-        self.fault = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.fault = ops.fault_word(self.device)
         self.vocab_size = self.spec.vocab_size
 
     # -- slots -------------------------------------------------------------------

@@ -89,6 +89,34 @@ def test_gemm_skinny_refuses_unaligned(ops):
         ops.gemv_bf16(x, w, torch.empty(2, 8, device=DEV))
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(128, 128, 64, 128), (128, 64, 128, 64), (256, 256, 256, 256),
+                                      (2048, 960, 576, 0), (300, 200, 72, 0), (129, 65, 136, 64),
+                                      (70, 1000, 1544, 128), (1000, 3072, 576, 256),
+                                      (513, 576, 1536, 0)])
+def test_gemm_tc(ops, M, N, K, bn):
+    """The tcgen05 kernel against float64, tails in every dimension."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = x.double() @ w.double().T
+    ldc = -(-N // 8) * 8
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    c = torch.full((M, ldc), 7.0, device=DEV)[:, :N]
+    assert ops.gemm_tc_supported(x, w, c)
+    ops.gemm_tc(x, w, c, bn=bn)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    close(c, want, 1e-5)
+    base = rnd(M, ldc, seed=3)[:, :N]
+    c2 = torch.empty((M, ldc), device=DEV)[:, :N]
+    c2.copy_(base)
+    ops.gemm_tc(x, w, c2, accumulate=True, bn=bn)
+    close(c2, base.double() + want, 1e-5)
+    cb = torch.empty((M, ldc), device=DEV, dtype=torch.bfloat16)[:, :N]
+    ops.gemm_tc(x, w, cb, bn=bn)
+    close(cb, want, 5e-3)
+    assert fault.item() == 0
+
+
 # ------------------------------------------------------------------ row-wise kernels
 @pytest.mark.parametrize("T,H", [(1, 10), (5, 100), (3, 576), (2, 3000)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])

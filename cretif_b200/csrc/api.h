@@ -69,6 +69,16 @@ int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, const void* k
                        int bt, int B, int n_splits, float* part_o, float* part_ml,
                        unsigned int* fault, void* stream);
 
+// Causal attention for whole prompts on tcgen05 (bfloat16, head_dim a multiple of 16 up to
+// 128, 64-token cache blocks).  qkv rows hold the query heads first; sequence b brings the
+// tokens cu_seqlens[b] .. cu_seqlens[b+1]-1 at positions seq_start[b] ..; max_new is the
+// most tokens one sequence brings.
+int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, const void* kc,
+                           const void* vc, long long n_blocks, const int* table, int table_stride,
+                           const int* cu_seqlens, const int* seq_start, const int* seq_slot,
+                           int nh, int nkv, int hd, float scale, int window, int bt, int B,
+                           int max_new, unsigned int* fault, void* stream);
+
 // One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.
 int cretif_sample(const float* logits, int ld, int rows, int V, float temperature, int top_k,
                   unsigned long long seed, const long long* request, int* draw, int* out,

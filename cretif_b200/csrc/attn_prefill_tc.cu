@@ -1,0 +1,320 @@
+// Causal grouped-query attention for whole prompts on the tcgen05 tensor cores, bfloat16.
+//
+// One CTA owns 128 consecutive query tokens of one sequence and one query head.  It walks
+// the sequence's cache blocks (64 keys each) up to the diagonal:
+//   warp 0     TMA producer: the Q tile once, then K and V tiles of each block straight out
+//              of the block cache (a block's [64 x head_dim] tile of a key/value head is one
+//              2-d box) into a ring of shared-memory stages;
+//   warp 1     one thread issues S = Q K^T (tcgen05.mma, accumulator in tensor memory), and
+//              after the softmax threads have written P, O_blk = P V (V is the MN-major
+//              operand, exactly as it lies in the cache);
+//   warps 2-5  softmax: each thread owns one query row, reads its row of S from tensor
+//              memory, keeps the running maximum and sum in 32-bit, writes P as bfloat16 into
+//              shared memory in the swizzled operand layout, then folds O_blk into its row
+//              of the output, which stays in registers.
+// The reference materialises [heads, S, kv_len] scores and transposes the cache for every
+// call (src/attention.cu:644-728); nothing of that exists here.
+//
+// Queries of the next sequence that fall into a tile's 128 rows are computed and dropped.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "api.h"
+#include "tc_common.cuh"
+
+namespace cretif {
+
+int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
+                       int box_rows);
+
+constexpr int kPfThreads = 192;
+constexpr int kPfBQ = 128;       // queries per CTA
+constexpr int kPfBK = 64;        // keys per step = tokens per cache block
+constexpr int kPfStages = 3;
+
+struct PfSmem {
+  // byte offsets for a head size with n_sub 64-wide column groups
+  int q, p, k, v, bars, total;
+  __host__ __device__ explicit PfSmem(int n_sub) {
+    q = 0;
+    p = q + n_sub * kPfBQ * 128;
+    k = p + kPfBQ * 128;
+    v = k + kPfStages * n_sub * kPfBK * 128;
+    bars = v + kPfStages * n_sub * kPfBK * 128;
+    total = bars + (2 * kPfStages + 4) * 8 + 16 + 1024;
+  }
+};
+
+// MN-major operand tile (V): rows of 128 bytes are one key each, 8 keys form a 1024-byte
+// swizzle atom; 64-wide column groups of the head are `lbo_bytes` apart.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((tc::smem_u32(tile) & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int HDMAX>
+__global__ void __launch_bounds__(kPfThreads)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                       const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                       int ldo, const int* __restrict__ table, int table_stride,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
+                       const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
+                       int window, unsigned int* __restrict__ fault) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int n_sub = (hd + 63) >> 6;
+  const PfSmem L(n_sub);
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* kv_empty = kv_full + kPfStages;
+  uint64_t* q_full = kv_empty + kPfStages;
+  uint64_t* s_full = q_full + 1;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int kvh = h / (nh / nkv);
+  const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
+  // heavy tiles (late queries, many keys) first
+  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int q0 = q_tile * kPfBQ;
+  if (q0 >= n_new) return;
+  const int start = seq_start[b];
+  const int slot = seq_slot[b];
+  const int* tab = table + (size_t)slot * table_stride;
+  const int rows_here = min(kPfBQ, n_new - q0);
+  const int pos_first = start + q0, pos_last = start + q0 + rows_here - 1;
+  const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int tile_lo = key_lo / kPfBK, tile_hi = pos_last / kPfBK;      // inclusive
+  const int n_tiles = tile_hi - tile_lo + 1;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColS = 0, kColO = 64;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPfStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
+    tc::mbar_init(q_full, 1);
+    tc::mbar_init(s_full, 1);
+    tc::mbar_init(p_full, 128);
+    tc::mbar_init(o_full, 1);
+    *abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_descriptor(&map_q);
+    tc::tma_prefetch_descriptor(&map_k);
+    tc::tma_prefetch_descriptor(&map_v);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::mbar_expect_tx(q_full, (uint32_t)(n_sub * kPfBQ * 128));
+      for (int sub = 0; sub < n_sub; ++sub)
+        tc::tma_load_2d(smem + L.q + sub * kPfBQ * 128, &map_q, h * hd + 64 * sub, tok0 + q0,
+                        q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kPfStages;
+        if (j >= kPfStages &&
+            !tc::mbar_wait(&kv_empty[s], (uint32_t)((j / kPfStages - 1) & 1), abort))
+          break;
+        const int blk = tab[tile_lo + j];
+        if (blk < 0) atomicOr(fault, kFaultBlockTable);
+        const int row = (max(blk, 0) * nkv + kvh) * kPfBK;
+        tc::mbar_expect_tx(&kv_full[s], (uint32_t)(2 * n_sub * kPfBK * 128));
+        for (int sub = 0; sub < n_sub; ++sub) {
+          tc::tma_load_2d(smem + L.k + (s * n_sub + sub) * kPfBK * 128, &map_k, 64 * sub, row,
+                          &kv_full[s]);
+          tc::tma_load_2d(smem + L.v + (s * n_sub + sub) * kPfBK * 128, &map_v, 64 * sub, row,
+                          &kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK);
+      const uint32_t idesc_pv = tc::instr_desc_bf16(kPfBQ, hd) | (1u << 16);   // B is MN-major
+      const int k_steps = hd >> 4;
+      bool ok = tc::mbar_wait(q_full, 0u, abort);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kPfStages;
+        ok = tc::mbar_wait(&kv_full[s], (uint32_t)((j / kPfStages) & 1), abort);
+        if (!ok) break;
+        tc::tc_fence_after();
+        for (int kk = 0; kk < k_steps; ++kk) {
+          const int sub = kk >> 2, in = kk & 3;
+          const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + sub * kPfBQ * 128) + 2 * in;
+          const uint64_t kd =
+              tc::smem_desc_k_sw128(smem + L.k + (s * n_sub + sub) * kPfBK * 128) + 2 * in;
+          tc::umma_bf16(tmem + kColS, qd, kd, idesc_qk, kk != 0);
+        }
+        tc::umma_commit(s_full);
+        ok = tc::mbar_wait(p_full, (uint32_t)(j & 1), abort);
+        if (!ok) break;
+        tc::tc_fence_after();
+        const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p);
+        const uint64_t vd = smem_desc_mn_sw128(smem + L.v + s * n_sub * kPfBK * 128,
+                                               (uint32_t)(kPfBK * 128));
+#pragma unroll
+        for (int kk = 0; kk < kPfBK / 16; ++kk)      // 16 keys = two 1024-byte atoms of V
+          tc::umma_bf16(tmem + kColO, pd + 2 * kk, vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
+        tc::umma_commit(&kv_empty[s]);
+        tc::umma_commit(o_full);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int q_pos = start + q0 + row;
+    const bool row_valid = row < rows_here;
+    const int lo_key = window > 0 ? max(0, q_pos - window + 1) : 0;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    float o[HDMAX];
+#pragma unroll
+    for (int d = 0; d < HDMAX; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    unsigned char* prow = smem + L.p + row * 128;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = tc::mbar_wait(s_full, (uint32_t)(j & 1), abort);
+      if (!ok) break;
+      tc::tc_fence_after();
+      uint32_t sa[32], sb[32];
+      tc::tmem_load_32(lane_addr + kColS, sa);
+      tc::tmem_load_32(lane_addr + kColS + 32, sb);
+      tc::tmem_load_wait();
+      const int key0 = (tile_lo + j) * kPfBK;
+      float t[64];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const int key = key0 + c;
+        const float s = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]) * scale_log2;
+        t[c] = (key <= q_pos && key >= lo_key) ? s : -INFINITY;
+        mx = fmaxf(mx, t[c]);
+      }
+      const float m_new = fmaxf(m, mx);
+      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+      float sum = 0.f;
+      uint32_t packed[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = (t[c] == -INFINITY) ? 0.f : exp2f(t[c] - m_new);
+        const float p1 = (t[c + 1] == -INFINITY) ? 0.f : exp2f(t[c + 1] - m_new);
+        sum += p0 + p1;
+        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+      }
+      l = l * alpha + sum;
+      m = m_new;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {        // 16-byte chunks, swizzled by the row
+        const uint4 v4 = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2],
+                                    packed[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v4;
+      }
+      tc::fence_proxy_async();                // generic-proxy writes → visible to the MMA
+      tc::mbar_arrive(p_full);
+      ok = tc::mbar_wait(o_full, (uint32_t)(j & 1), abort);
+      if (!ok) break;
+      tc::tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < HDMAX; c0 += 32) {
+        if (c0 < hd) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_addr + kColO + c0, r);
+          tc::tmem_load_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[c0 + e] = fmaf(o[c0 + e], alpha, __uint_as_float(r[e]));
+        }
+      }
+      tc::tc_fence_before();
+    }
+    if (ok && row_valid) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* orow = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hd;
+#pragma unroll
+      for (int d = 0; d < HDMAX; d += 8) {
+        if (d < hd) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = o[d + e] * inv;
+          store8(orow + d, v);
+        }
+      }
+    }
+  }
+  if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace cretif
+
+using namespace cretif;
+
+extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo,
+                                      const void* kc, const void* vc, long long n_blocks,
+                                      const int* table, int table_stride, const int* cu_seqlens,
+                                      const int* seq_start, const int* seq_slot, int nh, int nkv,
+                                      int hd, float scale, int window, int bt, int B, int max_new,
+                                      unsigned int* fault, void* stream) {
+  if (B <= 0 || T <= 0) return kOk;
+  if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBK ||
+      window < 0 || max_new <= 0 || nh > 65535 || B > 65535 || ldq % 8 || ldo % 8)
+    return kBadArgument;
+  if (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) & 15) return kMisaligned;
+  const long long cache_rows = n_blocks * nkv * kPfBK;
+  if (cache_rows > 0x7fffffffLL) return kBadArgument;
+  CUtensorMap map_q, map_k, map_v;
+  if (make_tile_map_bf16(&map_q, qkv, T, ldq, ldq, kPfBQ)) return kBadArgument;
+  if (make_tile_map_bf16(&map_k, kc, (int)cache_rows, hd, hd, kPfBK)) return kBadArgument;
+  if (make_tile_map_bf16(&map_v, vc, (int)cache_rows, hd, hd, kPfBK)) return kBadArgument;
+  const int n_sub = (hd + 63) / 64;
+  const PfSmem L(n_sub);
+  cudaStream_t st = (cudaStream_t)stream;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid((max_new + kPfBQ - 1) / kPfBQ, nh, B);
+  cudaError_t e;
+  if (hd <= 64) {
+    static int configured = 0;
+    if (L.total > configured) {
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+      if (e != cudaSuccess) return (int)e;
+      configured = L.total;
+    }
+    attn_prefill_tc_kernel<64><<<grid, kPfThreads, L.total, st>>>(
+        map_q, map_k, map_v, (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
+        seq_slot, nh, nkv, hd, scale_log2, window, fault);
+  } else {
+    static int configured = 0;
+    if (L.total > configured) {
+      e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+      if (e != cudaSuccess) return (int)e;
+      configured = L.total;
+    }
+    attn_prefill_tc_kernel<128><<<grid, kPfThreads, L.total, st>>>(
+        map_q, map_k, map_v, (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
+        seq_slot, nh, nkv, hd, scale_log2, window, fault);
+  }
+  return launch_status();
+}

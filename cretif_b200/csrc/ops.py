@@ -319,4 +319,20 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
 
 
 def attn_prefill_supported(hd: int, block_tokens: int) -> bool:
-    return False
+    return block_tokens == 64 and hd % 16 == 0 and 16 <= hd <= 128
+
+
+def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: int, nkv: int,
+                 hd: int, scale: float, window: int, block_tokens: int, B: int, max_new: int,
+                 fault) -> None:
+    """Causal attention of whole prompts; ``qkv`` rows start with the query heads."""
+    _need(qkv, "qkv", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
+    if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+            or not vc.is_contiguous()):
+        raise KernelError("attn_prefill: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
+    _check(lib().cretif_attn_prefill_tc(
+        _p(qkv), _rows(qkv, "qkv"), qkv.shape[0], _p(out), _rows(out, "out"), _p(kc), _p(vc),
+        ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(cu_seqlens), _p(seq_start),
+        _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, max_new,
+        _p(fault), _stream()), "attn_prefill_tc")

@@ -90,8 +90,9 @@ class Attention(Part):
                                 self.window, kv.block_tokens, splits, ctx.fault)
                 return
             if not ctx.is_decode and ops.attn_prefill_supported(self.hd, kv.block_tokens):
-                ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx, self.nh, self.nkv, self.hd,
-                                 self.scale, self.window, kv.block_tokens)
+                ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
+                                 ctx.seq_slot, self.nh, self.nkv, self.hd, self.scale,
+                                 self.window, kv.block_tokens, ctx.B, ctx.max_new, ctx.fault)
                 return
         ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                       self.nh, self.nkv, self.hd, self.scale, self.window, kv.block_tokens)

@@ -292,6 +292,44 @@ def test_attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
         close(out[b].reshape(1, nh, hd), want, 1e-2)
 
 
+PREFILL_CASES = [  # nh, nkv, hd, lens (cached + new), new tokens per sequence
+    (4, 2, 64, [200], [200]),
+    (9, 3, 64, [300, 64, 129, 1], [300, 64, 129, 1]),
+    (3, 1, 32, [130, 500], [130, 250]),          # the second sequence continues at 250
+    (4, 2, 16, [65, 128], [65, 100]),
+    (5, 5, 48, [70, 3, 257], [70, 3, 257]),
+    (2, 1, 128, [260, 90], [260, 90]),
+    (2, 2, 96, [150], [150]),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,news", PREFILL_CASES)
+@pytest.mark.parametrize("window", [0, 100])
+def test_attn_prefill_tc(ops, nh, nkv, hd, lens, news, window):
+    scale = 1.0 / math.sqrt(hd)
+    cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=6)
+    B = len(lens)
+    assert ops.attn_prefill_supported(hd, 64)
+    T = sum(news)
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd(T, width, dtype=torch.bfloat16, seed=7)
+    out = torch.zeros(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    cu = np.concatenate([[0], np.cumsum(news)]).astype(np.int32)
+    starts = np.array([n - m for n, m in zip(lens, news)], dtype=np.int32)
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    ops.attn_prefill(qkv, out, cache.k, cache.v, cache.table, torch.from_numpy(cu).to(DEV),
+                     torch.from_numpy(starts).to(DEV), cache.seq_slot, nh, nkv, hd, scale, window,
+                     64, B, max(news), fault)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    for b, n in enumerate(lens):
+        k, v = cache.keys(b, n)
+        q = qkv[cu[b]:cu[b + 1], :nh * hd].double().cpu().reshape(news[b], nh, hd)
+        want = plain_attention(q, k, v, scale, list(range(starts[b], n)), window)
+        close(out[cu[b]:cu[b + 1]].reshape(news[b], nh, hd), want, 1e-2)
+
+
 def test_attn_decode_finds_a_far_key(ops):
     """One key among thousands is made to dominate; the output must be its value."""
     nh, nkv, hd, n = 4, 2, 64, 3000

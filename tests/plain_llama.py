@@ -70,7 +70,7 @@ def rope_half(x: torch.Tensor, position: int, theta: float) -> torch.Tensor:
     Llama weight files in the reference's format carry query/key rows permuted
     per head so that its interleaved rotation (src/kernels/elementwise.cu:232-258)
     on them equals this half-split rotation on the unpermuted rows of a
-    config.json + safetensors checkpoint; ``test_parts_plain.py`` proves the
+    config.json + safetensors checkpoint; ``test_plain_llama.py`` proves the
     equivalence with :func:`permute_rows_for_interleaved`.
     """
     hd = x.shape[-1]
@@ -132,10 +132,20 @@ def lm_head(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int],
-            dtype=torch.float64, rope: Optional[str] = None) -> torch.Tensor:
+            dtype=torch.float64, rope: Optional[str] = None, storage=None) -> torch.Tensor:
     """Logits [S, vocab] of one whole sequence, layer order of src/model.cu:859-1039:
     embed → per layer {norm → q,k,v → rope(q,k) → attention → o → residual →
-    norm → SwiGLU → residual} → final norm → head (tied: the embedding matrix)."""
+    norm → SwiGLU → residual} → final norm → head (tied: the embedding matrix).
+
+    ``storage`` (e.g. ``torch.bfloat16``) rounds the activations that an engine with that
+    storage type writes to memory between kernels — normed rows, q/k/v before and after
+    the rotation, the attention output, gate/up and their activation — and nothing else:
+    sums, softmax, the residual stream and the logits stay in ``dtype``.  It models where a
+    reduced-precision engine loses bits, so that inputs with large scores can be compared
+    tightly; the reference itself keeps everything in 32-bit (docs/architecture.md:748-753).
+    """
+    def st(x):
+        return x if storage is None else x.to(storage).to(dtype)
     W = {k: v.to(dtype) for k, v in weights.items()}
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads") or nh
@@ -150,18 +160,24 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int],
     h = embed(W["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        n = rmsnorm(h, W[p + "input_layernorm.weight"], eps)
-        q = (n @ W[p + "self_attn.q_proj.weight"].T).reshape(S, nh, hd)   # src/attention.cu:567-576
-        k = (n @ W[p + "self_attn.k_proj.weight"].T).reshape(S, nkv, hd)
-        v = (n @ W[p + "self_attn.v_proj.weight"].T).reshape(S, nkv, hd)
-        q = torch.stack([rot(q[t], t, theta) for t in range(S)])         # src/attention.cu:589-597
-        k = torch.stack([rot(k[t], t, theta) for t in range(S)])
-        o = attention(q, k, v, 1.0 / math.sqrt(hd))
+        n = st(rmsnorm(h, W[p + "input_layernorm.weight"], eps))
+        q = st(n @ W[p + "self_attn.q_proj.weight"].T).reshape(S, nh, hd)  # src/attention.cu:567-576
+        k = st(n @ W[p + "self_attn.k_proj.weight"].T).reshape(S, nkv, hd)
+        v = st(n @ W[p + "self_attn.v_proj.weight"].T).reshape(S, nkv, hd)
+        q = st(torch.stack([rot(q[t], t, theta) for t in range(S)]))     # src/attention.cu:589-597
+        k = st(torch.stack([rot(k[t], t, theta) for t in range(S)]))
+        o = st(attention(q, k, v, 1.0 / math.sqrt(hd)))
         h = h + o.reshape(S, nh * hd) @ W[p + "self_attn.o_proj.weight"].T  # src/attention.cu:720-728
-        n = rmsnorm(h, W[p + "post_attention_layernorm.weight"], eps)
-        h = h + swiglu(n, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
-                       W[p + "mlp.down_proj.weight"])
-    n = rmsnorm(h, W["model.norm.weight"], eps)
+        n = st(rmsnorm(h, W[p + "post_attention_layernorm.weight"], eps))
+        if storage is None:
+            h = h + swiglu(n, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
+                           W[p + "mlp.down_proj.weight"])
+        else:                                   # the same formula with its stores rounded
+            gate = st(n @ W[p + "mlp.gate_proj.weight"].T)
+            up = st(n @ W[p + "mlp.up_proj.weight"].T)
+            act = st(gate / (1.0 + torch.exp(-gate)) * up)
+            h = h + act @ W[p + "mlp.down_proj.weight"].T
+    n = st(rmsnorm(h, W["model.norm.weight"], eps))
     head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else W["lm_head.weight"]
     return lm_head(n, head)
 

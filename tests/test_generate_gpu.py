@@ -1,0 +1,235 @@
+"""Generation through the Python entry point, long decoding, first tokens, reused slots,
+sharpened attention, sampling and the replay program."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+import tiny
+from replay_cuts import rel_err, run_batch, run_tail_by_one, run_whole
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    from cretif_b200.engine import Engine
+    made = {}
+
+    def get(name, dtype, max_tokens=2048):
+        if (name, dtype, max_tokens) not in made:
+            made[(name, dtype, max_tokens)] = Engine(model_dirs[name], dtype=dtype,
+                                                     max_tokens=max_tokens)
+        return made[(name, dtype, max_tokens)]
+    return get
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_matches_plain_in_float32(engines, plain_models, name):
+    eng = engines(name, "float32")
+    cfg, w = plain_models[name]
+    prompts = [tiny.tokens(name, n, 20 + n) for n in (1, 6, 19, 70)]
+    got = eng.generate(prompts, max_tokens=9, stop_ids=[])
+    for p, r in zip(prompts, got):
+        assert r.tokens == pl.greedy(cfg, w, p, 9) and r.finish_reason == "length"
+    # the same requests without CUDA graphs, and one at a time, give the same tokens
+    again = eng.generate(prompts, max_tokens=9, stop_ids=[], use_graph=False)
+    assert [r.tokens for r in again] == [r.tokens for r in got]
+    for p, r in zip(prompts, got):
+        assert eng.generate([p], max_tokens=9, stop_ids=[])[0].tokens == r.tokens
+    eng.cache.check()
+    assert eng.cache.stats()["slots_live"] == 0
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_in_bfloat16_picks_near_best_tokens(engines, plain_models, name):
+    """bfloat16 may break near-ties differently, so every generated token is checked against
+    the plain logits of its own prefix: it must be within tolerance of the best."""
+    eng = engines(name, "bfloat16")
+    cfg, w = plain_models[name]
+    prompts = [tiny.tokens(name, n, 30 + n) for n in (3, 33, 80)]
+    got = eng.generate(prompts, max_tokens=12, stop_ids=[])
+    for p, r in zip(prompts, got):
+        assert len(r.tokens) == 12
+        logits = pl.forward(cfg, w, p + r.tokens[:-1])[len(p) - 1:]
+        for t, row in zip(r.tokens, logits):
+            assert row.max() - row[t] <= TOL["bfloat16"] * row.abs().max()
+
+
+def test_stop_tokens_end_a_sequence_and_are_kept(engines, plain_models):
+    eng = engines("A", "float32")
+    cfg, w = plain_models["A"]
+    prompts = [tiny.tokens("A", n, 40 + n) for n in (5, 9, 13)]
+    free = pl.greedy(cfg, w, prompts[1], 8)
+    stop = free[3]
+    got = eng.generate(prompts, max_tokens=8, stop_ids=[stop])
+    first = free.index(stop)
+    assert got[1].tokens == free[:first + 1] and got[1].finish_reason == "stop"
+    for p, r in zip(prompts, got):
+        want = pl.greedy(cfg, w, p, 8, stop_ids={stop})
+        assert r.tokens == want
+    # the model's own eos_token_id is the default stop set
+    assert eng.spec.stop_token_ids == [7]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(engines, plain_models, dtype):
+    """300 tokens fed one by one after a short prompt (crossing four cache blocks)."""
+    eng = engines("C", dtype)
+    cfg, w = plain_models["C"]
+    toks = tiny.tokens("C", 320, 5)
+    got = run_tail_by_one(eng, toks, tail=300)
+    assert rel_err(got, pl.forward(cfg, w, toks).numpy()) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(engines, plain_models, name, dtype):
+    """One-token prompts, alone and in a batch, then the next tokens one by one."""
+    eng = engines(name, dtype)
+    cfg, w = plain_models[name]
+    reqs = [tiny.tokens(name, 6, 50 + i) for i in range(3)]
+    wants = [pl.forward(cfg, w, r).numpy() for r in reqs]
+    assert rel_err(run_tail_by_one(eng, reqs[0], tail=5), wants[0]) <= TOL[dtype]
+    outs = run_batch(eng, reqs, [1, 1, 2])
+    for got, want in zip(outs, wants):
+        assert rel_err(got, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_reused_slot_shows_nothing_of_its_last_owner(engines, plain_models, dtype):
+    eng = engines("B", dtype, max_tokens=256)
+    cfg, w = plain_models["B"]
+    long_req, short_req = tiny.tokens("B", 200, 60), tiny.tokens("B", 30, 61)
+    alone = run_whole(eng, short_req)
+    run_whole(eng, long_req)                       # fills the slot and blocks, then frees them
+    after = run_tail_by_one(eng, short_req, tail=20)
+    assert rel_err(after, pl.forward(cfg, w, short_req).numpy()) <= TOL[dtype]
+    assert rel_err(after, alone) <= TOL[dtype]
+
+
+@pytest.fixture(scope="module")
+def sharp_model(tmp_path_factory, model_dirs):
+    """Configuration B with layer 0's query and key projections scaled up so that attention
+    is sharp: each query then reads a few particular keys, far ones included, and a wrong
+    key, position or cache slot changes the logits visibly."""
+    from safetensors import safe_open
+    from cretif_b200.weights import write_model_folder
+    d = str(tmp_path_factory.mktemp("model_B_sharp"))
+    tensors = {}
+    with safe_open(os.path.join(model_dirs["B"], "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            tensors[k] = f.get_tensor(k)
+    for name in ("q_proj", "k_proj"):
+        key = f"model.layers.0.self_attn.{name}.weight"
+        tensors[key] = (tensors[key].float() * 24.0).to(torch.bfloat16)
+    with open(os.path.join(model_dirs["B"], "config.json")) as f:
+        cfg = json.load(f)
+    write_model_folder(d, cfg, tensors)
+    return d, pl.read_model_folder(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_attention_over_hundreds_of_keys(sharp_model, dtype):
+    from cretif_b200.engine import Engine
+    d, (cfg, w) = sharp_model
+    eng = Engine(d, dtype=dtype, max_tokens=1024)
+    # With scores this large, rounding q and k to bfloat16 alone moves the softmax by more
+    # than the usual bound, in any engine; so the bfloat16 run is compared with the plain
+    # model rounded at the same stores.  float32 is compared with the exact plain model.
+    storage = torch.bfloat16 if dtype == "bfloat16" else None
+    plain = lambda t: pl.forward(cfg, w, t, storage=storage).numpy()
+    toks = tiny.tokens("B", 250, 70)
+    want = plain(toks)
+    exact = pl.forward(cfg, w, toks).numpy()
+    if storage is not None:      # the sharpening bites: plain rounding alone breaks the bound
+        assert rel_err(want, exact) > TOL[dtype]
+    assert rel_err(run_whole(eng, toks), want) <= TOL[dtype]
+    assert rel_err(run_tail_by_one(eng, toks, tail=32), want) <= TOL[dtype]
+    reqs = [toks, tiny.tokens("B", 100, 71), tiny.tokens("B", 180, 72)]
+    outs = run_batch(eng, reqs, [218, 70, 1])
+    for r, got in zip(reqs, outs):
+        assert rel_err(got, plain(r)) <= TOL[dtype]
+
+
+def test_sampling_through_the_entry_point(engines):
+    eng = engines("A", "float32")
+    prompts = [tiny.tokens("A", n, 80 + n) for n in (4, 11, 30)]
+    a = eng.generate(prompts, max_tokens=10, temperature=1.5, seed=5, stop_ids=[])
+    b = eng.generate(prompts, max_tokens=10, temperature=1.5, seed=5, stop_ids=[])
+    c = eng.generate(prompts, max_tokens=10, temperature=1.5, seed=6, stop_ids=[])
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    assert [r.tokens for r in a] != [r.tokens for r in c]
+    # request 0's draws do not depend on who shares its batch
+    alone = eng.generate(prompts[:1], max_tokens=10, temperature=1.5, seed=5, stop_ids=[])
+    assert alone[0].tokens == a[0].tokens
+    k1 = eng.generate(prompts, max_tokens=6, temperature=0.7, top_k=1, stop_ids=[])
+    g = eng.generate(prompts, max_tokens=6, stop_ids=[])
+    assert [r.tokens for r in k1] == [r.tokens for r in g]
+    with pytest.raises(ValueError):
+        eng.generate(prompts, top_k=-1)
+
+
+def test_step_refuses_what_it_cannot_run(engines):
+    from cretif_b200.cache import CacheError, CacheFull
+    from cretif_b200.engine import StepError
+    eng = engines("A", "float32")
+    s = eng.alloc_slot()
+    with pytest.raises(StepError, match="vocabulary"):
+        eng.step([(s, [1, 256])])
+    with pytest.raises(StepError, match="at least one token"):
+        eng.step([(s, [])])
+    with pytest.raises(CacheError):
+        eng.step([(s, [1]), (s, [2])])
+    with pytest.raises(CacheFull, match="longest"):
+        eng.step([(s, [1] * 129)])
+    assert eng.cache.length(s) == 0                  # refused steps left nothing behind
+    eng.step([(s, [1, 2, 3])])
+    t = eng.alloc_slot()
+    with pytest.raises(StepError, match="either all start"):
+        eng.step([(s, [4]), (t, [1, 2])])
+    with pytest.raises(StepError, match="wanted places"):
+        eng.step([(s, [4])], want=[[1]])
+    assert tuple(eng.step([(s, [4])], want=[[]]).shape) == (0, 256)
+    eng.free_slot(s); eng.free_slot(t)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, plain_models, tmp_path, dtype):
+    """bin/trace_run as a user runs it: steps on stdin, logits files out, `done` lines."""
+    cfg, w = plain_models["B"]
+    ra, rb, rc = (tiny.tokens("B", n, 90 + n) for n in (40, 9, 70))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": ra[:38], "want": [0, 37]},
+                                     {"id": "b", "tokens": rb[:8], "want": [7]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [ra[38]], "want": [0]},
+                                     {"id": "b", "tokens": [rb[8]], "want": []}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": [ra[39]], "want": [0]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": rc, "want": list(range(70))}],
+              "end": ["c"]}]
+    out = tmp_path / "out"
+    env = dict(os.environ, PYTHONPATH="")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["B"],
+         "--dtype", dtype, "--out", str(out), "--max-tokens", "192"],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+        env=env, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    V = cfg["vocab_size"]
+    la, lb, lc = (pl.forward(cfg, w, r).numpy() for r in (ra, rb, rc))
+    read = lambda i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+    tol = TOL[dtype]
+    got0 = read(0)
+    assert got0.shape == (3, V)
+    assert rel_err(got0, np.stack([la[0], la[37], lb[7]])) <= tol
+    assert rel_err(read(1), la[38:39]) <= tol
+    assert rel_err(read(2), la[39:40]) <= tol
+    assert rel_err(read(3), lc) <= tol

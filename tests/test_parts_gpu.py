@@ -1,0 +1,302 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with
+state of its own that is registered here, built and stepped without touching the package."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return torch.randn(*shape, generator=g) * scale
+
+
+def close(got, want, rel):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-30)
+    assert err <= rel, f"relative error {err:.3e} > {rel:.1e}"
+
+
+def make_ctx(cache, slots, starts, news, dtype):
+    """A StepContext for sequences in `slots` bringing `news` tokens after `starts` cached."""
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.base import StepContext
+    B, T = len(slots), int(sum(news))
+    cu = np.concatenate([[0], np.cumsum(news)])
+    tok_seq = np.repeat(np.arange(B), news)
+    tok_pos = np.arange(T) - cu[tok_seq] + np.asarray(starts)[tok_seq]
+    i32 = lambda a: torch.as_tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    return StepContext(T=T, B=B, tok_ids=i32(np.zeros(T)), tok_pos=i32(tok_pos), tok_seq=i32(tok_seq),
+                       seq_slot=i32(slots), seq_start=i32(starts), cu_seqlens=i32(cu),
+                       is_decode=all(n == 1 for n in news), max_new=max(news),
+                       max_context=int(max(s + n for s, n in zip(starts, news))),
+                       fault=ops.fault_word(DEV), dtype=dtype, device=torch.device(DEV))
+
+
+# float32: rounding of 32-bit sums.  bfloat16: the suite-wide bound for bfloat16 storage of
+# activations and cached keys/values (the same 2e-2 the engine tests use).
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from cretif_b200.parts.base import build_part
+    from cretif_b200.config import PartSpec
+    H, eps = 88, 2e-5
+    part = build_part("norm", PartSpec("rmsnorm", {"eps": eps, "name": "w"}), H, dtype, DEV)
+    w = rnd(H) * 0.1 + 1
+    part.load({"weight": w.to(torch.bfloat16)})          # stored bf16, applied in 32-bit
+    wq = w.to(torch.bfloat16).double()
+    h, d = rnd(6, H, seed=1).to(DEV), rnd(6, H, seed=2).to(DEV)
+    h2 = h.clone()
+    n = part.forward(h2, d)
+    assert n.dtype == dtype
+    close(h2, h.double() + d.double(), 1e-7)
+    close(n, pl.rmsnorm((h.double() + d.double()).cpu(), wq, eps), TOL[dtype])
+    n0 = part.forward(h.clone(), None)
+    close(n0, pl.rmsnorm(h.double().cpu(), wq, eps), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+@pytest.mark.parametrize("window", [0, 50])
+def test_attention_part_prefill_then_decode(dtype, pairing, window):
+    """The mixer alone, with its position encoding and cache: a ragged prefill of three
+    sequences, then decode steps, against the plain functions on whole sequences."""
+    from cretif_b200.cache import SequenceCache
+    from cretif_b200.config import PartSpec
+    from cretif_b200.parts.base import LayerCache, build_part
+    H, nh, nkv, hd, theta = 72, 6, 2, 32, 5000.0
+    scale = 0.2
+    params = {"num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "scale": scale,
+              "window": window,
+              "position": {"kind": "rotary", "theta": theta, "rotary_dim": hd, "pairing": pairing},
+              "names": {"q": "q", "k": "k", "v": "v", "o": "o"}}
+    part = build_part("mixer", PartSpec("attention", params), H, dtype, DEV)
+    W = {"q": rnd(nh * hd, H, scale=0.2, seed=1), "k": rnd(nkv * hd, H, scale=0.2, seed=2),
+         "v": rnd(nkv * hd, H, scale=0.2, seed=3), "o": rnd(H, nh * hd, scale=0.2, seed=4)}
+    W = {k: v.to(torch.bfloat16) for k, v in W.items()}
+    part.load(W)
+    part.prepare(512)
+    cache = SequenceCache({0: part.cache_request()}, 1024, dtype, DEV, max_len=512)
+    lens, extra = [70, 5, 130], 6
+    xs = [rnd(n + extra, H, seed=10 + i).to(torch.bfloat16) for i, n in enumerate(lens)]
+    slots = [cache.alloc_slot() for _ in lens]
+    rot = pl.rope_interleaved if pairing == "interleaved" else pl.rope_half
+
+    def plain(x):
+        x = x.double()
+        S = x.shape[0]
+        q = (x @ W["q"].double().T).reshape(S, nh, hd)
+        k = (x @ W["k"].double().T).reshape(S, nkv, hd)
+        v = (x @ W["v"].double().T).reshape(S, nkv, hd)
+        q = torch.stack([rot(q[t], t, theta) for t in range(S)])
+        k = torch.stack([rot(k[t], t, theta) for t in range(S)])
+        o = pl.attention(q, k, v, scale, window=window)
+        return o.reshape(S, nh * hd) @ W["o"].double().T
+    wants = [plain(x) for x in xs]
+
+    def run(starts, news):
+        entries = list(zip(slots, news))
+        cache.begin_step(entries)
+        ctx = make_ctx(cache, slots, starts, news, dtype)
+        x = torch.cat([xs[i][s:s + n] for i, (s, n) in enumerate(zip(starts, news))]).to(DEV).to(dtype)
+        y = part.forward(x, ctx, LayerCache(kv=cache.kv_view(0), writes=True))
+        cache.end_step(entries)
+        return y
+    y = run([0, 0, 0], lens)
+    assert y.dtype == torch.float32
+    o = 0
+    for i, n in enumerate(lens):
+        close(y[o:o + n], wants[i][:n], TOL[dtype])
+        o += n
+    rows = [[] for _ in lens]
+    for step in range(extra):
+        y = run([n + step for n in lens], [1, 1, 1])
+        for i in range(len(lens)):
+            rows[i].append(y[i])
+    for i, n in enumerate(lens):
+        close(torch.stack(rows[i]), wants[i][n:n + extra], TOL[dtype])
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_mlp_part(dtype):
+    from cretif_b200.config import PartSpec
+    from cretif_b200.parts.base import build_part
+    H, I = 72, 200
+    part = build_part("feed_forward", PartSpec("gated_mlp", {
+        "intermediate_size": I, "activation": "silu",
+        "names": {"gate": "g", "up": "u", "down": "d"}}), H, dtype, DEV)
+    W = {"gate": rnd(I, H, scale=0.3, seed=1).to(torch.bfloat16),
+         "up": rnd(I, H, scale=0.3, seed=2).to(torch.bfloat16),
+         "down": rnd(H, I, scale=0.3, seed=3).to(torch.bfloat16)}
+    part.load(W)
+    for T in (1, 9, 150):                     # decode-sized and prefill-sized
+        x = rnd(T, H, seed=T).to(torch.bfloat16)
+        y = part.forward(x.to(DEV).to(dtype), None)
+        want = pl.swiglu(x.double(), W["gate"].double(), W["up"].double(), W["down"].double())
+        close(y, want, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_tied_head(dtype):
+    from cretif_b200.config import PartSpec
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.base import build_part
+    V, H = 333, 40
+    emb = build_part("embedding", PartSpec("token_embedding", {"name": "e", "vocab_size": V}), H,
+                     dtype, DEV)
+    table = rnd(V, H, seed=1).to(torch.bfloat16)
+    emb.load({"table": table})
+    head = build_part("head", PartSpec("linear_head", {"tied": True, "name": "h",
+                                                       "vocab_size": V}), H, dtype, DEV)
+    head.load({})
+    head.tie(emb)
+    assert head.weight.data_ptr() == emb.table.data_ptr() and head.weight_bytes() == 0
+    ids = torch.tensor([0, 332, 7], dtype=torch.int32, device=DEV)
+
+    class Ctx:
+        fault = ops.fault_word(DEV)
+    h = emb.forward(ids, Ctx)
+    assert h.dtype == torch.float32
+    assert torch.equal(h.cpu(), pl.embed(table.float(), [0, 332, 7]))
+    n = rnd(3, H, seed=2).to(torch.bfloat16)
+    logits = head.forward(n.to(DEV).to(dtype), Ctx)
+    assert logits.dtype == torch.float32 and tuple(logits.shape) == (3, V)
+    close(logits, pl.lm_head(n.double(), table.double()), 1e-5 if dtype == torch.float32 else 1e-5)
+
+
+def test_prenorm_arrangement_fuses_the_residual():
+    """h += pending; a = mixer(norm(h)); h += a; returns ffn(norm(h)) unadded."""
+    from cretif_b200.parts.base import lookup_part
+
+    class Norm:
+        def forward(self, h, delta=None, rows=None, write_h=True):
+            if delta is not None:
+                h += delta
+            return h * 2
+
+    class Mixer:
+        def forward(self, x, ctx, cache):
+            return x + 1
+
+    class FF:
+        def forward(self, x, ctx):
+            return x * 10
+
+    class Layer:
+        mixer_norm, mixer, feed_forward_norm, feed_forward = Norm(), Mixer(), Norm(), FF()
+    run = lookup_part("arrangement", "prenorm")
+    h = torch.ones(2, 3)
+    out = run(Layer, h, torch.full((2, 3), 0.5), None, None)
+    # h = 1.5; a = 2*1.5 + 1 = 4; h = 5.5; out = 10 * (2 * 5.5) = 110
+    assert torch.allclose(h, torch.full((2, 3), 5.5)) and torch.allclose(out, torch.full((2, 3), 110.0))
+
+
+# ---------------------------------------------------------------------------------------
+# A toy architecture defined here: its mixer keeps a running sum of its inputs per sequence
+# (fixed-size state, no keys or values) and returns the running mean.
+# ---------------------------------------------------------------------------------------
+def _register_toy():
+    from cretif_b200.cache import StateRequest
+    from cretif_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
+                                    register_architecture)
+    from cretif_b200.parts.base import Part, register_part
+    from cretif_b200.weights.loader import WeightSpec
+
+    @register_part("mixer", "running_mean")
+    class RunningMean(Part):
+        """y_t = gain * mean(x_0..x_t); state per sequence: [sum (H floats), count]."""
+
+        @classmethod
+        def weight_specs(cls, params, hidden_size):
+            return {"gain": (params["name"], WeightSpec((hidden_size,), init=(1.0, 0.1)))}
+
+        def load(self, tensors):
+            self.gain = self._vector32(tensors["gain"])
+
+        def cache_request(self):
+            return StateRequest((self.hidden_size + 1,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            cu = ctx.cu_seqlens.tolist()
+            for b, slot in enumerate(ctx.seq_slot.tolist()):
+                st = cache.state[slot]
+                xs = x[cu[b]:cu[b + 1]].float()
+                sums = st[:-1] + torch.cumsum(xs, dim=0)
+                counts = st[-1] + torch.arange(1, xs.shape[0] + 1, device=x.device)
+                out[cu[b]:cu[b + 1]] = self.gain * sums / counts[:, None]
+                if cache.writes:
+                    st[:-1] = sums[-1]
+                    st[-1] = counts[-1]
+            return out
+
+    def config_from_dict(raw):
+        return dict(raw)
+
+    def build_spec(cfg):
+        H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+        norm = lambda name: PartSpec("rmsnorm", {"eps": 1e-5, "name": name})
+        layers = [LayerSpec(prefix=f"blocks.{i}.",
+                            mixer=PartSpec("running_mean", {"name": "mix.gain"}),
+                            feed_forward=PartSpec("gated_mlp", {
+                                "intermediate_size": cfg["ffn"], "activation": "silu",
+                                "names": {"gate": "ff.g", "up": "ff.u", "down": "ff.d"}}),
+                            mixer_norm=norm("n1"), feed_forward_norm=norm("n2"))
+                  for i in range(L)]
+        return ModelSpec(architecture="ToyRunningMean", vocab_size=cfg["vocab_size"],
+                         hidden_size=H, embedding=PartSpec("token_embedding", {"name": "emb"}),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(L)],
+                         final_norm=norm("final"),
+                         head=PartSpec("linear_head", {"tied": True, "name": "head",
+                                                       "tied_to": "emb"}),
+                         max_positions=cfg["max_positions"])
+    register_architecture("ToyRunningMean", config_from_dict, build_spec)
+
+
+def _toy_plain(w, L, ids):
+    """The toy model on a whole sequence, in float64."""
+    h = pl.embed(w["emb"], ids)
+    for i in range(L):
+        p = f"blocks.{i}."
+        n = pl.rmsnorm(h, w[p + "n1"], 1e-5)
+        mean = torch.cumsum(n, dim=0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
+        h = h + w[p + "mix.gain"] * mean
+        n = pl.rmsnorm(h, w[p + "n2"], 1e-5)
+        h = h + pl.swiglu(n, w[p + "ff.g"], w[p + "ff.u"], w[p + "ff.d"])
+    return pl.lm_head(pl.rmsnorm(h, w["final"], 1e-5), w["emb"])
+
+
+def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    import json
+    from replay_cuts import rel_err, run_batch, run_tail_by_one, run_whole
+    from cretif_b200.engine import Engine
+    from cretif_b200.weights.random_model import write_random_model
+    _register_toy()
+    cfg = {"architectures": ["ToyRunningMean"], "hidden_size": 48, "num_hidden_layers": 2,
+           "ffn": 80, "vocab_size": 120, "max_positions": 256}
+    d = str(tmp_path / "toy")
+    write_random_model(d, cfg, seed=4, dtype=torch.float32)
+    eng = Engine(d, dtype="float32", max_tokens=1024)
+    st = eng.cache.stats()
+    assert st["groups"] == [] and st["state_bytes"] == eng.cache.max_slots * 2 * 49 * 4
+    _, w = pl.read_model_folder(d)
+    rng = np.random.default_rng(0)
+    reqs = [rng.integers(0, 120, size=n).tolist() for n in (40, 7, 23)]
+    wants = [_toy_plain(w, 2, r).numpy() for r in reqs]
+    for r, want in zip(reqs, wants):
+        assert rel_err(run_whole(eng, r), want) < 1e-4
+        assert rel_err(run_tail_by_one(eng, r, tail=10), want) < 1e-4
+    for _ in range(2):          # the second round takes the slots (and their state) again
+        outs = run_batch(eng, reqs, [30, 2, 23])
+        for got, want in zip(outs, wants):
+            assert rel_err(got, want) < 1e-4
+    eng.cache.check()

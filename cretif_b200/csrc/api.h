@@ -58,16 +58,32 @@ int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const v
                      const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
                      int window, int bt, int T, void* stream);
 
-// Decode attention (one query token per sequence), bfloat16, keys split into n_splits
+// Decode attention (one query token per sequence), bfloat16, keys split into n_splits <= 64
 // ranges per (sequence, kv head); part_o/part_ml are float32 scratch of the sizes that
-// cretif_attn_decode_scratch_floats reports.  block tokens must be 64.
+// cretif_attn_decode_scratch_floats reports, counters is int32 [B * nkv], zero before the
+// first launch and left zero by every launch.  block tokens must be 64.
 int cretif_attn_decode_scratch_floats(int B, int nh, int hd, int n_splits, long long* part_o,
                                       long long* part_ml);
 int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kc, const void* vc,
                        const int* table, int table_stride, const int* tok_pos, const int* tok_seq,
                        const int* seq_slot, int nh, int nkv, int hd, float scale, int window,
-                       int bt, int B, int n_splits, float* part_o, float* part_ml,
+                       int bt, int B, int n_splits, float* part_o, float* part_ml, int* counters,
                        unsigned int* fault, void* stream);
+
+// Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
+// is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
+int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
+                        const int* rows, float eps, const void* W, int ldw, void* C, int c_dt,
+                        int ldc, int accumulate, int M, int N, int K, void* stream);
+int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const void* Wqkv, int ldw,
+                          void* Q, int ldq, const float* cos_t, const float* sin_t, int pairing,
+                          int nh, int nkv, int hd, const int* tok_pos, const int* tok_seq,
+                          const int* seq_slot, const int* table, int table_stride, void* kc,
+                          void* vc, int bt, int write_cache, int M, int K, unsigned int* fault,
+                          void* stream);
+int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
+                              int ldw, void* act, int I, int M, int K, void* stream);
+int cretif_fused_smem_ok(int M, int K);
 
 // Causal attention for whole prompts on tcgen05 (bfloat16, head_dim a multiple of 16 up to
 // 128, 64-token cache blocks).  qkv rows hold the query heads first; sequence b brings the

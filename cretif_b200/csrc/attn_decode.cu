@@ -6,10 +6,13 @@
 // fills the GPU; one CTA streams its range's K and V tiles once (bulk asynchronous copies
 // of the contiguous block_tokens x head_dim tiles into shared memory, two stages deep) and
 // serves all query heads that share the key/value head.  Scores, running maximum and sum
-// are 32-bit.  A second small kernel merges the per-range partial results.
+// are 32-bit.  The CTA that finishes last for a (sequence, key/value head) — found with a
+// counter in global memory that it resets for the next launch — merges the ranges' partial
+// results in a fixed order and writes the output, so there is no second launch.
 //
-// Scratch: part_o [tokens, heads, n_splits, head_dim] and part_ml [tokens, heads,
-// n_splits, 2], both float32, provided by the caller.
+// Scratch, provided by the caller: part_o [tokens, heads, n_splits, head_dim] and part_ml
+// [tokens, heads, n_splits, 2] in float32, and `counters` [tokens * kv_heads] int32 that must
+// be zero before the first launch (every launch leaves them zero).
 #include "api.h"
 #include "common.cuh"
 
@@ -67,8 +70,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                    const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
                    int window, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
                    unsigned int* __restrict__ fault) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int is_last;
   const int g = nh / nkv;
   const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
@@ -92,15 +97,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
 
   float* po = part_o + (((size_t)b * nh + (size_t)kvh * g) * n_splits + split) * hd;
   float* pml = part_ml + (((size_t)b * nh + (size_t)kvh * g) * n_splits + split) * 2;
-  if (t_begin >= t_end) {              // nothing in this range: an empty partial
+  const bool empty_range = t_begin >= t_end;
+  if (empty_range) {                   // nothing in this range: an empty partial
     for (int j = 0; j < g; ++j) {
       if (tid == 0) { pml[(size_t)j * n_splits * 2] = -INFINITY; pml[(size_t)j * n_splits * 2 + 1] = 0.f; }
       for (int d = tid; d < hd; d += kDecThreads) po[(size_t)j * n_splits * hd + d] = 0.f;
     }
-    return;
   }
 
-  if (tid == 0) {
+  if (tid == 0 && !empty_range) {
     for (int s = 0; s < kDecStages; ++s) mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -119,7 +124,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
     bulk_load(ktile + (size_t)stage * tile_elems, kc + off, tile_bytes, &bars[stage]);
     bulk_load(vtile + (size_t)stage * tile_elems, vc + off, tile_bytes, &bars[stage]);
   };
-  if (tid == 0) {
+  if (tid == 0 && !empty_range) {
     issue(t_begin, 0);
     if (t_begin + 1 < t_end) issue(t_begin + 1, 1);
   }
@@ -248,7 +253,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   // ---- reduce the key groups' accumulators and write the partial
 #pragma unroll
   for (int j = 0; j < GMAX; ++j) {
-    if (j >= g) break;
+    if (j >= g || empty_range) break;
     __syncthreads();
     if (pv_active) {
 #pragma unroll
@@ -270,27 +275,45 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
       pml[(size_t)j * n_splits * 2 + 1] = lj;
     }
   }
-}
 
-// grid (nh, B): out[b, h, :] = sum_s w_s o_s / sum_s w_s l_s, w_s = exp(m_s - max m)
-template <typename TO>
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, TO* __restrict__ out,
-                                         int ldo, int nh, int hd, int n_splits) {
-  const int h = blockIdx.x, b = blockIdx.y;
-  const float* ml = part_ml + ((size_t)b * nh + h) * n_splits * 2;
-  const float* po = part_o + ((size_t)b * nh + h) * n_splits * hd;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
-  float denom = 0.f;
-  for (int s = 0; s < n_splits; ++s)
-    if (ml[2 * s] != -INFINITY) denom += expf(ml[2 * s] - m) * ml[2 * s + 1];
-  const float inv = 1.0f / denom;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float acc = 0.f;
+  // ---- the CTA that finishes last for this (sequence, kv head) merges the ranges
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* ctr = counters + (size_t)b * nkv + kvh;
+    const int prev = atomicAdd(ctr, 1);
+    is_last = prev == n_splits - 1;
+    if (is_last) *ctr = 0;               // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* wts = ps;                       // [g][n_splits] weights, reusing the score buffer
+  float* inv_den = alpha;                // [g]
+  const float* ml_base = part_ml + ((size_t)b * nh + (size_t)kvh * g) * n_splits * 2;
+  const float* po_base = part_o + ((size_t)b * nh + (size_t)kvh * g) * n_splits * hd;
+  for (int j = warp; j < g; j += 4) {
+    float mx = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) mx = fmaxf(mx, __ldcg(ml_base + ((size_t)j * n_splits + s) * 2));
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int s = lane; s < n_splits; s += 32) {
+      const float ms = __ldcg(ml_base + ((size_t)j * n_splits + s) * 2);
+      const float ls = __ldcg(ml_base + ((size_t)j * n_splits + s) * 2 + 1);
+      const float w = (ms == -INFINITY) ? 0.f : expf(ms - mx);
+      if (j * n_splits + s < GMAX * kDecTile) wts[j * n_splits + s] = w;
+      den += w * ls;
+    }
+    den = warp_sum(den);
+    if (lane == 0) inv_den[j] = 1.0f / den;
+  }
+  __syncthreads();
+  for (int i = tid; i < g * hd; i += kDecThreads) {
+    const int j = i / hd, d = i - j * hd;
+    float acc_o = 0.f;
     for (int s = 0; s < n_splits; ++s)
-      if (ml[2 * s] != -INFINITY) acc = fmaf(expf(ml[2 * s] - m), po[(size_t)s * hd + d], acc);
-    out[(size_t)b * ldo + (size_t)h * hd + d] = from_float<TO>(acc * inv);
+      acc_o = fmaf(wts[j * n_splits + s], __ldcg(po_base + ((size_t)j * n_splits + s) * hd + d), acc_o);
+    out[(size_t)b * ldo + (size_t)(kvh * g + j) * hd + d] = __float2bfloat16_rn(acc_o * inv_den[j]);
   }
 }
 
@@ -318,11 +341,11 @@ extern "C" int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, co
                                   const void* vc, const int* table, int table_stride,
                                   const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                   int nh, int nkv, int hd, float scale, int window, int bt, int B,
-                                  int n_splits, float* part_o, float* part_ml,
+                                  int n_splits, float* part_o, float* part_ml, int* counters,
                                   unsigned int* fault, void* stream) {
   if (B <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > kDecMaxGroup || hd % 16 || hd < 16 ||
-      hd > 256 || bt != kDecTile || n_splits <= 0 || n_splits > 65535 || nkv > 65535 ||
+      hd > 256 || bt != kDecTile || n_splits <= 0 || n_splits > kDecTile || nkv > 65535 ||
       B > 65535 || window < 0)
     return kBadArgument;
   if (((uintptr_t)kc | (uintptr_t)vc) & 15) return kMisaligned;
@@ -344,7 +367,7 @@ extern "C" int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, co
     attn_decode_kernel<GMAX><<<grid, kDecThreads, smem, st>>>(                                  \
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, table, \
         table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, part_o, part_ml,  \
-        fault);                                                                                 \
+        (__nv_bfloat16*)out, ldo, counters, fault);                                             \
     rc = launch_status();                                                                       \
   } while (0)
   if (g == 1) CRETIF_DECODE(1);
@@ -352,8 +375,5 @@ extern "C" int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, co
   else if (g <= 4) CRETIF_DECODE(4);
   else CRETIF_DECODE(8);
 #undef CRETIF_DECODE
-  if (rc) return rc;
-  attn_decode_merge_kernel<__nv_bfloat16><<<dim3(nh, B), 64, 0, st>>>(
-      part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, hd, n_splits);
-  return launch_status();
+  return rc;
 }

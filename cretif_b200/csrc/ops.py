@@ -309,13 +309,93 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
             or not vc.is_contiguous()):
         raise KernelError("attn_decode: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
+    if n_splits > 64:
+        raise KernelError("attn_decode: at most 64 ranges per (sequence, kv head)")
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
+    counters = _decode_counters(q.device, B * nkv)
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
         table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
         ctypes.c_float(scale), window, block_tokens, B, n_splits, _p(part_o), _p(part_ml),
-        _p(fault), _stream()), "attn_decode", kernels=2)
+        _p(counters), _p(fault), _stream()), "attn_decode")
+
+
+_COUNTERS = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters the decode attention uses to find its last CTA; every launch
+    leaves them zero, so one buffer per device serves all launches on a stream."""
+    key = str(torch.device(device))
+    if key not in _COUNTERS or _COUNTERS[key].numel() < n:
+        _COUNTERS[key] = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+    return _COUNTERS[key]
+
+
+# ------------------------------------------------------------------ fused decode projections
+def fused_supported(M: int, K: int, w) -> bool:
+    return (w.dtype == torch.bfloat16 and 0 < M <= 64 and K % 8 == 0 and w.stride(1) == 1
+            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+            and bool(lib().cretif_fused_smem_ok(M, K)))
+
+
+def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool = False) -> None:
+    """out (+)= bf16(rmsnorm(h[rows])) · wᵀ in one kernel (decode-sized row counts)."""
+    _need(h, "h", torch.float32, 2); _need(norm_w, "norm weight", torch.float32, 1)
+    _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
+    K = h.shape[1]
+    M = h.shape[0] if rows is None else rows.numel()
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or not h.is_contiguous():
+        raise KernelError("fused_norm_linear: shapes do not fit")
+    _check(lib().cretif_fused_linear(None, 0, _p(h), _p(norm_w), _p(rows), ctypes.c_float(eps),
+                                     _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
+                                     int(accumulate), M, N, K, _stream()), "fused_norm_linear")
+
+
+def fused_linear_add(x, w, h) -> None:
+    """h += x · wᵀ (x bfloat16, h the float32 residual stream)."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2)
+    _need(h, "h", torch.float32, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(h.shape) != (M, N):
+        raise KernelError("fused_linear_add: shapes do not fit")
+    _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
+                                     _p(w), _rows(w, "w"), _p(h), F32, _rows(h, "h"), 1, M, N, K,
+                                     _stream()), "fused_linear_add")
+
+
+def fused_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, cos, sin, pairing: int, nh: int,
+                   nkv: int, hd: int, tok_pos, tok_seq, seq_slot, table, kc, vc,
+                   block_tokens: int, write_cache: bool, fault) -> None:
+    """norm → q|k|v product → rotary → q buffer and block cache, one kernel."""
+    _need(h, "h", torch.float32, 2); _need(w_qkv, "w_qkv", torch.bfloat16, 2)
+    _need(q_out, "q", torch.bfloat16, 2)
+    M, K = h.shape
+    if w_qkv.shape != ((nh + 2 * nkv) * hd, K) or not h.is_contiguous():
+        raise KernelError("fused_qkv_rope: shapes do not fit")
+    if cos.shape[1] != hd // 2:
+        raise KernelError("fused_qkv_rope: needs rotary_dim == head_dim")
+    _check(lib().cretif_fused_qkv_rope(
+        _p(h), _p(norm_w), ctypes.c_float(eps), _p(w_qkv), _rows(w_qkv, "w_qkv"), _p(q_out),
+        _rows(q_out, "q"), _p(cos), _p(sin), pairing, nh, nkv, hd, _p(tok_pos), _p(tok_seq),
+        _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc), block_tokens,
+        int(write_cache), M, K, _p(fault), _stream()), "fused_qkv_rope")
+
+
+def fused_gate_up_silu(h, norm_w, eps: float, w_gu, act) -> None:
+    """act = silu(norm(h)·Wgᵀ) ⊙ (norm(h)·Wuᵀ) with [Wg; Wu] stacked, one kernel."""
+    _need(h, "h", torch.float32, 2); _need(w_gu, "w_gu", torch.bfloat16, 2)
+    _need(act, "act", torch.bfloat16, 2)
+    M, K = h.shape
+    I = act.shape[1]
+    if tuple(w_gu.shape) != (2 * I, K) or act.shape[0] != M or not act.is_contiguous():
+        raise KernelError("fused_gate_up_silu: shapes do not fit")
+    _check(lib().cretif_fused_gate_up_silu(_p(h), _p(norm_w), ctypes.c_float(eps), _p(w_gu),
+                                           _rows(w_gu, "w_gu"), _p(act), I, M, K, _stream()),
+           "fused_gate_up_silu")
 
 
 def attn_prefill_supported(hd: int, block_tokens: int) -> bool:

@@ -133,6 +133,10 @@ class Model:
             pending = layer.run(layer, h, pending, ctx, view)
         if want_rows is not None and want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
+        if hasattr(self.head, "forward_from_residual"):
+            logits = self.head.forward_from_residual(h, pending, self.final_norm, want_rows, ctx)
+            if logits is not None:
+                return logits
         n = self.final_norm.forward(h, pending, rows=want_rows, write_h=False)
         return self.head.forward(n, ctx)
 

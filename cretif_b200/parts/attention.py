@@ -20,6 +20,19 @@ from .base import Part, build_part, register_part
 from .linear import linear
 
 _force_plain = False
+_fused_steps = True
+# Steps of at most this many tokens take the fused projection kernels.
+FUSED_MAX_TOKENS = 64
+
+
+def fused_steps_enabled() -> bool:
+    return _fused_steps
+
+
+def enable_fused_steps(on: bool) -> None:
+    """Switch the fused few-token kernels on or off (tests compare both ways)."""
+    global _fused_steps
+    _fused_steps = bool(on)
 
 
 def force_plain_attention(on: bool) -> None:
@@ -79,6 +92,29 @@ class Attention(Part):
         o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
         self.attend(qkv, o, ctx, cache.kv)
         return linear(o, self.w_o, out_dtype=torch.float32)
+
+    def forward_from_residual(self, h, norm, ctx, cache) -> bool:
+        """Few tokens, bfloat16: norm + q|k|v + rotary + cache write in one kernel, attention,
+        then the output projection added into ``h``.  False if the step does not qualify."""
+        from .norm import RMSNorm
+        from .position import Rotary
+        if (_force_plain or not fused_steps_enabled() or self.dtype != torch.bfloat16
+                or ctx.T > FUSED_MAX_TOKENS or type(norm) is not RMSNorm
+                or type(self.position) is not Rotary or self.position.rot_dim != self.hd
+                or cache.kv is None or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
+                or not ops.fused_supported(ctx.T, self.q_dim, self.w_o)):
+            return False
+        kv = cache.kv
+        cos, sin = self.position._table
+        q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=h.device)
+        ops.fused_qkv_rope(h, norm.weight, norm.eps, self.w_qkv, q, cos, sin,
+                           self.position.pairing, self.nh, self.nkv, self.hd, ctx.tok_pos,
+                           ctx.tok_seq, ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens,
+                           cache.writes, ctx.fault)
+        o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=h.device)
+        self.attend(q, o, ctx, kv)
+        ops.fused_linear_add(o, self.w_o, h)
+        return True
 
     def attend(self, q, o, ctx, kv):
         if not _force_plain and self.dtype == torch.bfloat16:

@@ -42,5 +42,21 @@ class GatedMLP(Part):
         ops.silu_mul(gu, act)
         return linear(act, self.w_down, out_dtype=torch.float32)
 
+    def forward_from_residual(self, h, norm, ctx) -> bool:
+        """Few tokens, bfloat16: norm + gate|up + SiLU·mul in one kernel, then the down
+        projection added into ``h``.  False if the step does not qualify."""
+        from .attention import FUSED_MAX_TOKENS, fused_steps_enabled
+        from .norm import RMSNorm
+        T = h.shape[0]
+        if (not fused_steps_enabled() or self.dtype != torch.bfloat16 or T > FUSED_MAX_TOKENS
+                or type(norm) is not RMSNorm
+                or not ops.fused_supported(T, self.hidden_size, self.w_gate_up)
+                or not ops.fused_supported(T, self.inter, self.w_down)):
+            return False
+        act = torch.empty((T, self.inter), dtype=self.dtype, device=h.device)
+        ops.fused_gate_up_silu(h, norm.weight, norm.eps, self.w_gate_up, act)
+        ops.fused_linear_add(act, self.w_down, h)
+        return True
+
     def weight_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()

@@ -80,3 +80,21 @@ def test_unequal_batches_reuse_slots(engines, plain_logits, name, dtype):
             assert rel_err(got, plain_logits(name, r)) <= TOL[dtype], (name, round_, len(r))
         eng.cache.check()
         assert eng.cache.stats()["slots_live"] == 0
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_bfloat16_without_the_fused_few_token_kernels(engines, plain_logits, name):
+    """The separate norm / product / rotary / activation kernels serve steps the fused ones
+    refuse; switched to by hand here, they give the same logits within the same bound."""
+    from cretif_b200.parts.attention import enable_fused_steps
+    eng = engines(name, "bfloat16")
+    toks = tiny.tokens(name, LENGTHS[name][3] + 5, 9)
+    fused = run_tail_by_one(eng, toks, tail=32)
+    enable_fused_steps(False)
+    try:
+        plain = run_tail_by_one(eng, toks, tail=32)
+    finally:
+        enable_fused_steps(True)
+    want = plain_logits(name, toks)
+    assert rel_err(fused, want) <= TOL["bfloat16"] and rel_err(plain, want) <= TOL["bfloat16"]
+    assert rel_err(fused, plain) <= TOL["bfloat16"]

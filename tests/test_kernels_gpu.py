@@ -117,6 +117,98 @@ def test_gemm_tc(ops, M, N, K, bn):
     assert fault.item() == 0
 
 
+# ------------------------------------------------------------------ fused decode projections
+def _norm_bf16(h, w, eps, rows=None):
+    """bf16(rmsnorm(h[rows])) as the fused prologue stores it, in float64."""
+    x = h.double().cpu()
+    if rows is not None:
+        x = x[rows]
+    n = x * w.double().cpu() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    return n.to(torch.bfloat16).double()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1000, 576), (5, 50, 104), (16, 333, 200),
+                                   (33, 96, 72), (64, 130, 576)])
+def test_fused_norm_linear_and_add(ops, M, N, K):
+    eps = 1e-5
+    h, nw = rnd(M + 3, K), rnd(K, seed=1) * 0.1 + 1
+    w = rnd(N, K, dtype=torch.bfloat16, seed=2)
+    assert ops.fused_supported(M, K, w)
+    out = torch.empty(M, N, device=DEV)
+    ops.fused_norm_linear(h[:M].contiguous(), nw, eps, w, out)
+    close(out, _norm_bf16(h[:M], nw, eps) @ w.double().cpu().T, 3e-3)
+    rows = torch.tensor([(3 * i + 2) % (M + 3) for i in range(M)], dtype=torch.int32, device=DEV)
+    ops.fused_norm_linear(h, nw, eps, w, out, rows=rows)
+    close(out, _norm_bf16(h, nw, eps, rows.cpu().long()) @ w.double().cpu().T, 3e-3)
+    x = rnd(M, K, dtype=torch.bfloat16, seed=4)
+    base = rnd(M, N, seed=5)
+    acc = base.clone()
+    ops.fused_linear_add(x, w, acc)
+    close(acc, base.double().cpu() + x.double().cpu() @ w.double().cpu().T, 1e-5)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 1536, 576), (7, 173, 104), (20, 256, 96)])
+def test_fused_gate_up_silu_equals_the_separate_kernels(ops, M, I, K):
+    eps = 1e-6
+    h, nw = rnd(M, K), rnd(K, seed=1) * 0.1 + 1
+    w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
+    act = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+    ops.fused_gate_up_silu(h, nw, eps, w, act)
+    n = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    ops.add_rmsnorm(h.clone(), None, nw, n, eps)
+    gu = torch.empty(M, 2 * I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_simt(n, w, gu)
+    want = torch.empty(M, I, device=DEV, dtype=torch.bfloat16)
+    ops.silu_mul(gu, want)
+    close(act, want, 1e-2)                     # the same roundings; sums in another order
+    x = _norm_bf16(h, nw, eps)
+    g = (x @ w[:I].double().cpu().T).to(torch.bfloat16).double()
+    u = (x @ w[I:].double().cpu().T).to(torch.bfloat16).double()
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
+
+
+@pytest.mark.parametrize("pairing", [0, 1])
+@pytest.mark.parametrize("nh,nkv,hd,K", [(4, 2, 16, 64), (9, 3, 64, 576), (3, 1, 32, 96),
+                                         (5, 5, 48, 104)])
+def test_fused_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K):
+    eps, theta, P = 1e-5, 10000.0, 256
+    lens = [5, 70, 130]
+    j = torch.arange(hd // 2, dtype=torch.float64)
+    ang = torch.arange(P, dtype=torch.float64)[:, None] / theta ** (2 * j / hd)[None, :]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    qpos = [4, 3, 64, 69, 129, 0]
+    qseq = [0, 0, 1, 1, 2, 2]
+    T = len(qpos)
+    pos_t = torch.tensor(qpos, dtype=torch.int32, device=DEV)
+    seq_t = torch.tensor(qseq, dtype=torch.int32, device=DEV)
+    h, nw = rnd(T, K), rnd(K, seed=1) * 0.1 + 1
+    w = rnd((nh + 2 * nkv) * hd, K, dtype=torch.bfloat16, seed=2, scale=0.3)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    # separate kernels
+    ca = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    n = torch.empty(T, K, device=DEV, dtype=torch.bfloat16)
+    ops.add_rmsnorm(h.clone(), None, nw, n, eps)
+    qkv = torch.empty(T, (nh + 2 * nkv) * hd, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_simt(n, w, qkv)
+    ops.rope_kv_append(qkv, cos, sin, pairing, hd, nh, nkv, hd, pos_t, seq_t, ca.seq_slot,
+                       ca.table, ca.k, ca.v, 64, True, fault)
+    # fused
+    cb = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    q = torch.zeros(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    ops.fused_qkv_rope(h, nw, eps, w, q, cos, sin, pairing, nh, nkv, hd, pos_t, seq_t,
+                       cb.seq_slot, cb.table, cb.k, cb.v, 64, True, fault)
+    assert fault.item() == 0
+    close(q, qkv[:, :nh * hd], 1e-2)
+    close(cb.k, ca.k, 1e-2)
+    close(cb.v, ca.v, 1e-2)
+    # and writing can be switched off (a visit that borrows another visit's cache)
+    cc = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    before = cc.k.clone()
+    ops.fused_qkv_rope(h, nw, eps, w, q, cos, sin, pairing, nh, nkv, hd, pos_t, seq_t,
+                       cc.seq_slot, cc.table, cc.k, cc.v, 64, False, fault)
+    assert torch.equal(cc.k, before)
+
+
 # ------------------------------------------------------------------ row-wise kernels
 @pytest.mark.parametrize("T,H", [(1, 10), (5, 100), (3, 576), (2, 3000)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])

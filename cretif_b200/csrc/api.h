@@ -84,6 +84,8 @@ int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const 
 int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
                               int ldw, void* act, int I, int M, int K, void* stream);
 int cretif_fused_smem_ok(int M, int K);
+// Programmatic dependent launch of the fused kernels on (default) or off; returns the old value.
+int cretif_set_dependent_launch(int on);
 
 // Causal attention for whole prompts on tcgen05 (bfloat16, head_dim a multiple of 16 up to
 // 128, 64-token cache blocks).  qkv rows hold the query heads first; sequence b brings the

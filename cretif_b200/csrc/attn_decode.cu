@@ -74,6 +74,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
                    unsigned int* __restrict__ fault) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int is_last;
+  // A kernel launched behind this one with programmatic serialization may start its
+  // prologue now; it still waits for this grid to finish before it reads the output.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int g = nh / nkv;
   const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
@@ -105,16 +108,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
     }
   }
 
-  if (tid == 0 && !empty_range) {
-    for (int s = 0; s < kDecStages; ++s) mbar_init(&bars[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  for (int i = tid; i < g * hd; i += kDecThreads) {
-    const int j = i / hd, d = i - j * hd;
-    qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)(kvh * g + j) * hd + d]);
-  }
-  __syncthreads();
-
+  // Thread 0 sets up the barriers and asks for the first tiles at once; the others fill the
+  // query buffer meanwhile.
   const uint32_t tile_bytes = (uint32_t)tile_elems * 2u;
   auto issue = [&](int tile, int stage) {
     const int blk = tab[tile];
@@ -125,9 +120,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
     bulk_load(vtile + (size_t)stage * tile_elems, vc + off, tile_bytes, &bars[stage]);
   };
   if (tid == 0 && !empty_range) {
+    for (int s = 0; s < kDecStages; ++s) mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     issue(t_begin, 0);
     if (t_begin + 1 < t_end) issue(t_begin + 1, 1);
   }
+  for (int i = tid; i < g * hd; i += kDecThreads) {
+    const int j = i / hd, d = i - j * hd;
+    qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)(kvh * g + j) * hd + d]);
+  }
+  __syncthreads();
 
   // thread roles
   const int key_r = tid >> 1, half = tid & 1;            // QK: 2 threads per key
@@ -277,17 +279,19 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   }
 
   // ---- the CTA that finishes last for this (sequence, kv head) merges the ranges
-  __threadfence();
-  __syncthreads();
+  __syncthreads();                       // the CTA's partial is written ...
   if (tid == 0) {
+    __threadfence();                     // ... and made visible to the device by one fence
     int* ctr = counters + (size_t)b * nkv + kvh;
     const int prev = atomicAdd(ctr, 1);
     is_last = prev == n_splits - 1;
-    if (is_last) *ctr = 0;               // ready for the next launch
+    if (is_last) {
+      *ctr = 0;                          // ready for the next launch
+      __threadfence();                   // the other CTAs' partials are read after this
+    }
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
   float* wts = ps;                       // [g][n_splits] weights, reusing the score buffer
   float* inv_den = alpha;                // [g]
   const float* ml_base = part_ml + ((size_t)b * nh + (size_t)kvh * g) * n_splits * 2;
@@ -311,8 +315,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   for (int i = tid; i < g * hd; i += kDecThreads) {
     const int j = i / hd, d = i - j * hd;
     float acc_o = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-      acc_o = fmaf(wts[j * n_splits + s], __ldcg(po_base + ((size_t)j * n_splits + s) * hd + d), acc_o);
+    for (int s0 = 0; s0 < n_splits; s0 += 16) {       // 16 loads in flight, summed in order
+      float v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        v[u] = s0 + u < n_splits ? __ldcg(po_base + ((size_t)j * n_splits + s0 + u) * hd + d) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        if (s0 + u < n_splits) acc_o = fmaf(wts[j * n_splits + s0 + u], v[u], acc_o);
+    }
     out[(size_t)b * ldo + (size_t)(kvh * g + j) * hd + d] = __float2bfloat16_rn(acc_o * inv_den[j]);
   }
 }

@@ -93,77 +93,9 @@ __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
   }
 }
 
-template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(kFuWarps * 32)
-skinny_fused_kernel(const FusedParams p) {
-  extern __shared__ __align__(16) unsigned char fsmem[];
-  float(*red)[kFuRows][8 * NT + 1] = reinterpret_cast<float(*)[kFuRows][8 * NT + 1]>(fsmem);
-  // x tile (norm prologue) after the reduction buffer; row stride ≡ 64 (mod 128) bytes so
-  // that a quarter-warp's eight 16-byte reads touch all banks once
-  const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;
-  unsigned char* xs = fsmem + sizeof(float) * kFuWarps * kFuRows * (8 * NT + 1);
-  xs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(xs) + 15) & ~uintptr_t(15));
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = lane >> 2, c = lane & 3;
-  const int tile = blockIdx.x;
-
-  if (PRO == kProNorm) {
-    for (int m = warp; m < p.M; m += kFuWarps) {
-      const float* hrow = p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K;
-      float ss = 0.f;
-      for (int k = lane; k < p.K; k += 32) { const float v = hrow[k]; ss += v * v; }
-      ss = warp_sum(ss);
-      const float inv = rsqrtf(ss / (float)p.K + p.eps);
-      __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
-      for (int k = lane; k < p.K; k += 32)
-        xr[k] = __float2bfloat16_rn(hrow[k] * p.norm_w[k] * inv);
-    }
-    __syncthreads();
-  }
-
-  const int row_a = tile_row<EPI>(p, tile, r), row_b = tile_row<EPI>(p, tile, r + 8);
-  const __nv_bfloat16* wa = p.W + (size_t)max(row_a, 0) * p.ldw + c * 8;
-  const __nv_bfloat16* wb = p.W + (size_t)max(row_b, 0) * p.ldw + c * 8;
-
-  float acc[NT][4];
-#pragma unroll
-  for (int t = 0; t < NT; ++t)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
-
-  const int n_chunks = (p.K + 31) >> 5;
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  for (int ch = warp; ch < n_chunks; ch += kFuWarps) {
-    const int k = ch * 32 + c * 8;
-    const bool in = k < p.K;
-    const uint4 ua = in ? __ldg(reinterpret_cast<const uint4*>(wa + ch * 32)) : zero;
-    const uint4 ub = in ? __ldg(reinterpret_cast<const uint4*>(wb + ch * 32)) : zero;
-    const uint32_t a1[4] = {ua.x, ub.x, ua.y, ub.y};
-    const uint32_t a2[4] = {ua.z, ub.z, ua.w, ub.w};
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const int m = t * 8 + r;
-      uint4 ux = zero;
-      if (in && m < p.M) {
-        if (PRO == kProNorm)
-          ux = *reinterpret_cast<const uint4*>(xs + (size_t)m * xs_stride + (size_t)k * 2);
-        else
-          ux = __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.ldx + k));
-      }
-      mma_16816(acc[t], a1, ux.x, ux.y);
-      mma_16816(acc[t], a2, ux.z, ux.w);
-    }
-  }
-#pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    red[warp][r][t * 8 + 2 * c] = acc[t][0];
-    red[warp][r][t * 8 + 2 * c + 1] = acc[t][1];
-    red[warp][r + 8][t * 8 + 2 * c] = acc[t][2];
-    red[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
-  }
-  __syncthreads();
-
+template <int NT, int EPI>
+__device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
+                                            float (*red)[kFuRows][8 * NT + 1]) {
   if (EPI == kEpiPlain) {
     for (int i = threadIdx.x; i < kFuRows * p.M; i += kFuWarps * 32) {
       const int m = i / kFuRows, rr = i - m * kFuRows;
@@ -239,6 +171,169 @@ skinny_fused_kernel(const FusedParams p) {
   }
 }
 
+constexpr int kFuPre = 3;      // weight chunks per warp fetched ahead (covers K <= 768)
+
+template <int EPI>
+__device__ __forceinline__ void fetch_weights(const FusedParams& p, int tile, int warp, int r, int c,
+                                              int n_chunks, uint4 (&pa)[kFuPre], uint4 (&pb)[kFuPre]) {
+  const int row_a = tile_row<EPI>(p, tile, r), row_b = tile_row<EPI>(p, tile, r + 8);
+  const __nv_bfloat16* wa = p.W + (size_t)max(row_a, 0) * p.ldw + c * 8;
+  const __nv_bfloat16* wb = p.W + (size_t)max(row_b, 0) * p.ldw + c * 8;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int i = 0; i < kFuPre; ++i) {
+    const int ch = warp + kFuWarps * i;
+    const bool in = ch < n_chunks && ch * 32 + c * 8 < p.K;
+    pa[i] = in ? __ldg(reinterpret_cast<const uint4*>(wa + ch * 32)) : zero;
+    pb[i] = in ? __ldg(reinterpret_cast<const uint4*>(wb + ch * 32)) : zero;
+  }
+}
+
+template <int NT, int PRO, int EPI>
+__global__ void __launch_bounds__(kFuWarps * 32)
+skinny_fused_kernel(const FusedParams p, int n_tiles) {
+  extern __shared__ __align__(16) unsigned char fsmem[];
+  float(*red)[kFuRows][8 * NT + 1] = reinterpret_cast<float(*)[kFuRows][8 * NT + 1]>(fsmem);
+  // x tile (norm prologue) after the reduction buffer; row stride ≡ 64 (mod 128) bytes so
+  // that a quarter-warp's eight 16-byte reads touch all banks once
+  const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;
+  unsigned char* xs = fsmem + sizeof(float) * kFuWarps * kFuRows * (8 * NT + 1);
+  xs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(xs) + 15) & ~uintptr_t(15));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, c = lane & 3;
+  const int n_chunks = (p.K + 31) >> 5;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  // The first tile's weights do not depend on anything computed before this kernel: ask for
+  // them first, so that their latency runs under the prologue.
+  int tile = blockIdx.x;
+  uint4 pa[kFuPre], pb[kFuPre];
+  fetch_weights<EPI>(p, tile, warp, r, c, n_chunks, pa, pb);
+  // Programmatic dependent launch: the kernel behind this one may start its own weight
+  // fetch now, and this one goes on to read activations only when the kernel before it has
+  // finished (a no-op when the launch was an ordinary one).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (PRO == kProNorm) {
+    const int n4 = p.K >> 2;
+    for (int m = warp; m < p.M; m += kFuWarps) {
+      const float4* h4 = reinterpret_cast<const float4*>(p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K);
+      const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+      __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
+      if (n4 <= 256) {                       // the row fits in registers: one trip to memory
+        float4 v[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = u * 32 + lane;
+          v[u] = i < n4 ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = u * 32 + lane;
+          if (i < n4) {
+            const float4 w = w4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * w.x * inv, v[u].y * w.y * inv);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * w.z * inv, v[u].w * w.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+          }
+        }
+      } else {
+        float ss = 0.f;
+        for (int i = lane; i < n4; i += 32) {
+          const float4 v = h4[i];
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)p.K + p.eps);
+        for (int i = lane; i < n4; i += 32) {
+          const float4 v = h4[i], w = w4[i];
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * w.x * inv, v.y * w.y * inv);
+          __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * w.z * inv, v.w * w.w * inv);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  for (; tile < n_tiles; tile += gridDim.x) {
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+
+    auto consume = [&](const uint4& ua, const uint4& ub, int ch) {
+      const int k = ch * 32 + c * 8;
+      const bool in = ch < n_chunks && k < p.K;
+      const uint32_t a1[4] = {ua.x, ub.x, ua.y, ub.y};
+      const uint32_t a2[4] = {ua.z, ub.z, ua.w, ub.w};
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int m = t * 8 + r;
+        uint4 ux = zero;
+        if (in && m < p.M) {
+          if (PRO == kProNorm)
+            ux = *reinterpret_cast<const uint4*>(xs + (size_t)m * xs_stride + (size_t)k * 2);
+          else
+            ux = __ldg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.ldx + k));
+        }
+        mma_16816(acc[t], a1, ux.x, ux.y);
+        mma_16816(acc[t], a2, ux.z, ux.w);
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < kFuPre; ++i) consume(pa[i], pb[i], warp + kFuWarps * i);
+    if (n_chunks > kFuWarps * kFuPre) {
+      const int row_a = tile_row<EPI>(p, tile, r), row_b = tile_row<EPI>(p, tile, r + 8);
+      const __nv_bfloat16* wa = p.W + (size_t)max(row_a, 0) * p.ldw + c * 8;
+      const __nv_bfloat16* wb = p.W + (size_t)max(row_b, 0) * p.ldw + c * 8;
+      for (int ch = warp + kFuWarps * kFuPre; ch < n_chunks; ch += 2 * kFuWarps) {
+        const int ch2 = ch + kFuWarps;
+        const bool in1 = ch * 32 + c * 8 < p.K, in2 = ch2 < n_chunks && ch2 * 32 + c * 8 < p.K;
+        const uint4 ua1 = in1 ? __ldg(reinterpret_cast<const uint4*>(wa + ch * 32)) : zero;
+        const uint4 ub1 = in1 ? __ldg(reinterpret_cast<const uint4*>(wb + ch * 32)) : zero;
+        const uint4 ua2 = in2 ? __ldg(reinterpret_cast<const uint4*>(wa + ch2 * 32)) : zero;
+        const uint4 ub2 = in2 ? __ldg(reinterpret_cast<const uint4*>(wb + ch2 * 32)) : zero;
+        consume(ua1, ub1, ch);
+        consume(ua2, ub2, ch2);
+      }
+    }
+    // the next tile's weights travel while this tile is reduced and finished
+    if (tile + (int)gridDim.x < n_tiles)
+      fetch_weights<EPI>(p, tile + gridDim.x, warp, r, c, n_chunks, pa, pb);
+
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      red[warp][r][t * 8 + 2 * c] = acc[t][0];
+      red[warp][r][t * 8 + 2 * c + 1] = acc[t][1];
+      red[warp][r + 8][t * 8 + 2 * c] = acc[t][2];
+      red[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
+    }
+    __syncthreads();
+    finish_tile<NT, EPI>(p, tile, red);
+    __syncthreads();
+  }
+}
+
+// Launch the fused kernels with programmatic stream serialization (their weight fetch then
+// overlaps the tail of the kernel before them).
+static int g_dependent_launch = 1;
+
 static size_t fused_smem(int nt, int pro, int M, int K) {
   size_t bytes = sizeof(float) * kFuWarps * kFuRows * (8 * nt + 1) + 16;
   if (pro == kProNorm) bytes += (size_t)M * (((K * 2 + 127) / 128) * 128 + 64);
@@ -256,7 +351,29 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  skinny_fused_kernel<NT, PRO, EPI><<<tiles, kFuWarps * 32, smem, st>>>(p);
+  static int max_ctas = 0;
+  if (!max_ctas) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    max_ctas = 4 * (sms > 0 ? sms : 148);
+  }
+  const int grid = tiles < max_ctas ? tiles : max_ctas;
+  if (g_dependent_launch) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kFuWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_fused_kernel<NT, PRO, EPI>, p, tiles);
+    return e == cudaSuccess ? launch_status() : (int)e;
+  }
+  skinny_fused_kernel<NT, PRO, EPI><<<grid, kFuWarps * 32, smem, st>>>(p, tiles);
   return launch_status();
 }
 
@@ -330,6 +447,12 @@ extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, fl
   p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I;
   if (!common_ok(p) || !H || I <= 0) return kBadArgument;
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
+}
+
+extern "C" int cretif_set_dependent_launch(int on) {
+  const int was = g_dependent_launch;
+  g_dependent_launch = on ? 1 : 0;
+  return was;
 }
 
 extern "C" int cretif_fused_smem_ok(int M, int K) {

@@ -340,6 +340,11 @@ def fused_supported(M: int, K: int, w) -> bool:
             and bool(lib().cretif_fused_smem_ok(M, K)))
 
 
+def set_dependent_launch(on: bool) -> bool:
+    """Programmatic dependent launch of the fused kernels on or off; returns the old setting."""
+    return bool(lib().cretif_set_dependent_launch(int(on)))
+
+
 def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool = False) -> None:
     """out (+)= bf16(rmsnorm(h[rows])) · wᵀ in one kernel (decode-sized row counts)."""
     _need(h, "h", torch.float32, 2); _need(norm_w, "norm weight", torch.float32, 1)

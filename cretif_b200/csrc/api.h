@@ -70,6 +70,15 @@ int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, const void* k
                        int bt, int B, int n_splits, float* part_o, float* part_ml, int* counters,
                        unsigned int* fault, void* stream);
 
+// The same operation on the tensor cores (mma.sync, TMA-swizzled tiles), head_dim <= 128;
+// same scratch and counters.  n_blocks is the cache's block count.
+int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const void* kc,
+                           const void* vc, long long n_blocks, const int* table, int table_stride,
+                           const int* tok_pos, const int* tok_seq, const int* seq_slot, int nh,
+                           int nkv, int hd, float scale, int window, int bt, int B, int n_splits,
+                           float* part_o, float* part_ml, int* counters, unsigned int* fault,
+                           void* stream);
+
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,

@@ -297,8 +297,8 @@ def decode_splits(B: int, nkv: int, max_context: int, device) -> int:
     """Ranges per (sequence, kv head): enough CTAs for about four per SM, at most one per
     cache block of the longest context."""
     tiles = max(1, -(-max_context // 64))
-    want = -(-4 * sm_count(device) // max(1, B * nkv))
-    return max(1, min(tiles, want))
+    want = (3 * sm_count(device)) // max(1, B * nkv)      # about three CTAs fit an SM: one wave
+    return max(1, min(tiles, want, 64))
 
 
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
@@ -314,6 +314,13 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
     counters = _decode_counters(q.device, B * nkv)
+    if hd <= 128 and not _decode_simt_only:
+        _check(lib().cretif_attn_decode_mma(
+            _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
+            ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
+            _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
+            _p(part_o), _p(part_ml), _p(counters), _p(fault), _stream()), "attn_decode_mma")
+        return
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
         table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
@@ -322,6 +329,14 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
 
 
 _COUNTERS = {}
+_decode_simt_only = False
+
+
+def decode_attention_simt_only(on: bool) -> None:
+    """Use the CUDA-core decode attention kernel even where the tensor-core one applies
+    (it is the only one for head sizes above 128; tests run both)."""
+    global _decode_simt_only
+    _decode_simt_only = bool(on)
 
 
 def _decode_counters(device, n: int) -> torch.Tensor:

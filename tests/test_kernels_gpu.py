@@ -365,7 +365,17 @@ def test_attn_simt_decode_and_prefill(ops, dtype, nh, nkv, hd, lens, window):
 @pytest.mark.parametrize("nh,nkv,hd,lens", ATTN_CASES + [(9, 3, 64, [2048, 700, 1, 4096])])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("splits", [1, 3, 16])
-def test_attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
+@pytest.mark.parametrize("simt", [False, True])
+def test_attn_decode_split(ops, nh, nkv, hd, lens, window, splits, simt):
+    """Both decode kernels (tensor-core for head sizes up to 128, CUDA-core for all)."""
+    ops.decode_attention_simt_only(simt)
+    try:
+        _attn_decode_split(ops, nh, nkv, hd, lens, window, splits)
+    finally:
+        ops.decode_attention_simt_only(False)
+
+
+def _attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
     scale = 1.0 / math.sqrt(hd)
     cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=4)
     B = len(lens)

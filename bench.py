@@ -191,6 +191,39 @@ def run_e2e(engine, batch, steps, prompt_len):
                         "the sampled ids"}
 
 
+def probe(engine, args) -> int:
+    """A small eager workload for profilers: `--probe decode` runs --steps decode steps of
+    --batch sequences without a CUDA graph after a 2,048-token prefill; `--probe prefill`
+    runs --steps prefills of one 2,048-token prompt."""
+    import numpy as np
+    import torch
+    from cretif_b200.engine.generate import EngineBackend
+    from cretif_b200.sampling import SamplingParams
+    if args.probe == "prefill":
+        ms = run_prefill(engine, PROMPT_LEN, repeats=max(1, args.steps), warmup=1)
+        print(f"prefill of {PROMPT_LEN} tokens: {ms:.3f} ms")
+        return 0
+    rng = np.random.default_rng(0)
+    B = args.batch
+    prompts = [rng.integers(0, engine.vocab_size, size=PROMPT_LEN).tolist() for _ in range(B)]
+    be = EngineBackend(engine, SamplingParams(), use_graph=False)
+    be.start_batch(list(range(B)), prompts, [PROMPT_LEN + args.steps + 8] * B)
+    try:
+        be.prefill()
+        active = list(range(B))
+        be.decode(active)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            be.decode(active)
+        torch.cuda.synchronize()
+        print(f"eager decode, batch {B}: {(time.perf_counter() - t0) * 1e3 / args.steps:.3f} "
+              "ms/step (launch-bound without the graph)")
+    finally:
+        be.end_batch()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -201,6 +234,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
+                    help="run a few eager steps of one phase and print their time (for "
+                         "profilers); no JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -239,6 +275,9 @@ def main() -> int:
                         max_len=CONTEXT)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
+
+    if args.probe:
+        return probe(engine, args)
 
     with ClockSampler() as clocks:
         ms, mean_ctx, per_step = run_decode(engine, args.batch, steps, args.warmup, PROMPT_LEN)

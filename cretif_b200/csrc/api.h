@@ -92,7 +92,7 @@ int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const 
                           void* stream);
 int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
                               int ldw, void* act, int I, int M, int K, void* stream);
-int cretif_fused_smem_ok(int M, int K);
+int cretif_fused_smem_ok(int M, int K, int norm_prologue);
 // Programmatic dependent launch of the fused kernels on (default) or off; returns the old value.
 int cretif_set_dependent_launch(int on);
 

@@ -190,7 +190,7 @@ __device__ __forceinline__ void fetch_weights(const FusedParams& p, int tile, in
 }
 
 template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(kFuWarps * 32)
+__global__ void __launch_bounds__(kFuWarps * 32, NT <= 2 ? 3 : 2)
 skinny_fused_kernel(const FusedParams p, int n_tiles) {
   extern __shared__ __align__(16) unsigned char fsmem[];
   float(*red)[kFuRows][8 * NT + 1] = reinterpret_cast<float(*)[kFuRows][8 * NT + 1]>(fsmem);
@@ -455,7 +455,7 @@ extern "C" int cretif_set_dependent_launch(int on) {
   return was;
 }
 
-extern "C" int cretif_fused_smem_ok(int M, int K) {
+extern "C" int cretif_fused_smem_ok(int M, int K, int norm_prologue) {
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
-  return fused_smem(nt, kProNorm, M, K) <= 200 * 1024 ? 1 : 0;
+  return fused_smem(nt, norm_prologue ? kProNorm : kProPlain, M, K) <= 200 * 1024 ? 1 : 0;
 }

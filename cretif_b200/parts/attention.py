@@ -102,7 +102,7 @@ class Attention(Part):
                 or ctx.T > FUSED_MAX_TOKENS or type(norm) is not RMSNorm
                 or type(self.position) is not Rotary or self.position.rot_dim != self.hd
                 or cache.kv is None or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
-                or not ops.fused_supported(ctx.T, self.q_dim, self.w_o)):
+                or not ops.fused_supported(ctx.T, self.q_dim, self.w_o, norm=False)):
             return False
         kv = cache.kv
         cos, sin = self.position._table

@@ -51,7 +51,7 @@ class GatedMLP(Part):
         if (not fused_steps_enabled() or self.dtype != torch.bfloat16 or T > FUSED_MAX_TOKENS
                 or type(norm) is not RMSNorm
                 or not ops.fused_supported(T, self.hidden_size, self.w_gate_up)
-                or not ops.fused_supported(T, self.inter, self.w_down)):
+                or not ops.fused_supported(T, self.inter, self.w_down, norm=False)):
             return False
         act = torch.empty((T, self.inter), dtype=self.dtype, device=h.device)
         ops.fused_gate_up_silu(h, norm.weight, norm.eps, self.w_gate_up, act)

@@ -1,17 +1,18 @@
 // Causal grouped-query attention for whole prompts on the tcgen05 tensor cores, bfloat16.
 //
 // One CTA owns 128 consecutive query tokens of one sequence and one query head.  It walks
-// the sequence's cache blocks (64 keys each) up to the diagonal:
+// the sequence's cache blocks up to the diagonal, two 64-key blocks (128 keys) per step:
 //   warp 0     TMA producer: the Q tile once, then K and V tiles of each block straight out
 //              of the block cache (a block's [64 x head_dim] tile of a key/value head is one
 //              2-d box) into a ring of shared-memory stages;
 //   warp 1     one thread issues S = Q K^T (tcgen05.mma, accumulator in tensor memory), and
 //              after the softmax threads have written P, O_blk = P V (V is the MN-major
 //              operand, exactly as it lies in the cache);
-//   warps 2-5  softmax: each thread owns one query row, reads its row of S from tensor
-//              memory, keeps the running maximum and sum in 32-bit, writes P as bfloat16 into
-//              shared memory in the swizzled operand layout, then folds O_blk into its row
-//              of the output, which stays in registers.
+//   warps 2-9  softmax: two threads share one query row (64 of the step's keys and half of the
+//              output columns each); they read S from tensor memory, keep the running
+//              maximum and sum in 32-bit, write P as bfloat16 into shared memory in the
+//              swizzled operand layout, then fold O_blk into their part of the output row,
+//              which stays in registers.
 // The reference materialises [heads, S, kv_len] scores and transposes the cache for every
 // call (src/attention.cu:644-728); nothing of that exists here.
 //
@@ -27,26 +28,33 @@ namespace cretif {
 int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
                        int box_rows);
 
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 320;   // producer, MMA issuer, eight softmax warps
 constexpr int kPfBQ = 128;       // queries per CTA
-constexpr int kPfBK = 64;        // keys per step = tokens per cache block
-constexpr int kPfStages = 3;
+constexpr int kPfBlk = 64;       // tokens per cache block
+constexpr int kPfBK = 128;       // keys per step: two cache blocks
+constexpr int kPfStages = 2;
 
 struct PfSmem {
   // byte offsets for a head size with n_sub 64-wide column groups
-  int q, p, k, v, bars, total;
+  int q, p, k, v, bars, xch, total;
   __host__ __device__ explicit PfSmem(int n_sub) {
     q = 0;
     p = q + n_sub * kPfBQ * 128;
-    k = p + kPfBQ * 128;
+    k = p + (kPfBK / 64) * kPfBQ * 128;
     v = k + kPfStages * n_sub * kPfBK * 128;
     bars = v + kPfStages * n_sub * kPfBK * 128;
-    total = bars + (2 * kPfStages + 4) * 8 + 16 + 1024;
+    xch = bars + (2 * kPfStages + 4) * 8 + 16;
+    total = xch + 4 * kPfBQ * 4 + 1024;
   }
 };
 
 // MN-major operand tile (V): rows of 128 bytes are one key each, 8 keys form a 1024-byte
 // swizzle atom; 64-wide column groups of the head are `lbo_bytes` apart.
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t lbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((tc::smem_u32(tile) & 0x3FFFFu) >> 4);
@@ -58,7 +66,7 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_
 }
 
 template <int HDMAX>
-__global__ void __launch_bounds__(kPfThreads)
+__global__ void __launch_bounds__(kPfThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -94,16 +102,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int rows_here = min(kPfBQ, n_new - q0);
   const int pos_first = start + q0, pos_last = start + q0 + rows_here - 1;
   const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
-  const int tile_lo = key_lo / kPfBK, tile_hi = pos_last / kPfBK;      // inclusive
-  const int n_tiles = tile_hi - tile_lo + 1;
+  const int blk_lo = key_lo / kPfBlk, blk_hi = pos_last / kPfBlk;      // cache blocks, inclusive
+  const int n_tiles = (blk_hi - blk_lo + 2) / 2;                        // steps of two blocks
   constexpr uint32_t kTmemCols = 256;
-  constexpr uint32_t kColS = 0, kColO = 64;
+  constexpr uint32_t kColS = 0, kColO = 128;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPfStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
     tc::mbar_init(q_full, 1);
     tc::mbar_init(s_full, 1);
-    tc::mbar_init(p_full, 128);
+    tc::mbar_init(p_full, 256);
     tc::mbar_init(o_full, 1);
     *abort = 0;
     tc::fence_barrier_init();
@@ -131,15 +139,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (j >= kPfStages &&
             !tc::mbar_wait(&kv_empty[s], (uint32_t)((j / kPfStages - 1) & 1), abort))
           break;
-        const int blk = tab[tile_lo + j];
-        if (blk < 0) atomicOr(fault, kFaultBlockTable);
-        const int row = (max(blk, 0) * nkv + kvh) * kPfBK;
         tc::mbar_expect_tx(&kv_full[s], (uint32_t)(2 * n_sub * kPfBK * 128));
-        for (int sub = 0; sub < n_sub; ++sub) {
-          tc::tma_load_2d(smem + L.k + (s * n_sub + sub) * kPfBK * 128, &map_k, 64 * sub, row,
-                          &kv_full[s]);
-          tc::tma_load_2d(smem + L.v + (s * n_sub + sub) * kPfBK * 128, &map_v, 64 * sub, row,
-                          &kv_full[s]);
+        for (int half = 0; half < 2; ++half) {
+          // a step past the last block loads that block again: its keys are masked, and the
+          // operand tile holds finite numbers instead of whatever was in shared memory
+          const int blk = tab[min(blk_lo + 2 * j + half, blk_hi)];
+          if (blk < 0) atomicOr(fault, kFaultBlockTable);
+          const int row = (max(blk, 0) * nkv + kvh) * kPfBlk;
+          for (int sub = 0; sub < n_sub; ++sub) {
+            const int off = (s * n_sub + sub) * kPfBK * 128 + half * kPfBlk * 128;
+            tc::tma_load_2d(smem + L.k + off, &map_k, 64 * sub, row, &kv_full[s]);
+            tc::tma_load_2d(smem + L.v + off, &map_v, 64 * sub, row, &kv_full[s]);
+          }
         }
       }
     }
@@ -165,60 +176,72 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = tc::mbar_wait(p_full, (uint32_t)(j & 1), abort);
         if (!ok) break;
         tc::tc_fence_after();
-        const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p);
         const uint64_t vd = smem_desc_mn_sw128(smem + L.v + s * n_sub * kPfBK * 128,
                                                (uint32_t)(kPfBK * 128));
 #pragma unroll
-        for (int kk = 0; kk < kPfBK / 16; ++kk)      // 16 keys = two 1024-byte atoms of V
-          tc::umma_bf16(tmem + kColO, pd + 2 * kk, vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
+        for (int kk = 0; kk < kPfBK / 16; ++kk) {    // 16 keys = two 1024-byte atoms of V
+          const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p + (kk >> 2) * kPfBQ * 128) +
+                              2 * (kk & 3);
+          tc::umma_bf16(tmem + kColO, pd, vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
+        }
         tc::umma_commit(&kv_empty[s]);
         tc::umma_commit(o_full);
       }
     }
   } else {
-    const int quad = warp & 3;
+    // Eight softmax warps: warps w and w + 4 share the 32 rows of TMEM lane quadrant w % 4;
+    // of a row's 128 keys per step, the first of the pair takes keys 0..63 and the second
+    // 64..127, and of the output's columns each keeps one half.  They meet once per step
+    // (a named barrier of 64 threads) to agree on the row's maximum.
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const int q_pos = start + q0 + row;
     const bool row_valid = row < rows_here;
     const int lo_key = window > 0 ? max(0, q_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    float o[HDMAX];
+    const int ocols = hd >> 1, obase = half * ocols;     // this thread's output columns
+    float o[HDMAX / 2];
 #pragma unroll
-    for (int d = 0; d < HDMAX; ++d) o[d] = 0.f;
+    for (int d = 0; d < HDMAX / 2; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    unsigned char* prow = smem + L.p + row * 128;
+    unsigned char* prow = smem + L.p + half * kPfBQ * 128 + row * 128;
+    float* xch = reinterpret_cast<float*>(smem + L.xch);              // [2 buffers][2][128]
+    // A wait that gives up does not leave the loop: the pair's barriers must stay matched.
+    // Later waits return at once (the abort flag is up) and the result is flagged, not used.
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = tc::mbar_wait(s_full, (uint32_t)(j & 1), abort);
-      if (!ok) break;
+      ok = tc::mbar_wait(s_full, (uint32_t)(j & 1), abort) && ok;
       tc::tc_fence_after();
       uint32_t sa[32], sb[32];
-      tc::tmem_load_32(lane_addr + kColS, sa);
-      tc::tmem_load_32(lane_addr + kColS + 32, sb);
+      tc::tmem_load_32(lane_addr + kColS + half * 64, sa);
+      tc::tmem_load_32(lane_addr + kColS + half * 64 + 32, sb);
       tc::tmem_load_wait();
-      const int key0 = (tile_lo + j) * kPfBK;
+      const int key0 = (blk_lo + 2 * j) * kPfBlk + half * 64;
       float t[64];
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
         const int key = key0 + c;
-        const float s = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]) * scale_log2;
-        t[c] = (key <= q_pos && key >= lo_key) ? s : -INFINITY;
-        mx = fmaxf(mx, t[c]);
+        const float sv = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]) * scale_log2;
+        t[c] = (key <= q_pos && key >= lo_key) ? sv : -INFINITY;
+        mx4[c & 3] = fmaxf(mx4[c & 3], t[c]);
       }
-      const float m_new = fmaxf(m, mx);
+      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* xb = xch + (j & 1) * 256;        // double-buffered: one barrier per step
+      xb[half * 128 + row] = mine;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      const float m_new = fmaxf(m, fmaxf(mine, xb[(half ^ 1) * 128 + row]));
       const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float p0 = (t[c] == -INFINITY) ? 0.f : exp2f(t[c] - m_new);
         const float p1 = (t[c + 1] == -INFINITY) ? 0.f : exp2f(t[c + 1] - m_new);
-        sum += p0 + p1;
-        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+        sum4[(c >> 1) & 3] += p0 + p1;
+        packed[c >> 1] = pack2(p0, p1);
       }
-      l = l * alpha + sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m = m_new;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {        // 16-byte chunks, swizzled by the row
@@ -228,27 +251,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       tc::fence_proxy_async();                // generic-proxy writes → visible to the MMA
       tc::mbar_arrive(p_full);
-      ok = tc::mbar_wait(o_full, (uint32_t)(j & 1), abort);
-      if (!ok) break;
+      ok = tc::mbar_wait(o_full, (uint32_t)(j & 1), abort) && ok;
       tc::tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < HDMAX; c0 += 32) {
-        if (c0 < hd) {
+      for (int c0 = 0; c0 < HDMAX / 2; c0 += 32) {
+        if (c0 < ocols) {
           uint32_t r[32];
-          tc::tmem_load_32(lane_addr + kColO + c0, r);
+          tc::tmem_load_32(lane_addr + kColO + obase + c0, r);
           tc::tmem_load_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[c0 + e] = fmaf(o[c0 + e], alpha, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < HDMAX / 2) o[c0 + e] = fmaf(o[c0 + e], alpha, __uint_as_float(r[e]));
         }
       }
       tc::tc_fence_before();
     }
+    // the row's sum is the two halves' sums (the buffer of step n_tiles was last read two
+    // steps ago)
+    float* xb = xch + (n_tiles & 1) * 256;
+    xb[half * 128 + row] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+    l += xb[(half ^ 1) * 128 + row];
     if (ok && row_valid) {
       const float inv = 1.0f / l;
-      __nv_bfloat16* orow = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hd;
+      __nv_bfloat16* orow = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hd + obase;
 #pragma unroll
-      for (int d = 0; d < HDMAX; d += 8) {
-        if (d < hd) {
+      for (int d = 0; d < HDMAX / 2; d += 8) {
+        if (d < ocols) {
           float v[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[e] = o[d + e] * inv;
@@ -277,16 +306,16 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
                                       int hd, float scale, int window, int bt, int B, int max_new,
                                       unsigned int* fault, void* stream) {
   if (B <= 0 || T <= 0) return kOk;
-  if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBK ||
+  if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
       window < 0 || max_new <= 0 || nh > 65535 || B > 65535 || ldq % 8 || ldo % 8)
     return kBadArgument;
   if (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) & 15) return kMisaligned;
-  const long long cache_rows = n_blocks * nkv * kPfBK;
+  const long long cache_rows = n_blocks * nkv * kPfBlk;
   if (cache_rows > 0x7fffffffLL) return kBadArgument;
   CUtensorMap map_q, map_k, map_v;
   if (make_tile_map_bf16(&map_q, qkv, T, ldq, ldq, kPfBQ)) return kBadArgument;
-  if (make_tile_map_bf16(&map_k, kc, (int)cache_rows, hd, hd, kPfBK)) return kBadArgument;
-  if (make_tile_map_bf16(&map_v, vc, (int)cache_rows, hd, hd, kPfBK)) return kBadArgument;
+  if (make_tile_map_bf16(&map_k, kc, (int)cache_rows, hd, hd, kPfBlk)) return kBadArgument;
+  if (make_tile_map_bf16(&map_v, vc, (int)cache_rows, hd, hd, kPfBlk)) return kBadArgument;
   const int n_sub = (hd + 63) / 64;
   const PfSmem L(n_sub);
   cudaStream_t st = (cudaStream_t)stream;

@@ -16,6 +16,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "api.h"
 #include "tc_common.cuh"
 
@@ -169,8 +171,35 @@ static EncodeTiledFn encode_fn() {
 }
 
 // A [rows, cols] bf16 matrix with row stride ld (elements), tiles of box_rows x 64.
+// Encoding a map costs a few microseconds on the host, and weights, the cache and recycled
+// activation buffers come back with the same address and shape, so recent maps are kept.
+struct MapKey {
+  const void* base;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows;
+  }
+};
+constexpr int kMapCacheSize = 1024;
+static MapKey g_map_keys[kMapCacheSize];
+static CUtensorMap g_map_vals[kMapCacheSize];
+static bool g_map_used[kMapCacheSize];
+static std::mutex g_map_mutex;
+
 int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
                        int box_rows) {
+  const MapKey key = {base, rows, cols, ld, box_rows};
+  size_t hsh = (size_t)((uintptr_t)base >> 4) * 1000003u ^ (size_t)rows * 8191u ^
+               (size_t)cols * 131u ^ (size_t)ld * 31u ^ (size_t)box_rows;
+  const int at = (int)(hsh % kMapCacheSize);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_map_used[at] && g_map_keys[at] == key) {
+      *map = g_map_vals[at];
+      return 0;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return kBadArgument;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -180,7 +209,12 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
                   strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : kBadArgument;
+  if (r != CUDA_SUCCESS) return kBadArgument;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  g_map_keys[at] = key;
+  g_map_vals[at] = *map;
+  g_map_used[at] = true;
+  return 0;
 }
 
 template <int BN, typename TC>

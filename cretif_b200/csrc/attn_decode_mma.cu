@@ -14,7 +14,10 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "api.h"
+#include "attn_decode_noalloc.h"
 #include "tc_common.cuh"
 
 namespace cretif {
@@ -359,4 +362,63 @@ extern "C" int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo
   }
 #undef CRETIF_DM
   return kBadArgument;
+}
+
+// ---------------------------------------------------------------- no-allocation entry point
+// The scratch of the split-range kernel in a fixed array of the library (see
+// attn_decode_noalloc.h).  In host code the array's name is only a stand-in for the symbol,
+// not a device address: the address is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CRETIF_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+constexpr size_t kNoallocCounterBytes = (size_t)CRETIF_NOALLOC_MAX_COUNTERS * sizeof(int);
+unsigned char* g_noalloc_ptr[kNoallocMaxDevices];     // device address of the array, per device
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" unsigned int cretif_attn_decode_noalloc_capacity(void) {
+  return CRETIF_NOALLOC_SCRATCH_BYTES;
+}
+
+extern "C" int cretif_attn_decode_noalloc(const void* q, int ldq, void* out, int ldo,
+                                          const void* kc, const void* vc, long long n_blocks,
+                                          const int* table, int table_stride, const int* tok_pos,
+                                          const int* tok_seq, const int* seq_slot, int nh, int nkv,
+                                          int hd, float scale, int window, int bt, int B,
+                                          int n_splits, unsigned int* fault, void* stream) {
+  if (B <= 0) return kOk;
+  if (nh <= 0 || nkv <= 0 || hd <= 0 || n_splits <= 0) return kBadArgument;
+  // sizes beyond the fixed array are refused before anything is launched
+  const unsigned long long n_counters = (unsigned long long)B * nkv;
+  const unsigned long long floats_o = (unsigned long long)B * nh * n_splits * hd;
+  const unsigned long long floats_ml = (unsigned long long)B * nh * n_splits * 2;
+  if (n_counters > CRETIF_NOALLOC_MAX_COUNTERS) return kBadArgument;
+  if ((floats_o + floats_ml) * sizeof(float) > CRETIF_NOALLOC_SCRATCH_BYTES - kNoallocCounterBytes)
+    return kBadArgument;
+
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return kBadArgument;
+  unsigned char* base;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {                 // set-up, once per device, that device current
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  int* counters = reinterpret_cast<int*>(base);
+  float* part_o = reinterpret_cast<float*>(base + kNoallocCounterBytes);
+  float* part_ml = part_o + floats_o;
+  // the counters must start at zero whatever an earlier (perhaps faulted) call left there
+  e = cudaMemsetAsync(counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return cretif_attn_decode_mma(q, ldq, out, ldo, kc, vc, n_blocks, table, table_stride, tok_pos,
+                                tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, B, n_splits,
+                                part_o, part_ml, counters, fault, stream);
 }

@@ -21,8 +21,9 @@ int cretif_add_rmsnorm(float* h, const void* delta, int delta_dt, const float* w
                        int out_dt, const int* rows, int R, int H, float eps, int write_h,
                        void* stream);
 
-// act[t, i] = silu(gu[t, i]) * gu[t, I + i]
-int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, void* stream);
+// act[t, i] = silu(gate) * up; block = 0: gu row = [gate | up]; block = b: groups of b gate
+// columns followed by their b up columns.
+int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, int block, void* stream);
 
 // Rotate q and k of every token by its position's angles (pairing 0: (j, j+rot/2),
 // 1: (2j, 2j+1)); q in place, rotated k and v into the block cache.
@@ -51,6 +52,18 @@ int cretif_gemm_skinny_max_rows(void);
 // 0 lets the launcher choose.  A wait that expires sets bit 2 of *fault.
 int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda,
                    int ldw, int ldc, int accumulate, int bn, unsigned int* fault, void* stream);
+
+// The same product with fused epilogues (see gemm_tc.cu): SiLU·mul for the stacked gate|up
+// matrix whose rows are interleaved in blocks of 64 (I % 64 == 0), and rotary + cache write for
+// the stacked q|k|v matrix (head_dim 64 or 128, rotary over the whole head).
+int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, int M, int I, int K, int lda,
+                        int ldw, unsigned int* fault, void* stream);
+int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq, const float* cos_t,
+                            const float* sin_t, int pairing, int nh, int nkv, int hd,
+                            const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                            const int* table, int table_stride, void* kc, void* vc, int bt,
+                            int write_cache, int M, int K, int lda, int ldw, unsigned int* fault,
+                            void* stream);
 
 // Causal grouped-query attention over the block cache, any step shape.
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
@@ -91,7 +104,7 @@ int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const 
                           void* vc, int bt, int write_cache, int M, int K, unsigned int* fault,
                           void* stream);
 int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
-                              int ldw, void* act, int I, int M, int K, void* stream);
+                              int ldw, void* act, int I, int gu_block, int M, int K, void* stream);
 int cretif_fused_smem_ok(int M, int K, int norm_prologue);
 // Programmatic dependent launch of the fused kernels on (default) or off; returns the old value.
 int cretif_set_dependent_launch(int on);

@@ -61,7 +61,7 @@ struct FusedParams {
   unsigned int* fault;
   // epilogue silu
   __nv_bfloat16* act;       // [M, I]
-  int I;
+  int I, gu_block;          // gu_block > 0: gate/up rows interleaved in groups of that size
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -82,6 +82,10 @@ __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
   } else if (EPI == kEpiSilu) {
     const int i = tile * 8 + (r & 7);
     if (i >= p.I) return -1;
+    if (p.gu_block) {
+      const int g = (i / p.gu_block) * 2 * p.gu_block + i % p.gu_block;
+      return r < 8 ? g : g + p.gu_block;
+    }
     return r < 8 ? i : p.I + i;
   } else {
     const int tiles_per_head = p.hd >> 4;
@@ -439,13 +443,14 @@ extern "C" int cretif_fused_qkv_rope(const float* H, const float* norm_w, float 
 
 // act = silu(norm(h) · Wg^T) * (norm(h) · Wu^T), Wgu = [Wg; Wu] stacked.
 extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps,
-                                         const void* Wgu, int ldw, void* act, int I, int M, int K,
-                                         void* stream) {
+                                         const void* Wgu, int ldw, void* act, int I, int gu_block,
+                                         int M, int K, void* stream) {
   if (M <= 0) return kOk;
   FusedParams p = {};
   p.W = (const __nv_bfloat16*)Wgu; p.M = M; p.N = 2 * I; p.K = K; p.ldw = ldw;
-  p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I;
-  if (!common_ok(p) || !H || I <= 0) return kBadArgument;
+  p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I; p.gu_block = gu_block;
+  if (!common_ok(p) || !H || I <= 0 || gu_block < 0 || (gu_block && (I % gu_block || gu_block % 8)))
+    return kBadArgument;
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
 }
 

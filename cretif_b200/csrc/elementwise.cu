@@ -56,16 +56,98 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   }
 }
 
+// The same with 16-byte accesses: H % 4 == 0 and 16-byte aligned rows.  A thread keeps up to
+// four float4 of its row in registers, so a row makes one trip through memory.
+__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                     __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4f(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ weight, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps,
+                                       int write_h) {
+  __shared__ float scratch[33];
+  constexpr int kKeep = 4;
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* hrow = h + (size_t)src * H;
+  const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+  const int n4 = H >> 2;
+  float4 keep[kKeep];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kKeep; ++it) {
+    const int i = it * blockDim.x + threadIdx.x;
+    if (i < n4) {
+      float4 v = load4f(hrow + 4 * i);
+      if (drow) {
+        const float4 d = load4f(drow + 4 * i);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      }
+      if (write_h) store4f(hrow + 4 * i, v);
+      keep[it] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
+  for (int i = kKeep * blockDim.x + threadIdx.x; i < n4; i += blockDim.x) {   // very wide rows
+    float4 v = load4f(hrow + 4 * i);
+    if (drow) {
+      const float4 d = load4f(drow + 4 * i);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    if (write_h) store4f(hrow + 4 * i, v);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  TO* orow = out + (size_t)r * H;
+#pragma unroll
+  for (int it = 0; it < kKeep; ++it) {
+    const int i = it * blockDim.x + threadIdx.x;
+    if (i < n4) {
+      const float4 w = load4f(weight + 4 * i), v = keep[it];
+      store4f(orow + 4 * i, make_float4(v.x * w.x * inv, v.y * w.y * inv, v.z * w.z * inv,
+                                        v.w * w.w * inv));
+    }
+  }
+  for (int i = kKeep * blockDim.x + threadIdx.x; i < n4; i += blockDim.x) {
+    float4 v = load4f(hrow + 4 * i);
+    if (drow && !write_h) {
+      const float4 d = load4f(drow + 4 * i);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    const float4 w = load4f(weight + 4 * i);
+    store4f(orow + 4 * i, make_float4(v.x * w.x * inv, v.y * w.y * inv, v.z * w.z * inv,
+                                      v.w * w.w * inv));
+  }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
+// `block` = 0: gu row = [gate (I) | up (I)]; block = b > 0: gate and up alternate in groups of b
+// columns (b gate columns, then the b up columns that belong to them).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int I,
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int I, int block,
                                 size_t total) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / I;
   const int i = (int)(idx - t * I);
-  const float g = to_float(gu[t * 2 * (size_t)I + i]);
-  const float u = to_float(gu[t * 2 * (size_t)I + I + i]);
+  const int gcol = block ? (i / block) * 2 * block + i % block : i;
+  const int ucol = block ? gcol + block : I + i;
+  const float g = to_float(gu[t * 2 * (size_t)I + gcol]);
+  const float u = to_float(gu[t * 2 * (size_t)I + ucol]);
   act[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
@@ -168,6 +250,21 @@ template <typename TD>
 static int add_rmsnorm_out(float* h, const TD* delta, const float* w, void* out, int out_dt,
                            const int* rows, int R, int H, float eps, int write_h,
                            cudaStream_t st) {
+  const bool aligned = H % 4 == 0 && (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)w |
+                                       (uintptr_t)out) & 15) == 0;
+  if (aligned) {
+    const int n4 = H / 4;
+    const int vthreads = n4 >= 512 ? 256 : (n4 >= 128 ? 128 : (n4 >= 64 ? 64 : 32));
+    if (out_dt == kF32)
+      add_rmsnorm_vec_kernel<TD, float><<<R, vthreads, 0, st>>>(h, delta, w, (float*)out, rows, H,
+                                                               eps, write_h);
+    else if (out_dt == kBF16)
+      add_rmsnorm_vec_kernel<TD, __nv_bfloat16><<<R, vthreads, 0, st>>>(
+          h, delta, w, (__nv_bfloat16*)out, rows, H, eps, write_h);
+    else
+      return kBadDType;
+    return launch_status();
+  }
   const int threads = H >= 2048 ? 512 : (H >= 256 ? 256 : 64);
   if (out_dt == kF32)
     add_rmsnorm_kernel<TD, float><<<R, threads, 0, st>>>(h, delta, w, (float*)out, rows, H, eps,
@@ -196,17 +293,18 @@ extern "C" int cretif_add_rmsnorm(float* h, const void* delta, int delta_dt, con
   return kBadDType;
 }
 
-extern "C" int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, void* stream) {
+extern "C" int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, int block,
+                               void* stream) {
   if (T <= 0) return kOk;
-  if (I <= 0) return kBadArgument;
+  if (I <= 0 || block < 0 || (block > 0 && I % block)) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t total = (size_t)T * I;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dt == kF32)
-    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)act, I, total);
+    silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)act, I, block, total);
   else if (dt == kBF16)
     silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu,
-                                                          (__nv_bfloat16*)act, I, total);
+                                                          (__nv_bfloat16*)act, I, block, total);
   else
     return kBadDType;
   return launch_status();

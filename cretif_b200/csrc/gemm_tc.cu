@@ -35,11 +35,37 @@ struct TcSmem {
   static constexpr int kTotal = kBars + (2 * kTcStages + 1) * 8 + 16 + 1024;  // + align slack
 };
 
-template <int BN, typename TC>
+// What the epilogue warps do with the accumulator.
+//   kTcStore  store as bfloat16 / float32, or add into a float32 matrix;
+//   kTcSilu   the stacked gate|up product whose weight rows are interleaved in blocks of 64
+//             (64 gate rows, then the 64 up rows that belong to them): a 128-wide tile holds
+//             matching gate and up columns, and act = silu(gate) * up is stored (BN = 128);
+//   kTcRope   the stacked q|k|v product with one head per tile (BN = head_dim): rotary on q and
+//             k, q to the query buffer, k and v into the block cache at the token's position.
+enum TcEpilogue : int { kTcStore = 0, kTcSilu = 1, kTcRope = 2 };
+
+struct TcEpi {
+  void* C; int ldc, accumulate;                            // store
+  __nv_bfloat16* act; int I;                               // silu
+  __nv_bfloat16* Q; int ldq;                               // rope
+  const float* cos_t; const float* sin_t;
+  int pairing, nh, nkv, hd;
+  const int* tok_pos; const int* tok_seq; const int* seq_slot; const int* table;
+  int table_stride;
+  __nv_bfloat16* kc; __nv_bfloat16* vc;
+  int bt, write_cache;
+};
+
+__device__ __forceinline__ float round_bf16(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               TC* __restrict__ C, int M, int N, int K, int ldc, int accumulate,
-               unsigned int* __restrict__ fault) {
+               const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault) {
+  TC* const C = reinterpret_cast<TC*>(ep.C);
+  const int ldc = ep.ldc, accumulate = ep.accumulate;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -109,11 +135,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m = m0 + quad * 32 + lane;
     const bool ok = tc::mbar_wait(acc_full, 0u, abort);
     tc::tc_fence_after();
-    if (ok) {
+    const uint32_t lane_acc = tmem_acc + ((uint32_t)(quad * 32) << 16);
+    if (ok && EPI == kTcStore) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tc::tmem_load_32(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, r);
+        tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
         tc::tmem_load_wait();
         if (m < M && n0 + c0 < N) {
           TC* out = C + (size_t)m * ldc + n0 + c0;
@@ -137,6 +164,121 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (accumulate) x += to_float(out[j + e]);
                 out[j + e] = from_float<TC>(x);
               }
+            }
+          }
+        }
+      }
+    }
+    if (ok && EPI == kTcSilu) {
+      // tile columns [0,64) are gate, [64,128) the matching up columns of act[:, n0/2 ..]
+      const int col0 = n0 >> 1;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t g[32], u[32];
+        tc::tmem_load_32(lane_acc + (uint32_t)c0, g);
+        tc::tmem_load_32(lane_acc + (uint32_t)(64 + c0), u);
+        tc::tmem_load_wait();
+        if (m < M && col0 + c0 < ep.I) {
+          __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              // gate and up pass through bfloat16 as they do when stored separately
+              const float gg = round_bf16(__uint_as_float(g[j + e]));
+              const float uu = round_bf16(__uint_as_float(u[j + e]));
+              v[e] = gg / (1.0f + expf(-gg)) * uu;
+            }
+            if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
+          }
+        }
+      }
+    }
+    if (ok && EPI == kTcRope) {
+      const int head = n0 / ep.hd, half = ep.hd >> 1;
+      const bool valid = m < M;
+      const int pos = valid ? ep.tok_pos[m] : 0;
+      __nv_bfloat16* dst = nullptr;           // where this row's head goes
+      if (valid) {
+        if (head < ep.nh) {
+          dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
+        } else if (ep.write_cache) {
+          const int slot = ep.seq_slot[ep.tok_seq[m]];
+          const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
+          if (blk < 0) {
+            atomicOr(fault, kFaultBlockTable);
+          } else {
+            const bool is_k = head < ep.nh + ep.nkv;
+            const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
+            dst = (is_k ? ep.kc : ep.vc) +
+                  (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
+          }
+        }
+      }
+      const bool rotate = head < ep.nh + ep.nkv;
+      const float* cs = ep.cos_t + (size_t)pos * half;
+      const float* sn = ep.sin_t + (size_t)pos * half;
+      if (!rotate) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          if (dst) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+              store8(dst + c0 + j, v);
+            }
+          }
+        }
+      } else if (ep.pairing == 0) {            // pairs (j, j + head_dim/2)
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          uint32_t lo[32], hi[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, lo);
+          tc::tmem_load_32(lane_acc + (uint32_t)(BN / 2 + c0), hi);
+          tc::tmem_load_wait();
+          if (dst) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float c8[8], s8[8], y0[8], y1[8];
+              load8(cs + c0 + j, c8);
+              load8(sn + c0 + j, s8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float x0 = round_bf16(__uint_as_float(lo[j + e]));
+                const float x1 = round_bf16(__uint_as_float(hi[j + e]));
+                y0[e] = x0 * c8[e] - x1 * s8[e];
+                y1[e] = x0 * s8[e] + x1 * c8[e];
+              }
+              store8(dst + c0 + j, y0);
+              store8(dst + half + c0 + j, y1);
+            }
+          }
+        }
+      } else {                                  // pairs (2j, 2j + 1)
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          if (dst) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float y[8];
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                const int jj = (c0 + j + e) >> 1;
+                const float x0 = round_bf16(__uint_as_float(r[j + e]));
+                const float x1 = round_bf16(__uint_as_float(r[j + e + 1]));
+                y[e] = x0 * cs[jj] - x1 * sn[jj];
+                y[e + 1] = x0 * sn[jj] + x1 * cs[jj];
+              }
+              store8(dst + c0 + j, y);
             }
           }
         }
@@ -217,24 +359,29 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
   return 0;
 }
 
-template <int BN, typename TC>
-static int launch_tc(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
-                     int ldc, int accumulate, unsigned int* fault, cudaStream_t st) {
+template <int BN, int EPI, typename TC>
+static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N, int K, int lda,
+                     int ldw, unsigned int* fault, cudaStream_t st) {
   CUtensorMap map_a, map_w;
   if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
   if (make_tile_map_bf16(&map_w, W, N, K, ldw, BN)) return kBadArgument;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          TcSmem<BN>::kTotal);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
-  gemm_tc_kernel<BN, TC><<<grid, kTcThreads, TcSmem<BN>::kTotal, st>>>(
-      map_a, map_w, (TC*)C, M, N, K, ldc, accumulate, fault);
+  gemm_tc_kernel<BN, EPI, TC><<<grid, kTcThreads, TcSmem<BN>::kTotal, st>>>(map_a, map_w, ep, M, N,
+                                                                           K, fault);
   return launch_status();
+}
+
+static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, int ldw) {
+  return K > 0 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K &&
+         (M + kTcBM - 1) / kTcBM <= 65535 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
 }
 
 }  // namespace cretif
@@ -254,10 +401,12 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
     const long long mt = (M + kTcBM - 1) / kTcBM;
     bn = (mt * ((N + 255) / 256) >= 148) ? 256 : (mt * ((N + 127) / 128) >= 148 ? 128 : 64);
   }
+  TcEpi ep = {};
+  ep.C = C; ep.ldc = ldc; ep.accumulate = accumulate;
 #define CRETIF_TC(BN)                                                                         \
-  (c_dt == kBF16 ? launch_tc<BN, __nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, accumulate,  \
-                                                fault, st)                                    \
-                 : launch_tc<BN, float>(A, W, C, M, N, K, lda, ldw, ldc, accumulate, fault, st))
+  (c_dt == kBF16 ? launch_tc<BN, kTcStore, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, \
+                                                          st)                                 \
+                 : launch_tc<BN, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st))
   if (c_dt != kBF16 && c_dt != kF32) return kBadDType;
   if (c_dt == kBF16 && accumulate) return kBadArgument;
   switch (bn) {
@@ -267,4 +416,40 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
     default: return kBadArgument;
   }
 #undef CRETIF_TC
+}
+
+// act[M, I] = silu(A·Wg^T) * (A·Wu^T); Wgu holds gate and up rows interleaved in blocks of 64.
+extern "C" int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, int M, int I, int K,
+                                   int lda, int ldw, unsigned int* fault, void* stream) {
+  if (M <= 0 || I <= 0) return kOk;
+  if (!tc_operands_ok(A, Wgu, M, K, lda, ldw) || I % 64) return kBadArgument;
+  if (((uintptr_t)act) & 15) return kMisaligned;
+  TcEpi ep = {};
+  ep.act = (__nv_bfloat16*)act; ep.I = I;
+  return launch_tc<128, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
+                                                (cudaStream_t)stream);
+}
+
+// q|k|v = A·Wqkv^T with rotary on q and k; q to Q, k and v into the block cache.
+extern "C" int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq,
+                                       const float* cos_t, const float* sin_t, int pairing, int nh,
+                                       int nkv, int hd, const int* tok_pos, const int* tok_seq,
+                                       const int* seq_slot, const int* table, int table_stride,
+                                       void* kc, void* vc, int bt, int write_cache, int M, int K,
+                                       int lda, int ldw, unsigned int* fault, void* stream) {
+  if (M <= 0) return kOk;
+  if (!tc_operands_ok(A, Wqkv, M, K, lda, ldw) || nh <= 0 || nkv <= 0 || (hd != 64 && hd != 128) ||
+      bt <= 0 || ldq % 8 || ldq < nh * hd)
+    return kBadArgument;
+  if (((uintptr_t)Q | (uintptr_t)kc | (uintptr_t)vc) & 15) return kMisaligned;
+  TcEpi ep = {};
+  ep.Q = (__nv_bfloat16*)Q; ep.ldq = ldq; ep.cos_t = cos_t; ep.sin_t = sin_t; ep.pairing = pairing;
+  ep.nh = nh; ep.nkv = nkv; ep.hd = hd; ep.tok_pos = tok_pos; ep.tok_seq = tok_seq;
+  ep.seq_slot = seq_slot; ep.table = table; ep.table_stride = table_stride;
+  ep.kc = (__nv_bfloat16*)kc; ep.vc = (__nv_bfloat16*)vc; ep.bt = bt; ep.write_cache = write_cache;
+  const int N = (nh + 2 * nkv) * hd;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (hd == 64)
+    return launch_tc<64, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
+  return launch_tc<128, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
 }

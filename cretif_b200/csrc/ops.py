@@ -135,12 +135,14 @@ def add_rmsnorm(h, delta, weight, out, eps: float, rows=None, write_h: bool = Tr
                                     ctypes.c_float(eps), int(write_h), _stream()), "add_rmsnorm")
 
 
-def silu_mul(gu, act) -> None:
+def silu_mul(gu, act, block: int = 0) -> None:
+    """act = silu(gate) * up.  ``block`` = 0: gu rows are [gate | up]; ``block`` = b: groups of b
+    gate columns each followed by their b up columns."""
     _need(gu, "gu", dim=2); _need(act, "act", gu.dtype, 2)
     T, I = act.shape
     if tuple(gu.shape) != (T, 2 * I) or not gu.is_contiguous() or not act.is_contiguous():
         raise KernelError(f"silu_mul: gu must be contiguous [{T}, {2 * I}]")
-    _check(lib().cretif_silu_mul(_p(gu), _p(act), _dt(gu), T, I, _stream()), "silu_mul")
+    _check(lib().cretif_silu_mul(_p(gu), _p(act), _dt(gu), T, I, block, _stream()), "silu_mul")
 
 
 def rope_kv_append(qkv, cos, sin, pairing: int, rot_dim: int, nh: int, nkv: int, hd: int,
@@ -418,8 +420,9 @@ def fused_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, cos, sin, pairing: int, 
         int(write_cache), M, K, _p(fault), _stream()), "fused_qkv_rope")
 
 
-def fused_gate_up_silu(h, norm_w, eps: float, w_gu, act) -> None:
-    """act = silu(norm(h)·Wgᵀ) ⊙ (norm(h)·Wuᵀ) with [Wg; Wu] stacked, one kernel."""
+def fused_gate_up_silu(h, norm_w, eps: float, w_gu, act, block: int = 0) -> None:
+    """act = silu(norm(h)·Wgᵀ) ⊙ (norm(h)·Wuᵀ), one kernel; w_gu = [Wg; Wu] stacked
+    (``block`` = 0) or with rows interleaved in groups of ``block``."""
     _need(h, "h", torch.float32, 2); _need(w_gu, "w_gu", torch.bfloat16, 2)
     _need(act, "act", torch.bfloat16, 2)
     M, K = h.shape
@@ -427,8 +430,39 @@ def fused_gate_up_silu(h, norm_w, eps: float, w_gu, act) -> None:
     if tuple(w_gu.shape) != (2 * I, K) or act.shape[0] != M or not act.is_contiguous():
         raise KernelError("fused_gate_up_silu: shapes do not fit")
     _check(lib().cretif_fused_gate_up_silu(_p(h), _p(norm_w), ctypes.c_float(eps), _p(w_gu),
-                                           _rows(w_gu, "w_gu"), _p(act), I, M, K, _stream()),
-           "fused_gate_up_silu")
+                                           _rows(w_gu, "w_gu"), _p(act), I, block, M, K,
+                                           _stream()), "fused_gate_up_silu")
+
+
+def gemm_tc_silu(x, w_gu, act) -> None:
+    """act = silu(x·Wgᵀ) ⊙ (x·Wuᵀ) on the tensor cores; w_gu rows interleaved in groups of 64."""
+    _need(x, "x", torch.bfloat16, 2); _need(w_gu, "w_gu", torch.bfloat16, 2)
+    _need(act, "act", torch.bfloat16, 2)
+    M, K = x.shape
+    I = act.shape[1]
+    if tuple(w_gu.shape) != (2 * I, K) or act.shape[0] != M or not act.is_contiguous():
+        raise KernelError("gemm_tc_silu: shapes do not fit")
+    _check(lib().cretif_gemm_tc_silu(_p(x), _p(w_gu), _p(act), M, I, K, _rows(x, "x"),
+                                     _rows(w_gu, "w_gu"), _p(fault_word(x.device)), _stream()),
+           "gemm_tc_silu")
+
+
+def gemm_tc_qkv_rope(x, w_qkv, q_out, cos, sin, pairing: int, nh: int, nkv: int, hd: int,
+                     tok_pos, tok_seq, seq_slot, table, kc, vc, block_tokens: int,
+                     write_cache: bool) -> None:
+    """q|k|v product on the tensor cores with rotary and the cache write in its epilogue."""
+    _need(x, "x", torch.bfloat16, 2); _need(w_qkv, "w_qkv", torch.bfloat16, 2)
+    _need(q_out, "q", torch.bfloat16, 2)
+    M, K = x.shape
+    if tuple(w_qkv.shape) != ((nh + 2 * nkv) * hd, K) or q_out.shape[0] != M:
+        raise KernelError("gemm_tc_qkv_rope: shapes do not fit")
+    if cos.shape[1] != hd // 2:
+        raise KernelError("gemm_tc_qkv_rope: needs rotary_dim == head_dim")
+    _check(lib().cretif_gemm_tc_qkv_rope(
+        _p(x), _p(w_qkv), _p(q_out), _rows(q_out, "q"), _p(cos), _p(sin), pairing, nh, nkv, hd,
+        _p(tok_pos), _p(tok_seq), _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc),
+        block_tokens, int(write_cache), M, K, _rows(x, "x"), _rows(w_qkv, "w_qkv"),
+        _p(fault_word(x.device)), _stream()), "gemm_tc_qkv_rope")
 
 
 def attn_prefill_supported(hd: int, block_tokens: int) -> bool:

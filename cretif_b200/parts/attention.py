@@ -21,8 +21,9 @@ from .linear import linear
 
 _force_plain = False
 _fused_steps = True
-# Steps of at most this many tokens take the fused projection kernels.
-FUSED_MAX_TOKENS = 64
+# Steps of at most this many tokens take the fused projection kernels (measured on a B200 at
+# SmolLM2-135M sizes: fused wins up to 32 tokens, the tensor-core product beyond).
+FUSED_MAX_TOKENS = 32
 
 
 def fused_steps_enabled() -> bool:
@@ -87,10 +88,25 @@ class Attention(Part):
         return KVRequest(self.nkv, self.hd, self.window)
 
     def forward(self, x, ctx, cache):
-        qkv = linear(x, self.w_qkv)                                   # [T, q + 2 kv]
-        self.position.rotate_and_store(qkv, ctx, cache, self.nh, self.nkv, self.hd)
+        from .linear import plain_forced, skinny_max_rows
+        from .position import Rotary
         o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
-        self.attend(qkv, o, ctx, cache.kv)
+        if (self.dtype == torch.bfloat16 and ctx.T > skinny_max_rows() and not plain_forced()
+                and not _force_plain and self.hd in (64, 128) and type(self.position) is Rotary
+                and self.position.rot_dim == self.hd and cache.kv is not None
+                and ops.gemm_tc_supported(x, self.w_qkv, o)):
+            # many tokens: rotary and the cache write ride in the product's epilogue
+            kv = cache.kv
+            cos, sin = self.position._table
+            q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
+            ops.gemm_tc_qkv_rope(x, self.w_qkv, q, cos, sin, self.position.pairing, self.nh,
+                                 self.nkv, self.hd, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                                 kv.table, kv.k, kv.v, kv.block_tokens, cache.writes)
+            self.attend(q, o, ctx, kv)
+        else:
+            qkv = linear(x, self.w_qkv)                               # [T, q + 2 kv]
+            self.position.rotate_and_store(qkv, ctx, cache, self.nh, self.nkv, self.hd)
+            self.attend(qkv, o, ctx, cache.kv)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx, cache) -> bool:

@@ -20,7 +20,7 @@ import torch
 from ..csrc import ops
 
 # Rows up to which the weight-streaming kernel is used instead of the tensor-core one.
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 32
 
 _force_plain = False
 
@@ -29,6 +29,14 @@ def force_plain_kernels(on: bool) -> None:
     """Route every product to the CUDA-core kernel (used by tests as the yardstick)."""
     global _force_plain
     _force_plain = bool(on)
+
+
+def plain_forced() -> bool:
+    return _force_plain
+
+
+def skinny_max_rows() -> int:
+    return SKINNY_MAX_ROWS
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

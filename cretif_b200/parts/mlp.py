@@ -11,7 +11,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import linear
+from .linear import linear, plain_forced, skinny_max_rows as SKINNY_ROWS
 
 
 @register_part("feed_forward", "gated_mlp")
@@ -32,14 +32,31 @@ class GatedMLP(Part):
                 "up": (n["up"], WeightSpec((I, hidden_size))),
                 "down": (n["down"], WeightSpec((hidden_size, I)))}
 
+    # Rows of the stacked gate|up matrix alternate in groups of this many (64 gate rows, then
+    # their 64 up rows) when the tensor-core product can fuse SiLU·mul into its epilogue.
+    GU_BLOCK = 64
+
     def load(self, tensors):
-        self.w_gate_up = self._matrix(torch.cat([tensors["gate"], tensors["up"]], dim=0))
+        gate, up = tensors["gate"], tensors["up"]
+        I = self.inter
+        self.gu_block = self.GU_BLOCK if (self.dtype == torch.bfloat16 and I % self.GU_BLOCK == 0) else 0
+        if self.gu_block:
+            b = self.gu_block
+            stacked = torch.stack([gate.reshape(I // b, b, -1), up.reshape(I // b, b, -1)], dim=1)
+            self.w_gate_up = self._matrix(stacked.reshape(2 * I, -1))
+        else:
+            self.w_gate_up = self._matrix(torch.cat([gate, up], dim=0))
         self.w_down = self._matrix(tensors["down"])
 
     def forward(self, x, ctx):
-        gu = linear(x, self.w_gate_up)                                # [T, 2 I]
-        act = torch.empty((x.shape[0], self.inter), dtype=self.dtype, device=x.device)
-        ops.silu_mul(gu, act)
+        T = x.shape[0]
+        act = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
+        if (self.gu_block == 64 and T > SKINNY_ROWS() and not plain_forced()
+                and ops.gemm_tc_supported(x, self.w_gate_up, act)):
+            ops.gemm_tc_silu(x, self.w_gate_up, act)                  # product + SiLU·mul
+        else:
+            gu = linear(x, self.w_gate_up)                            # [T, 2 I]
+            ops.silu_mul(gu, act, self.gu_block)
         return linear(act, self.w_down, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx) -> bool:
@@ -54,7 +71,7 @@ class GatedMLP(Part):
                 or not ops.fused_supported(T, self.inter, self.w_down, norm=False)):
             return False
         act = torch.empty((T, self.inter), dtype=self.dtype, device=h.device)
-        ops.fused_gate_up_silu(h, norm.weight, norm.eps, self.w_gate_up, act)
+        ops.fused_gate_up_silu(h, norm.weight, norm.eps, self.w_gate_up, act, self.gu_block)
         ops.fused_linear_add(act, self.w_down, h)
         return True
 

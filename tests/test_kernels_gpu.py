@@ -210,7 +210,7 @@ def test_fused_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K
 
 
 # ------------------------------------------------------------------ row-wise kernels
-@pytest.mark.parametrize("T,H", [(1, 10), (5, 100), (3, 576), (2, 3000)])
+@pytest.mark.parametrize("T,H", [(1, 10), (5, 100), (3, 576), (2, 3000), (4, 6), (2, 8200)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(ops, T, H, out_dtype):
     eps = 3e-6
@@ -248,6 +248,84 @@ def test_silu_mul(ops, dtype):
     ops.silu_mul(gu, act)
     g, u = gu[:, :I].double(), gu[:, I:].double()
     close(act, g / (1 + torch.exp(-g)) * u, 1e-6 if dtype == torch.float32 else 5e-3)
+    # gate and up columns alternating in groups of 16
+    I, b = 96, 16
+    gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
+    act = torch.empty(T, I, device=DEV, dtype=dtype)
+    ops.silu_mul(gu, act, b)
+    blocks = gu.double().reshape(T, I // b, 2, b)
+    g, u = blocks[:, :, 0, :].reshape(T, I), blocks[:, :, 1, :].reshape(T, I)
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-6 if dtype == torch.float32 else 5e-3)
+
+
+def _interleave(gate, up, b=64):
+    I = gate.shape[0]
+    return torch.stack([gate.reshape(I // b, b, -1), up.reshape(I // b, b, -1)], dim=1).reshape(
+        2 * I, -1).contiguous()
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 1536, 576), (70, 192, 104), (2048, 256, 96)])
+def test_gemm_tc_silu(ops, M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16)
+    gate = rnd(I, K, dtype=torch.bfloat16, seed=1, scale=0.3)
+    up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
+    w = _interleave(gate, up)
+    act = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    ops.gemm_tc_silu(x, w, act)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    g = (x.double() @ gate.double().T).to(torch.bfloat16).double()
+    u = (x.double() @ up.double().T).to(torch.bfloat16).double()
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
+    # the few-token kernel reads the same interleaved matrix
+    h, nw = rnd(8, K), rnd(K, seed=3) * 0.1 + 1
+    a2 = torch.empty(8, I, device=DEV, dtype=torch.bfloat16)
+    ops.fused_gate_up_silu(h, nw, 1e-5, w, a2, 64)
+    a3 = torch.empty(8, I, device=DEV, dtype=torch.bfloat16)
+    ops.fused_gate_up_silu(h, nw, 1e-5, torch.cat([gate, up]).contiguous(), a3, 0)
+    close(a2, a3, 1e-2)
+
+
+@pytest.mark.parametrize("pairing", [0, 1])
+@pytest.mark.parametrize("nh,nkv,hd,K", [(9, 3, 64, 576), (2, 1, 128, 96), (3, 3, 64, 72)])
+def test_gemm_tc_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K):
+    theta, P = 10000.0, 512
+    lens = [200, 70, 333]
+    news = [200, 70, 150]                     # the third sequence continues at 183
+    j = torch.arange(hd // 2, dtype=torch.float64)
+    ang = torch.arange(P, dtype=torch.float64)[:, None] / theta ** (2 * j / hd)[None, :]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    qpos, qseq = [], []
+    for b, (n, m) in enumerate(zip(lens, news)):
+        qpos += list(range(n - m, n)); qseq += [b] * m
+    T = len(qpos)
+    pos_t = torch.tensor(qpos, dtype=torch.int32, device=DEV)
+    seq_t = torch.tensor(qseq, dtype=torch.int32, device=DEV)
+    x = rnd(T, K, dtype=torch.bfloat16)
+    w = rnd((nh + 2 * nkv) * hd, K, dtype=torch.bfloat16, seed=2, scale=0.3)
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    ca = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    qkv = torch.empty(T, (nh + 2 * nkv) * hd, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_simt(x, w, qkv)
+    ops.rope_kv_append(qkv, cos, sin, pairing, hd, nh, nkv, hd, pos_t, seq_t, ca.seq_slot,
+                       ca.table, ca.k, ca.v, 64, True, fault)
+    cb = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    q = torch.zeros(T, nh * hd, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc_qkv_rope(x, w, q, cos, sin, pairing, nh, nkv, hd, pos_t, seq_t, cb.seq_slot,
+                         cb.table, cb.k, cb.v, 64, True)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    close(q, qkv[:, :nh * hd], 1e-2)
+    close(cb.k, ca.k, 1e-2)
+    close(cb.v, ca.v, 1e-2)
+    cc = ToyCache(lens, nkv, hd, torch.bfloat16, seed=3)
+    before = cc.k.clone()
+    ops.gemm_tc_qkv_rope(x, w, q, cos, sin, pairing, nh, nkv, hd, pos_t, seq_t, cc.seq_slot,
+                         cc.table, cc.k, cc.v, 64, False)
+    assert torch.equal(cc.k, before)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

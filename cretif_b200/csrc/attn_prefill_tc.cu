@@ -55,6 +55,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// 2^x on the special-function unit; 2^(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t lbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((tc::smem_u32(tile) & 0x3FFFFu) >> 4);
@@ -198,6 +205,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int q_pos = start + q0 + row;
     const bool row_valid = row < rows_here;
     const int lo_key = window > 0 ? max(0, q_pos - window + 1) : 0;
+    // a step needs masks if it reaches past the first row's position or starts before the
+    // last row's window
+    const int lo_key_last = window > 0 ? max(0, start + q0 + kPfBQ - 1 - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     const int ocols = hd >> 1, obase = half * ocols;     // this thread's output columns
     float o[HDMAX / 2];
@@ -217,27 +227,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       tc::tmem_load_32(lane_addr + kColS + half * 64 + 32, sb);
       tc::tmem_load_wait();
       const int key0 = (blk_lo + 2 * j) * kPfBlk + half * 64;
+      // Raw scores stay in their registers; only steps that touch the diagonal, the
+      // sequence's end or a window's edge pay for masking (uniform for the whole CTA).
       float t[64];
+      const bool masked = key0 + 63 > pos_first || key0 < lo_key_last;
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = key0 + c;
+          const float sv = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]);
+          t[c] = (key <= q_pos && key >= lo_key) ? sv : -INFINITY;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]);
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int key = key0 + c;
-        const float sv = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]) * scale_log2;
-        t[c] = (key <= q_pos && key >= lo_key) ? sv : -INFINITY;
-        mx4[c & 3] = fmaxf(mx4[c & 3], t[c]);
-      }
-      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], t[c]);
+      // the scale is positive, so the largest raw score is the largest scaled one
+      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       float* xb = xch + (j & 1) * 256;        // double-buffered: one barrier per step
       xb[half * 128 + row] = mine;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
       const float m_new = fmaxf(m, fmaxf(mine, xb[(half ^ 1) * 128 + row]));
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+      const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+      // p = 2^(s * scale - m); a masked score (-inf) gives 0, and a row with nothing to see
+      // yet (m_new = -inf) uses 0 as its reference so that no inf - inf appears
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = (t[c] == -INFINITY) ? 0.f : exp2f(t[c] - m_new);
-        const float p1 = (t[c + 1] == -INFINITY) ? 0.f : exp2f(t[c + 1] - m_new);
+        const float p0 = fast_exp2(fmaf(t[c], scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(t[c + 1], scale_log2, neg_m));
         sum4[(c >> 1) & 3] += p0 + p1;
         packed[c >> 1] = pack2(p0, p1);
       }
@@ -307,7 +330,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
                                       unsigned int* fault, void* stream) {
   if (B <= 0 || T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
-      window < 0 || max_new <= 0 || nh > 65535 || B > 65535 || ldq % 8 || ldo % 8)
+      window < 0 || !(scale > 0.f) || max_new <= 0 || nh > 65535 || B > 65535 || ldq % 8 || ldo % 8)
     return kBadArgument;
   if (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) & 15) return kMisaligned;
   const long long cache_rows = n_blocks * nkv * kPfBlk;

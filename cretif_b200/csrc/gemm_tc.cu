@@ -23,16 +23,19 @@
 
 namespace cretif {
 
-constexpr int kTcBM = 128, kTcBK = 64, kTcStages = 4;
+constexpr int kTcBM = 128, kTcBK = 64;
 constexpr int kTcThreads = 192;
 
+// Narrow tiles take three stages so that two (BN = 128) or three (BN = 64) CTAs share an SM
+// and hide each other's fill and drain; the widest tile takes four.
 template <int BN>
 struct TcSmem {
+  static constexpr int kStages = BN >= 256 ? 4 : 3;
   static constexpr int kATile = kTcBM * kTcBK * 2;
   static constexpr int kBTile = BN * kTcBK * 2;
   static constexpr int kStage = kATile + kBTile;
-  static constexpr int kBars = kTcStages * kStage;          // offset of the barriers
-  static constexpr int kTotal = kBars + (2 * kTcStages + 1) * 8 + 16 + 1024;  // + align slack
+  static constexpr int kBars = kStages * kStage;          // offset of the barriers
+  static constexpr int kTotal = kBars + (2 * kStages + 1) * 8 + 16 + 1024;  // + align slack
 };
 
 // What the epilogue warps do with the accumulator.
@@ -70,6 +73,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TcSmem<BN>;
+  constexpr int kTcStages = L::kStages;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* empty = full + kTcStages;
   uint64_t* acc_full = empty + kTcStages;

@@ -149,6 +149,9 @@ def run_decode(engine, batch, steps, warmup, prompt_len, seed=0):
 
 
 def run_prefill(engine, tokens, repeats, warmup):
+    """One step over a prompt of `tokens` ids through Engine.step, timed with CUDA events.
+    (A step shape that repeats is replayed as a CUDA graph from its third call on; the
+    host-to-device copy of the token ids is inside the timed region.)"""
     import numpy as np
     import torch
     rng = np.random.default_rng(7)
@@ -156,15 +159,12 @@ def run_prefill(engine, tokens, repeats, warmup):
     times = []
     for i in range(warmup + repeats):
         slot = engine.alloc_slot()
-        ctx, want_rows, _ = engine.make_context([(slot, prompt)], "last")
-        engine.cache.begin_step([(slot, tokens)])
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        engine.model.forward(ctx, engine.cache, want_rows)
+        engine.step([(slot, prompt)], "last", check=False)
         b.record()
         torch.cuda.synchronize()
-        engine.cache.end_step([(slot, tokens)])
         engine.free_slot(slot)
         if i >= warmup:
             times.append(a.elapsed_time(b))

@@ -12,6 +12,7 @@ of the context, :832-849) are made here on the host before anything is launched.
 """
 from __future__ import annotations
 
+import collections
 import os
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
@@ -70,7 +71,7 @@ class Engine:
 
     def __init__(self, model_dir: str, dtype="bfloat16", max_tokens: int = 8192,
                  device="cuda:0", block_tokens: int = 64, max_slots: Optional[int] = None,
-                 max_len: Optional[int] = None):
+                 max_len: Optional[int] = None, step_graphs: bool = True):
         self.device = require_cuda(device)
         self.dtype = parse_dtype(dtype)
         self.model_dir = model_dir
@@ -89,6 +90,18 @@ class Engine:
         self.model.prepare(self.cache.max_len)
         self.fault = ops.fault_word(self.device)
         self.vocab_size = self.spec.vocab_size
+        # Steps whose shape (tokens per sequence, wanted places) repeats are captured as CUDA
+        # graphs on their second appearance and replayed afterwards; the least recently used
+        # ones are dropped.  Indices, slots and positions are read from a fixed device buffer
+        # that is refreshed before each replay, so a captured step serves any sequences.
+        self.step_graphs = step_graphs and self.model.graph_safe
+        self.graph_max_tokens = 8192
+        self.max_step_graphs = 16
+        self._graphs = collections.OrderedDict()
+        self._seen: Dict[tuple, int] = {}
+        self._last_meta_len = 0
+        self._graph_stream = torch.cuda.Stream(device=self.device)
+        self._graph_pool = torch.cuda.graph_pool_handle()
 
     # -- slots -------------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -98,8 +111,10 @@ class Engine:
         self.cache.free_slot(slot)
 
     # -- the step ------------------------------------------------------------------
-    def make_context(self, entries: Sequence[Entry], want) -> Tuple[StepContext, torch.Tensor, int]:
-        """Validate a step on the host and put its index arrays on the device."""
+    def make_context(self, entries: Sequence[Entry], want, meta: Optional[torch.Tensor] = None
+                     ) -> Tuple[StepContext, torch.Tensor, int]:
+        """Validate a step on the host and put its index arrays on the device (into ``meta``
+        when a buffer of the right size is given, else into a new tensor)."""
         if not entries:
             raise StepError("a step needs at least one sequence")
         slots = [int(s) for s, _ in entries]
@@ -138,7 +153,12 @@ class Engine:
             rows = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int64)
         packed = np.concatenate([ids, tok_pos, tok_seq, np.asarray(slots), starts, cu, rows]
                                 ).astype(np.int32)
-        meta = torch.from_numpy(packed).pin_memory().to(self.device, non_blocking=True)
+        self._last_meta_len = int(packed.size)
+        pinned = torch.from_numpy(packed).pin_memory()
+        if meta is None:
+            meta = pinned.to(self.device, non_blocking=True)
+        else:                                   # the fixed buffer of a captured step
+            meta.copy_(pinned, non_blocking=True)
         o = 0
 
         def take(n):
@@ -159,15 +179,61 @@ class Engine:
              check: bool = True) -> torch.Tensor:
         """Run one step; returns float32 logits ``[wanted, vocab]`` on the device, in the
         order of ``entries`` and of each entry's wanted places."""
-        ctx, want_rows, n_want = self.make_context(entries, want)
-        pairs = [(s, n) for s, n in zip(ctx.seq_slot_host, ctx.seq_new_host)]
-        self.cache.begin_step(pairs)
         all_rows = isinstance(want, str) and want == "all"
-        logits = self.model.forward(ctx, self.cache, None if all_rows else want_rows)
+        key = self._shape_key(entries, want) if self.step_graphs else None
+        captured = self._graphs.get(key) if key is not None else None
+        if captured is not None:
+            # the same step shape has been captured: refresh its indices, replay its kernels
+            ctx, want_rows, n_want = self.make_context(entries, want, meta=captured["meta"])
+            pairs = [(s, n) for s, n in zip(ctx.seq_slot_host, ctx.seq_new_host)]
+            self.cache.begin_step(pairs)
+            captured["graph"].replay()
+            logits = captured["logits"].clone()
+            self._graphs.move_to_end(key)
+        else:
+            ctx, want_rows, n_want = self.make_context(entries, want)
+            pairs = [(s, n) for s, n in zip(ctx.seq_slot_host, ctx.seq_new_host)]
+            self.cache.begin_step(pairs)
+            logits = self.model.forward(ctx, self.cache, None if all_rows else want_rows)
+            if key is not None:
+                self._maybe_capture(key, entries, want, all_rows, ctx.T)
         self.cache.end_step(pairs)
         if check:
             self.check_fault()
         return logits
+
+    # -- captured steps --------------------------------------------------------------
+    def _shape_key(self, entries, want):
+        """What a captured step depends on beyond the indices it reads from the device: how
+        many tokens each sequence brings and where logits are wanted."""
+        news = tuple(len(t) for _, t in entries)
+        if sum(news) > self.graph_max_tokens:
+            return None
+        w = want if isinstance(want, str) else tuple(tuple(int(i) for i in x) for x in want)
+        return (news, w)
+
+    def _maybe_capture(self, key, entries, want, all_rows, T) -> None:
+        """A step shape seen for the second time is captured as a CUDA graph (the step that
+        was just run left the cache in the state the capture's warm run expects: the capture
+        itself launches nothing)."""
+        self._seen[key] = self._seen.get(key, 0) + 1
+        if self._seen[key] < 2:
+            return
+        if len(self._seen) > 4096:
+            self._seen.clear()
+        n_meta = self._last_meta_len
+        meta = torch.zeros(n_meta, dtype=torch.int32, device=self.device)
+        ctx, want_rows, _ = self.make_context(entries, want, meta=meta)
+        graph = torch.cuda.CUDAGraph()
+        cur = torch.cuda.current_stream()
+        self._graph_stream.wait_stream(cur)
+        with torch.cuda.stream(self._graph_stream):
+            with torch.cuda.graph(graph, pool=self._graph_pool, stream=self._graph_stream):
+                logits = self.model.forward(ctx, self.cache, None if all_rows else want_rows)
+        cur.wait_stream(self._graph_stream)
+        self._graphs[key] = {"graph": graph, "meta": meta, "logits": logits}
+        while len(self._graphs) > self.max_step_graphs:
+            self._graphs.popitem(last=False)
 
     def check_fault(self) -> None:
         """Read the status word the kernels write (synchronises the device)."""

@@ -131,6 +131,7 @@ class DecodeRunner:
     launches with the same batch nothing is copied to the device."""
 
     def __init__(self, engine, sampler: Sampler, use_graph: bool = True):
+        use_graph = use_graph and engine.model.graph_safe
         self.engine, self.sampler, self.use_graph = engine, sampler, use_graph
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.bufs: Dict[int, dict] = {}

@@ -83,6 +83,14 @@ class Model:
         self.head = build_part("head", _with(spec.head, vocab_size=spec.vocab_size), H, dtype,
                                device)
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether every part allows its steps to be captured as CUDA graphs."""
+        parts = [self.embedding, self.final_norm, self.head]
+        for layer in self.layers:
+            parts += [layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     # -- weights ---------------------------------------------------------------
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Hand each part its tensors (CPU, by full name) and let it place them."""

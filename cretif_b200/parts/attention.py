@@ -48,6 +48,8 @@ class Attention(Part):
     (0 = all keys), ``position`` (a position part's kind and constants), ``names``
     (tensor names of q, k, v, o relative to the layer's prefix)."""
 
+    graph_safe = True
+
     def __init__(self, params, hidden_size, dtype, device):
         super().__init__(params, hidden_size, dtype, device)
         self.nh = int(params["num_heads"])

@@ -99,7 +99,15 @@ class LayerCache:
 
 
 class Part:
-    """Base of all parts: constants, weights, device placement."""
+    """Base of all parts: constants, weights, device placement.
+
+    ``graph_safe`` says that ``forward`` only launches work on the current stream — no
+    host reads of device data, no host-side state that changes from step to step — so a step
+    through the part can be captured as a CUDA graph.  It is False unless a part says
+    otherwise; a model with one part that is not graph-safe simply runs every step eagerly.
+    """
+
+    graph_safe = False
 
     def __init__(self, params: Dict[str, Any], hidden_size: int, dtype: torch.dtype, device):
         self.params = dict(params)

@@ -21,6 +21,8 @@ from .linear import linear
 class TokenEmbedding(Part):
     """params: ``name``; sized by the model's vocabulary (``vocab_size`` is injected)."""
 
+    graph_safe = True
+
     @classmethod
     def weight_specs(cls, params, hidden_size):
         return {"table": (params["name"], WeightSpec((params["vocab_size"], hidden_size)))}
@@ -40,6 +42,8 @@ class TokenEmbedding(Part):
 @register_part("head", "linear_head")
 class LinearHead(Part):
     """params: ``tied`` (share the embedding matrix), ``name``, ``vocab_size``."""
+
+    graph_safe = True
 
     @classmethod
     def weight_specs(cls, params, hidden_size):

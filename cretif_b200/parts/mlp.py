@@ -18,6 +18,8 @@ from .linear import linear, plain_forced, skinny_max_rows as SKINNY_ROWS
 class GatedMLP(Part):
     """params: ``intermediate_size``, ``activation`` ("silu"), ``names`` (gate, up, down)."""
 
+    graph_safe = True
+
     def __init__(self, params, hidden_size, dtype, device):
         super().__init__(params, hidden_size, dtype, device)
         self.inter = int(params["intermediate_size"])

@@ -18,6 +18,8 @@ from .base import Part, register_part
 class RMSNorm(Part):
     """params: ``eps``; ``name`` (tensor name relative to the prefix)."""
 
+    graph_safe = True
+
     @classmethod
     def weight_specs(cls, params, hidden_size):
         return {"weight": (params["name"], WeightSpec((hidden_size,), init=(1.0, 0.02)))}

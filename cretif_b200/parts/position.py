@@ -43,6 +43,8 @@ def rotary_table(theta: float, rot_dim: int, positions: int, device):
 class Rotary(Part):
     """params: ``theta``, ``rotary_dim``, ``pairing`` ("half" or "interleaved")."""
 
+    graph_safe = True
+
     def load(self, tensors):
         self.theta = float(self.params["theta"])
         self.rot_dim = int(self.params["rotary_dim"])
@@ -68,6 +70,8 @@ class Rotary(Part):
 @register_part("position", "none")
 class NoPosition(Part):
     """Stores keys and values unrotated."""
+
+    graph_safe = True
 
     def load(self, tensors):
         self._table = None

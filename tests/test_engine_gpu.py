@@ -98,3 +98,32 @@ def test_bfloat16_without_the_fused_few_token_kernels(engines, plain_logits, nam
     want = plain_logits(name, toks)
     assert rel_err(fused, want) <= TOL["bfloat16"] and rel_err(plain, want) <= TOL["bfloat16"]
     assert rel_err(fused, plain) <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_repeated_step_shape_is_replayed_as_a_graph(model_dirs, plain_logits, dtype):
+    """The first step of a shape runs eagerly, the second is captured, later ones are
+    replayed: other tokens, other slots and other cache blocks each time, same logits as the
+    plain model; and an engine without captured steps agrees."""
+    from cretif_b200.engine import Engine
+    eng = Engine(model_dirs["B"], dtype=dtype, max_tokens=1024)
+    off = Engine(model_dirs["B"], dtype=dtype, max_tokens=1024, step_graphs=False)
+    assert eng.step_graphs and not off.step_graphs
+    held = [eng.alloc_slot() for _ in range(2)]           # shift the slots the runs will get
+    for i in range(5):
+        toks = tiny.tokens("B", 70, 100 + i)
+        got = run_tail_by_one(eng, toks, tail=6)          # shapes (64,) and (1,) repeat
+        assert rel_err(got, plain_logits("B", toks)) <= TOL[dtype], i
+        if i == 2:
+            eng.free_slot(held.pop())                      # and change them again
+    assert len(eng._graphs) == 2
+    toks = tiny.tokens("B", 70, 104)
+    assert rel_err(run_tail_by_one(off, toks, tail=6), plain_logits("B", toks)) <= TOL[dtype]
+    assert len(off._graphs) == 0
+    # batches: the shape is the tuple of lengths
+    reqs = [tiny.tokens("B", n, 200 + n) for n in (30, 9, 17)]
+    for _ in range(3):
+        outs = run_batch(eng, reqs, [25, 9, 12])
+        for r, got in zip(reqs, outs):
+            assert rel_err(got, plain_logits("B", r)) <= TOL[dtype]
+    eng.cache.check()

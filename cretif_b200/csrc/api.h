@@ -119,6 +119,17 @@ int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, 
                            int nh, int nkv, int hd, float scale, int window, int bt, int B,
                            int max_new, unsigned int* fault, void* stream);
 
+// The whole decode step in one persistent launch (see decode_step.cu).  Layer records are
+// built on the host with cretif_step_layer_fill and copied to the device by the caller.
+int cretif_step_layer_bytes(void);
+int cretif_decode_step_supported(int B, int hd);
+int cretif_step_layer_fill(void* dst, const void* w_qkv, const void* w_o, const void* w_gu,
+                           const void* w_down, const float* norm1, const float* norm2, float eps1,
+                           float eps2, void* kc, void* vc, long long n_blocks, int nkv, int hd,
+                           const int* table, int table_stride, int write_cache);
+int cretif_decode_step(const int* ints, const float* floats, void* const* ptrs, int ctas,
+                       void* stream);
+
 // One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.
 int cretif_sample(const float* logits, int ld, int rows, int V, float temperature, int top_k,
                   unsigned long long seed, const long long* request, int* draw, int* out,

@@ -1,309 +1,15 @@
-// Decode attention over the block cache on the tensor cores (bfloat16, head_dim <= 128).
-//
-// One CTA serves one (sequence, key/value head, range of cache blocks).  A producer warp moves
-// the K and V tiles of each 64-key block into a ring of shared-memory stages with TMA (2-d
-// boxes out of the cache, 128-byte swizzle, so that ldmatrix reads them without bank
-// conflicts).  Each of the four consumer warps owns 16 of a tile's 64 keys and keeps its own
-// running maximum, sum and output for all query heads of the key/value head: the heads are
-// the rows of m16n8k16 products (S = Q K^T, then O += P V with P taken straight from the
-// accumulator registers), so the warps never synchronise inside the loop; their four partial
-// results are merged once at the end of the CTA.  Ranges of one sequence are merged by the
-// CTA that finishes last, as in attn_decode.cu (same scratch, same counters).
-//
-// The reference walks positions serially with one block per head (src/attention.cu:410-494).
-#include <cuda.h>
-#include <cuda_runtime.h>
-
+// Host side of the tensor-core decode attention and the entry point that allocates nothing;
+// the kernel is in attn_decode_mma.cuh.
 #include <mutex>
 
-#include "api.h"
+#include "attn_decode_mma.cuh"
 #include "attn_decode_noalloc.h"
-#include "tc_common.cuh"
 
 namespace cretif {
 
-int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
-                       int box_rows);
-
-constexpr int kDmWarps = 4;                 // consumer warps
-constexpr int kDmThreads = (kDmWarps + 1) * 32;
-constexpr int kDmTile = 64;
-constexpr int kDmStages = 3;
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void mma_16816_f32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                              uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-      "{%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// HD16 = head_dim / 16 (compile time: sizes the register arrays)
-template <int HD16>
-__global__ void __launch_bounds__(kDmThreads)
-attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v,
-                       const __nv_bfloat16* __restrict__ q, int ldq,
-                       const int* __restrict__ table, int table_stride,
-                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                       const int* __restrict__ seq_slot, int nh, int nkv, float scale_log2,
-                       int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
-                       unsigned int* __restrict__ fault) {
-  constexpr int hd = HD16 * 16;
-  constexpr int kSub = (hd + 63) / 64;                 // 64-wide column groups of a tile
-  constexpr int kTileBytes = kSub * kDmTile * 128;     // one of K or V
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* ktiles = smem;
-  unsigned char* vtiles = smem + kDmStages * kTileBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * kDmStages * kTileBytes);
-  uint64_t* empty = full + kDmStages;
-  volatile int* abort = reinterpret_cast<volatile int*>(empty + kDmStages);
-  int* is_last = const_cast<int*>(abort) + 1;
-  float* mrg = reinterpret_cast<float*>(const_cast<int*>(abort) + 4);   // warps' partials
-
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int g = nh / nkv;
-  const int split = blockIdx.x, n_splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos = tok_pos[b];
-  const int slot = seq_slot[tok_seq[b]];
-  const int* tab = table + (size_t)slot * table_stride;
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
-  const int first_tile = first_key / kDmTile, n_tiles = pos / kDmTile + 1;
-  const int per = (n_tiles - first_tile + n_splits - 1) / n_splits;
-  const int t_begin = first_tile + split * per, t_end = min(n_tiles, t_begin + per);
-  const int my_tiles = max(0, t_end - t_begin);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kDmStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], kDmWarps); }
-    *abort = 0;
-    tc::fence_barrier_init();
-  }
-  __syncthreads();
-
-  // per-warp results for the merge: [warp][g] m, l and [warp][g][hd] o
-  float* mrg_m = mrg;
-  float* mrg_l = mrg + kDmWarps * 8;
-  float* mrg_o = mrg + 2 * kDmWarps * 8;
-
-  if (warp == kDmWarps) {
-    // ---------------- producer
-    if (lane == 0) {
-      for (int it = 0; it < my_tiles; ++it) {
-        const int s = it % kDmStages;
-        if (it >= kDmStages && !tc::mbar_wait(&empty[s], (uint32_t)((it / kDmStages - 1) & 1), abort))
-          break;
-        const int blk = tab[t_begin + it];
-        if (blk < 0) atomicOr(fault, kFaultBlockTable);
-        const int row = (max(blk, 0) * nkv + kvh) * kDmTile;
-        tc::mbar_expect_tx(&full[s], 2u * kTileBytes);
-#pragma unroll
-        for (int sub = 0; sub < kSub; ++sub) {
-          tc::tma_load_2d(ktiles + s * kTileBytes + sub * kDmTile * 128, &map_k, 64 * sub, row, &full[s]);
-          tc::tma_load_2d(vtiles + s * kTileBytes + sub * kDmTile * 128, &map_v, 64 * sub, row, &full[s]);
-        }
-      }
-    }
-  } else {
-    // ---------------- consumers: warp w owns keys 16w .. 16w+15 of every tile
-    const int r = lane >> 2, c = lane & 3;
-    // Q as the A operand: rows = heads of this kv head (rows >= g are zero)
-    uint32_t qa[HD16][2];
-    {
-      const __nv_bfloat16* qrow = q + (size_t)b * ldq + (size_t)(kvh * g + r) * hd;
-#pragma unroll
-      for (int ks = 0; ks < HD16; ++ks) {
-        qa[ks][0] = r < g ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
-        qa[ks][1] = r < g ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * c) : 0u;
-      }
-    }
-    float o[HD16 * 2][2];                 // [8-dim tile][2 dims] of row r
-#pragma unroll
-    for (int i = 0; i < HD16 * 2; ++i) o[i][0] = o[i][1] = 0.f;
-    float m = -INFINITY, l = 0.f;         // of row r (partial over this thread's keys for l)
-    const int mat = lane >> 3, rin = lane & 7;
-    bool ok = true;
-    for (int it = 0; it < my_tiles; ++it) {
-      const int s = it % kDmStages;
-      if (!tc::mbar_wait(&full[s], (uint32_t)((it / kDmStages) & 1), abort)) { ok = false; break; }
-      const uint32_t kbase = tc::smem_u32(ktiles + s * kTileBytes);
-      const uint32_t vbase = tc::smem_u32(vtiles + s * kTileBytes);
-      // ---- S = Q K^T for this warp's 16 keys
-      float sacc[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[n][e] = 0.f;
-      {
-        const int key = warp * 16 + (mat >> 1) * 8 + rin;          // row of the tile this lane addresses
-#pragma unroll
-        for (int ks = 0; ks < HD16; ++ks) {
-          const int chunk = ks * 2 + (mat & 1);                    // 16-byte chunk along head_dim
-          const uint32_t addr = kbase + (chunk >> 3) * (kDmTile * 128) + key * 128 +
-                                (((chunk & 7) ^ (key & 7)) << 4);
-          uint32_t kb[4];
-          ldmatrix_x4(kb, addr);
-          mma_16816_f32(sacc[0], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
-          mma_16816_f32(sacc[1], qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
-        }
-      }
-      // ---- online softmax of row r over this thread's 4 keys (and the quad's 16)
-      const int key0 = (t_begin + it) * kDmTile + warp * 16;
-      float t4[4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = key0 + n * 8 + 2 * c + e;
-          const bool valid = key <= pos && key >= first_key;
-          t4[n * 2 + e] = valid ? sacc[n][e] * scale_log2 : -INFINITY;
-        }
-      float mx = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m, mx);
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-      float p4[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) p4[e] = (t4[e] == -INFINITY) ? 0.f : exp2f(t4[e] - m_new);
-      l = l * alpha + (p4[0] + p4[1] + p4[2] + p4[3]);
-      m = m_new;
-#pragma unroll
-      for (int i = 0; i < HD16 * 2; ++i) { o[i][0] *= alpha; o[i][1] *= alpha; }
-      // ---- O += P V : P (16 x 16 keys) straight from the accumulators
-      const uint32_t pa0 = pack_bf16(p4[0], p4[1]), pa2 = pack_bf16(p4[2], p4[3]);
-      {
-        const int key = warp * 16 + (mat & 1) * 8 + rin;
-#pragma unroll
-        for (int np = 0; np < HD16; ++np) {                        // pairs of 8-dim tiles
-          const int chunk = np * 2 + (mat >> 1);
-          const uint32_t addr = vbase + (chunk >> 3) * (kDmTile * 128) + key * 128 +
-                                (((chunk & 7) ^ (key & 7)) << 4);
-          uint32_t vb[4];
-          ldmatrix_x4_trans(vb, addr);
-          float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f};
-          float c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
-          mma_16816_f32(c0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
-          mma_16816_f32(c1, pa0, 0u, pa2, 0u, vb[2], vb[3]);
-          o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1];
-          o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
-        }
-      }
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&empty[s]);
-    }
-    (void)ok;
-    // ---- this warp's result for the merge
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (r < g) {
-      if (c == 0) { mrg_m[warp * 8 + r] = m; mrg_l[warp * 8 + r] = l; }
-#pragma unroll
-      for (int i = 0; i < HD16 * 2; ++i) {
-        mrg_o[((size_t)warp * 8 + r) * hd + i * 8 + 2 * c] = o[i][0];
-        mrg_o[((size_t)warp * 8 + r) * hd + i * 8 + 2 * c + 1] = o[i][1];
-      }
-    }
-  }
-  __syncthreads();
-  if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
-
-  // ---- merge the four warps into this range's partial (unnormalised o, m, l)
-  float* po = part_o + (((size_t)b * nh + (size_t)kvh * g) * n_splits + split) * hd;
-  float* pml = part_ml + (((size_t)b * nh + (size_t)kvh * g) * n_splits + split) * 2;
-  for (int i = threadIdx.x; i < g * hd; i += kDmThreads) {
-    const int j = i / hd, d = i - j * hd;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kDmWarps; ++w) mm = fmaxf(mm, my_tiles > 0 ? mrg_m[w * 8 + j] : -INFINITY);
-    float acc = 0.f, ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < kDmWarps; ++w) {
-      const float mw = my_tiles > 0 ? mrg_m[w * 8 + j] : -INFINITY;
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-      acc = fmaf(f, my_tiles > 0 ? mrg_o[((size_t)w * 8 + j) * hd + d] : 0.f, acc);
-      ll = fmaf(f, my_tiles > 0 ? mrg_l[w * 8 + j] : 0.f, ll);
-    }
-    po[(size_t)j * n_splits * hd + d] = acc;
-    if (d == 0) { pml[(size_t)j * n_splits * 2] = mm; pml[(size_t)j * n_splits * 2 + 1] = ll; }
-  }
-
-  // ---- the CTA that finishes last for this (sequence, kv head) merges the ranges
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    int* ctr = counters + (size_t)b * nkv + kvh;
-    const int prev = atomicAdd(ctr, 1);
-    *is_last = prev == n_splits - 1;
-    if (*is_last) { *ctr = 0; __threadfence(); }
-  }
-  __syncthreads();
-  if (!*is_last) return;
-  float* wts = mrg;                       // [g][n_splits]
-  float* inv_den = mrg + 8 * kDmTile;     // [g]
-  const float* ml_base = part_ml + ((size_t)b * nh + (size_t)kvh * g) * n_splits * 2;
-  const float* po_base = part_o + ((size_t)b * nh + (size_t)kvh * g) * n_splits * hd;
-  for (int j = warp; j < g; j += kDmWarps + 1) {
-    float mx = -INFINITY;
-    for (int s = lane; s < n_splits; s += 32)
-      mx = fmaxf(mx, __ldcg(ml_base + ((size_t)j * n_splits + s) * 2));
-    mx = warp_max(mx);
-    float den = 0.f;
-    for (int s = lane; s < n_splits; s += 32) {
-      const float ms = __ldcg(ml_base + ((size_t)j * n_splits + s) * 2);
-      const float ls = __ldcg(ml_base + ((size_t)j * n_splits + s) * 2 + 1);
-      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
-      wts[j * n_splits + s] = w;
-      den += w * ls;
-    }
-    den = warp_sum(den);
-    if (lane == 0) inv_den[j] = 1.0f / den;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < g * hd; i += kDmThreads) {
-    const int j = i / hd, d = i - j * hd;
-    float acc_o = 0.f;
-    for (int s0 = 0; s0 < n_splits; s0 += 16) {
-      float v[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u)
-        v[u] = s0 + u < n_splits ? __ldcg(po_base + ((size_t)j * n_splits + s0 + u) * hd + d) : 0.f;
-#pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (s0 + u < n_splits) acc_o = fmaf(wts[j * n_splits + s0 + u], v[u], acc_o);
-    }
-    out[(size_t)b * ldo + (size_t)(kvh * g + j) * hd + d] = __float2bfloat16_rn(acc_o * inv_den[j]);
-  }
-}
-
 template <int HD16>
 static size_t dm_smem_bytes() {
-  constexpr int hd = HD16 * 16;
-  constexpr int kSub = (hd + 63) / 64;
-  size_t bytes = (size_t)2 * kDmStages * kSub * kDmTile * 128;   // K and V stages
-  bytes += 2 * kDmStages * 8 + 16;                                // barriers, abort, is_last
-  size_t mrg = (size_t)(2 * kDmWarps * 8 + kDmWarps * 8 * hd) * 4;
-  size_t wts = (size_t)(8 * kDmTile + 8) * 4;
-  bytes += mrg > wts ? mrg : wts;
-  return bytes + 1024;
+  return dm_smem_core<HD16>() + 1024;
 }
 
 template <int HD16>

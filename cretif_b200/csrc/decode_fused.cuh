@@ -1,0 +1,359 @@
+// Fused decode projections: the weight-streaming product of gemm_skinny.cu with the work
+// that surrounds it in a decode step folded into its prologue and epilogue, so that a
+// layer needs five launches instead of ten:
+//
+//   prologue NORM   x = bf16(h * w_norm * rsqrt(mean(h^2) + eps)) computed by every CTA from the
+//                   32-bit residual stream (a few KB for a decode batch) into shared memory,
+//                   optionally from gathered rows (the rows whose logits are wanted);
+//   epilogue ROPE   the stacked q|k|v product: rotary pairs of q and k are rotated in 32-bit,
+//                   q goes to the query buffer, rotated k and v go straight into the block
+//                   cache at each token's position;
+//   epilogue SILU   the stacked gate|up product: act = silu(gate) * up;
+//   epilogue PLAIN  store (bfloat16 / float32) or add into the 32-bit residual stream.
+//
+// To make the epilogues local, a CTA's 16 weight rows are not consecutive: for ROPE they are
+// the two halves of 8 rotary pairs, for SILU 8 gate rows and the 8 up rows below them.  The
+// 8-row distance is exactly the distance between the two accumulator rows a lane of the
+// m16n8k16 product holds, and after the warps' partial sums have met in shared memory one
+// thread finishes one pair.
+//
+// Arithmetic is the unfused kernels' (elementwise.cu), so a token gets the same numbers
+// whichever path ran it.  The reference fuses only residual + norm
+// (src/kernels/elementwise.cu:463-506).
+#pragma once
+
+#include "api.h"
+#include "common.cuh"
+
+namespace cretif {
+
+constexpr int kFuWarps = 8;
+constexpr int kFuRows = 16;
+enum Prologue : int { kProPlain = 0, kProNorm = 1 };
+enum Epilogue : int { kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2 };
+
+struct FusedParams {
+  // product
+  const __nv_bfloat16* W;   // [N, K]
+  int M, N, K, ldw;
+  // prologue
+  const __nv_bfloat16* X;   // plain: [M, K] bf16
+  int ldx;
+  const float* H;           // norm: residual stream [*, K]
+  const float* norm_w;      // [K]
+  const int* rows;          // optional gather: x row m comes from H[rows[m]]
+  float eps;
+  // epilogue plain
+  void* C;
+  int ldc, c_dt, accumulate;
+  // epilogue rope
+  __nv_bfloat16* Q;         // [M, nh*hd]
+  int ldq;
+  const float* cos_t;
+  const float* sin_t;
+  int pairing, nh, nkv, hd;
+  const int* tok_pos;
+  const int* tok_seq;
+  const int* seq_slot;
+  const int* table;
+  int table_stride;
+  __nv_bfloat16* kc;
+  __nv_bfloat16* vc;
+  int bt, write_cache;
+  unsigned int* fault;
+  // epilogue silu
+  __nv_bfloat16* act;       // [M, I]
+  int I, gu_block;          // gu_block > 0: gate/up rows interleaved in groups of that size
+};
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Weight row of tile row r (0..15) of CTA `tile`; -1 if beyond the matrix.
+template <int EPI>
+__device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
+  if (EPI == kEpiPlain) {
+    const int n = tile * kFuRows + r;
+    return n < p.N ? n : -1;
+  } else if (EPI == kEpiSilu) {
+    const int i = tile * 8 + (r & 7);
+    if (i >= p.I) return -1;
+    if (p.gu_block) {
+      const int g = (i / p.gu_block) * 2 * p.gu_block + i % p.gu_block;
+      return r < 8 ? g : g + p.gu_block;
+    }
+    return r < 8 ? i : p.I + i;
+  } else {
+    const int tiles_per_head = p.hd >> 4;
+    const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+    if (head >= p.nh + p.nkv) return head * p.hd + t * 16 + r;        // v: plain rows
+    const int j = t * 8 + (r & 7);                                    // rotary pair index
+    if (p.pairing) return head * p.hd + 2 * j + (r >> 3);
+    return head * p.hd + j + (r >> 3) * (p.hd >> 1);
+  }
+}
+
+template <int NT, int EPI>
+__device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
+                                            float (*red)[kFuRows][8 * NT + 1]) {
+  if (EPI == kEpiPlain) {
+    for (int i = threadIdx.x; i < kFuRows * p.M; i += kFuWarps * 32) {
+      const int m = i / kFuRows, rr = i - m * kFuRows;
+      const int n = tile * kFuRows + rr;
+      if (n >= p.N) continue;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kFuWarps; ++w) sum += red[w][rr][m];
+      if (p.c_dt == kF32) {
+        float* out = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n;
+        if (p.accumulate) sum += __ldcg(out);
+        *out = sum;
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum);
+      }
+    }
+  } else {
+    // one thread per (token, pair): rows pr and pr + 8 of the tile
+    for (int i = threadIdx.x; i < 8 * p.M; i += kFuWarps * 32) {
+      const int m = i >> 3, pr = i & 7;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < kFuWarps; ++w) { s0 += red[w][pr][m]; s1 += red[w][pr + 8][m]; }
+      if (EPI == kEpiSilu) {
+        const int col = tile * 8 + pr;
+        if (col >= p.I) continue;
+        // the unfused path stores gate and up as bfloat16 before the activation
+        const float g = __bfloat162float(__float2bfloat16_rn(s0));
+        const float u = __bfloat162float(__float2bfloat16_rn(s1));
+        p.act[(size_t)m * p.I + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+      } else {
+        const int tiles_per_head = p.hd >> 4;
+        const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+        const int pos = p.tok_pos[m];
+        size_t cache_row = 0;
+        bool cache_ok = false;
+        if (head >= p.nh && p.write_cache) {
+          const int slot = p.seq_slot[p.tok_seq[m]];
+          const int blk = p.table[(size_t)slot * p.table_stride + pos / p.bt];
+          if (blk < 0) atomicOr(p.fault, kFaultBlockTable);
+          else {
+            cache_ok = true;
+            const int kvh = head < p.nh + p.nkv ? head - p.nh : head - p.nh - p.nkv;
+            cache_row = (((size_t)blk * p.nkv + kvh) * p.bt + (pos % p.bt)) * p.hd;
+          }
+        }
+        if (head >= p.nh + p.nkv) {                      // v: rows t*16 + pr and + 8, no rotation
+          if (cache_ok) {
+            p.vc[cache_row + t * 16 + pr] = __float2bfloat16_rn(s0);
+            p.vc[cache_row + t * 16 + pr + 8] = __float2bfloat16_rn(s1);
+          }
+          continue;
+        }
+        const int j = t * 8 + pr;
+        const int i0 = p.pairing ? 2 * j : j, i1 = p.pairing ? 2 * j + 1 : j + (p.hd >> 1);
+        // the unfused path stores q and k as bfloat16 before rotating them
+        const float x0 = __bfloat162float(__float2bfloat16_rn(s0));
+        const float x1 = __bfloat162float(__float2bfloat16_rn(s1));
+        const float cs = p.cos_t[(size_t)pos * (p.hd >> 1) + j];
+        const float sn = p.sin_t[(size_t)pos * (p.hd >> 1) + j];
+        const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
+        const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
+        if (head < p.nh) {
+          __nv_bfloat16* q = p.Q + (size_t)m * p.ldq + (size_t)head * p.hd;
+          q[i0] = y0;
+          q[i1] = y1;
+        } else if (cache_ok) {
+          p.kc[cache_row + i0] = y0;
+          p.kc[cache_row + i1] = y1;
+        }
+      }
+    }
+  }
+}
+
+constexpr int kFuPre = 3;      // weight chunks per warp fetched ahead (covers K <= 768)
+
+template <int EPI>
+__device__ __forceinline__ void fetch_weights(const FusedParams& p, int tile, int warp, int r, int c,
+                                              int n_chunks, uint4 (&pa)[kFuPre], uint4 (&pb)[kFuPre]) {
+  const int row_a = tile_row<EPI>(p, tile, r), row_b = tile_row<EPI>(p, tile, r + 8);
+  const __nv_bfloat16* wa = p.W + (size_t)max(row_a, 0) * p.ldw + c * 8;
+  const __nv_bfloat16* wb = p.W + (size_t)max(row_b, 0) * p.ldw + c * 8;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int i = 0; i < kFuPre; ++i) {
+    const int ch = warp + kFuWarps * i;
+    const bool in = ch < n_chunks && ch * 32 + c * 8 < p.K;
+    pa[i] = in ? __ldg(reinterpret_cast<const uint4*>(wa + ch * 32)) : zero;
+    pb[i] = in ? __ldg(reinterpret_cast<const uint4*>(wb + ch * 32)) : zero;
+  }
+}
+
+// The body of the fused product for the CTA's share of tiles: tiles first_tile,
+// first_tile + tile_stride, ...  `pdl`: signal/await the neighbouring launches
+// (programmatic dependent launch); the whole-step kernel passes false.
+template <int NT, int PRO, int EPI>
+__device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_tiles,
+                                                   unsigned char* fsmem, int first_tile,
+                                                   int tile_stride, bool pdl) {
+  if (first_tile >= n_tiles) return;          // (the whole CTA: nothing to do in this call)
+  float(*red)[kFuRows][8 * NT + 1] = reinterpret_cast<float(*)[kFuRows][8 * NT + 1]>(fsmem);
+  // x tile (norm prologue) after the reduction buffer; row stride ≡ 64 (mod 128) bytes so
+  // that a quarter-warp's eight 16-byte reads touch all banks once
+  const int xs_stride = ((p.K * 2 + 127) / 128) * 128 + 64;
+  unsigned char* xs = fsmem + sizeof(float) * kFuWarps * kFuRows * (8 * NT + 1);
+  xs = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(xs) + 15) & ~uintptr_t(15));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, c = lane & 3;
+  const int n_chunks = (p.K + 31) >> 5;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  // The first tile's weights do not depend on anything computed before this kernel: ask for
+  // them first, so that their latency runs under the prologue.
+  int tile = first_tile;
+  uint4 pa[kFuPre], pb[kFuPre];
+  if (tile < n_tiles) fetch_weights<EPI>(p, tile, warp, r, c, n_chunks, pa, pb);
+  // Programmatic dependent launch: the kernel behind this one may start its own weight
+  // fetch now, and this one goes on to read activations only when the kernel before it has
+  // finished (a no-op when the launch was an ordinary one).
+  if (pdl) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+
+  if (PRO == kProNorm) {
+    const int n4 = p.K >> 2;
+    for (int m = warp; m < p.M; m += kFuWarps) {
+      const float4* h4 = reinterpret_cast<const float4*>(p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K);
+      const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+      __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
+      if (n4 <= 256) {                       // the row fits in registers: one trip to memory
+        float4 v[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = u * 32 + lane;
+          v[u] = i < n4 ? __ldcg(h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = u * 32 + lane;
+          if (i < n4) {
+            const float4 w = w4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * w.x * inv, v[u].y * w.y * inv);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * w.z * inv, v[u].w * w.w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+          }
+        }
+      } else {
+        float ss = 0.f;
+        for (int i = lane; i < n4; i += 32) {
+          const float4 v = __ldcg(h4 + i);
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)p.K + p.eps);
+        for (int i = lane; i < n4; i += 32) {
+          const float4 v = __ldcg(h4 + i), w = w4[i];
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * w.x * inv, v.y * w.y * inv);
+          __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * w.z * inv, v.w * w.w * inv);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  for (; tile < n_tiles; tile += tile_stride) {
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+
+    auto consume = [&](const uint4& ua, const uint4& ub, int ch) {
+      const int k = ch * 32 + c * 8;
+      const bool in = ch < n_chunks && k < p.K;
+      const uint32_t a1[4] = {ua.x, ub.x, ua.y, ub.y};
+      const uint32_t a2[4] = {ua.z, ub.z, ua.w, ub.w};
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const int m = t * 8 + r;
+        uint4 ux = zero;
+        if (in && m < p.M) {
+          if (PRO == kProNorm)
+            ux = *reinterpret_cast<const uint4*>(xs + (size_t)m * xs_stride + (size_t)k * 2);
+          else
+            ux = __ldcg(reinterpret_cast<const uint4*>(p.X + (size_t)m * p.ldx + k));
+        }
+        mma_16816(acc[t], a1, ux.x, ux.y);
+        mma_16816(acc[t], a2, ux.z, ux.w);
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < kFuPre; ++i) consume(pa[i], pb[i], warp + kFuWarps * i);
+    if (n_chunks > kFuWarps * kFuPre) {
+      const int row_a = tile_row<EPI>(p, tile, r), row_b = tile_row<EPI>(p, tile, r + 8);
+      const __nv_bfloat16* wa = p.W + (size_t)max(row_a, 0) * p.ldw + c * 8;
+      const __nv_bfloat16* wb = p.W + (size_t)max(row_b, 0) * p.ldw + c * 8;
+      for (int ch = warp + kFuWarps * kFuPre; ch < n_chunks; ch += 2 * kFuWarps) {
+        const int ch2 = ch + kFuWarps;
+        const bool in1 = ch * 32 + c * 8 < p.K, in2 = ch2 < n_chunks && ch2 * 32 + c * 8 < p.K;
+        const uint4 ua1 = in1 ? __ldg(reinterpret_cast<const uint4*>(wa + ch * 32)) : zero;
+        const uint4 ub1 = in1 ? __ldg(reinterpret_cast<const uint4*>(wb + ch * 32)) : zero;
+        const uint4 ua2 = in2 ? __ldg(reinterpret_cast<const uint4*>(wa + ch2 * 32)) : zero;
+        const uint4 ub2 = in2 ? __ldg(reinterpret_cast<const uint4*>(wb + ch2 * 32)) : zero;
+        consume(ua1, ub1, ch);
+        consume(ua2, ub2, ch2);
+      }
+    }
+    // the next tile's weights travel while this tile is reduced and finished
+    if (tile + tile_stride < n_tiles)
+      fetch_weights<EPI>(p, tile + tile_stride, warp, r, c, n_chunks, pa, pb);
+
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      red[warp][r][t * 8 + 2 * c] = acc[t][0];
+      red[warp][r][t * 8 + 2 * c + 1] = acc[t][1];
+      red[warp][r + 8][t * 8 + 2 * c] = acc[t][2];
+      red[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
+    }
+    __syncthreads();
+    finish_tile<NT, EPI>(p, tile, red);
+    __syncthreads();
+  }
+}
+
+
+template <int NT, int PRO, int EPI>
+__global__ void __launch_bounds__(kFuWarps * 32, NT <= 2 ? 3 : 2)
+skinny_fused_kernel(const FusedParams p, int n_tiles) {
+  extern __shared__ __align__(16) unsigned char fsmem_k[];
+  skinny_fused_tiles<NT, PRO, EPI>(p, n_tiles, fsmem_k, blockIdx.x, gridDim.x, true);
+}
+
+inline size_t fused_smem(int nt, int pro, int M, int K) {
+  size_t bytes = sizeof(float) * kFuWarps * kFuRows * (8 * nt + 1) + 16;
+  if (pro == kProNorm) bytes += (size_t)M * (((K * 2 + 127) / 128) * 128 + 64);
+  return bytes;
+}
+
+}  // namespace cretif

@@ -88,6 +88,8 @@ class Engine:
                                    self.device, block_tokens=block_tokens, max_slots=max_slots,
                                    max_len=longest)
         self.model.prepare(self.cache.max_len)
+        from .step_kernel import StepKernel
+        self.model.step_kernel = StepKernel(self.model, self.cache)
         self.fault = ops.fault_word(self.device)
         self.vocab_size = self.spec.vocab_size
         # Steps whose shape (tokens per sequence, wanted places) repeats are captured as CUDA
@@ -240,6 +242,9 @@ class Engine:
         word = int(self.fault.item())
         if word:
             self.fault.zero_()
+            sk = getattr(self.model, "step_kernel", None)
+            if sk is not None and sk.ok:
+                sk.barrier.zero_()         # a step that gave up may have left it half counted
             what = [msg for bit, msg in _FAULTS.items() if word & bit]
             raise StepError("device fault: " + "; ".join(what or [f"status {word}"]))
 

@@ -130,6 +130,9 @@ class Model:
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Run the scheduled layers on the step's tokens; logits [rows, vocab] float32
         at ``want_rows`` (token indices), or at every token when it is None."""
+        sk = getattr(self, "step_kernel", None)
+        if sk is not None and sk.takes(ctx):
+            return sk.run(ctx, want_rows)            # the whole step in one launch
         h = self.embedding.forward(ctx.tok_ids, ctx)
         pending = None
         for i, entry in enumerate(self.spec.schedule):

@@ -68,14 +68,26 @@ struct StepParams {
   float* logits;                      // [n_want, V]
   unsigned int* barrier;              // [2]: arrivals, leavers; zero before the first launch
   unsigned int* fault;
+  unsigned long long* stamps;         // optional: CTA 0 notes the time (ns) after every barrier
 };
 
 constexpr unsigned kGridSpinLimit = 1u << 22;
 
+// Ask L2 for a matrix the grid will read soon (one 128-byte line per thread and round), so
+// that the phase that needs it finds it on the chip: weights of the next layer travel while
+// this layer computes and waits at its barriers.
+__device__ __forceinline__ void prefetch_l2(const void* base, size_t bytes, int cta, int P) {
+  const char* p = static_cast<const char*>(base);
+  const size_t lines = (bytes + 127) >> 7;
+  for (size_t i = (size_t)cta * blockDim.x + threadIdx.x; i < lines; i += (size_t)P * blockDim.x)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p + (i << 7)));
+}
+
 // All CTAs of the grid meet here; `target` = number of arrivals that completes this barrier.
 __device__ __forceinline__ void grid_barrier(unsigned int* arrivals, unsigned int target,
-                                             unsigned int* fault) {
-  asm volatile("fence.proxy.async;" ::: "memory");   // this thread's stores vs. later TMA reads
+                                             unsigned int* fault, bool before_tma = false) {
+  // stores that a later phase reads with TMA (the cache rows) must cross to the async proxy
+  if (before_tma) asm volatile("fence.proxy.async;" ::: "memory");
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -109,6 +121,14 @@ decode_step_kernel(const StepParams p) {
   unsigned char* gemv_smem = smem + ((dm_smem_core<HD16>() + 1023) & ~size_t(1023));
   const int P = gridDim.x, cta = blockIdx.x;
   unsigned int done = 0;            // barriers passed so far
+  auto stamp = [&]() {
+    if (p.stamps && cta == 0 && threadIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      p.stamps[done] = t;
+    }
+  };
+  stamp();
   dm_init<HD16>(attn_smem);
   uint32_t it_base = 0;
 
@@ -121,12 +141,36 @@ decode_step_kernel(const StepParams p) {
     for (int i = threadIdx.x; i < p.H; i += blockDim.x)
       p.h[(size_t)row * p.H + i] = ok ? __bfloat162float(src[i]) : 0.f;
   }
-  grid_barrier(p.barrier, ++done * P, p.fault);
-
   const int q_dim = p.nh * p.hd, qkv_rows = (p.nh + 2 * p.nkv) * p.hd;
   const int n_items = p.B * p.nkv * p.n_splits;
+  const size_t qkv_bytes = (size_t)qkv_rows * p.H * 2, o_bytes = (size_t)p.H * q_dim * 2;
+  const size_t gu_bytes = (size_t)2 * p.I * p.H * 2, down_bytes = (size_t)p.H * p.I * 2;
+  const size_t head_bytes = (size_t)p.V * p.H * 2;
+  const int head_layers = p.n_layers < 8 ? p.n_layers : 8;     // the head travels in 8 parts
+  {
+    const StepLayer& L0 = p.layers[0];
+    prefetch_l2(L0.w_qkv, qkv_bytes, cta, P);
+    prefetch_l2(L0.w_o, o_bytes, cta, P);
+    prefetch_l2(L0.w_gu, gu_bytes, cta, P);
+    prefetch_l2(L0.w_down, down_bytes, cta, P);
+  }
+  grid_barrier(p.barrier, ++done * P, p.fault);
+  stamp();
+
   for (int l = 0; l < p.n_layers; ++l) {
     const StepLayer& L = p.layers[l];
+    if (l + 1 < p.n_layers) {                 // next layer's first two matrices
+      prefetch_l2(p.layers[l + 1].w_qkv, qkv_bytes, cta, P);
+      prefetch_l2(p.layers[l + 1].w_o, o_bytes, cta, P);
+    }
+    if (l >= p.n_layers - head_layers) {      // a slice of the head's matrix
+      const int part = l - (p.n_layers - head_layers);
+      const size_t chunk = (head_bytes / head_layers + 127) & ~size_t(127);
+      const size_t off = chunk * part;
+      if (off < head_bytes)
+        prefetch_l2(reinterpret_cast<const char*>(p.head) + off,
+                    off + chunk <= head_bytes ? chunk : head_bytes - off, cta, P);
+    }
     {   // A: norm -> q|k|v -> rotary -> cache
       FusedParams f = {};
       f.W = L.w_qkv; f.M = p.B; f.N = qkv_rows; f.K = p.H; f.ldw = p.H;
@@ -137,7 +181,8 @@ decode_step_kernel(const StepParams p) {
       f.kc = L.kc; f.vc = L.vc; f.bt = p.bt; f.write_cache = L.write_cache; f.fault = p.fault;
       skinny_fused_tiles<NT, kProNorm, kEpiRope>(f, qkv_rows / kFuRows, gemv_smem, cta, P, false);
     }
-    grid_barrier(p.barrier, ++done * P, p.fault);
+    grid_barrier(p.barrier, ++done * P, p.fault, true);
+    stamp();
     // B: attention
     for (int item = cta; item < n_items; item += P) {
       const int split = item % p.n_splits, rest = item / p.n_splits;
@@ -148,6 +193,11 @@ decode_step_kernel(const StepParams p) {
                                  rest / p.nkv, it_base);
     }
     grid_barrier(p.barrier, ++done * P, p.fault);
+    stamp();
+    if (l + 1 < p.n_layers) {                 // next layer's feed-forward matrices
+      prefetch_l2(p.layers[l + 1].w_gu, gu_bytes, cta, P);
+      prefetch_l2(p.layers[l + 1].w_down, down_bytes, cta, P);
+    }
     {   // C: h += attn · Wo^T
       FusedParams f = {};
       f.W = L.w_o; f.M = p.B; f.N = p.H; f.K = q_dim; f.ldw = q_dim;
@@ -156,6 +206,7 @@ decode_step_kernel(const StepParams p) {
                                                    cta, P, false);
     }
     grid_barrier(p.barrier, ++done * P, p.fault);
+    stamp();
     {   // D: norm -> gate|up -> SiLU·mul
       FusedParams f = {};
       f.W = L.w_gu; f.M = p.B; f.N = 2 * p.I; f.K = p.H; f.ldw = p.H;
@@ -164,6 +215,7 @@ decode_step_kernel(const StepParams p) {
       skinny_fused_tiles<NT, kProNorm, kEpiSilu>(f, (p.I + 7) / 8, gemv_smem, cta, P, false);
     }
     grid_barrier(p.barrier, ++done * P, p.fault);
+    stamp();
     {   // E: h += act · Wdown^T
       FusedParams f = {};
       f.W = L.w_down; f.M = p.B; f.N = p.H; f.K = p.I; f.ldw = p.I;
@@ -172,6 +224,7 @@ decode_step_kernel(const StepParams p) {
                                                    cta, P, false);
     }
     grid_barrier(p.barrier, ++done * P, p.fault);
+    stamp();
   }
   {   // final norm -> head at the wanted rows
     FusedParams f = {};
@@ -181,6 +234,8 @@ decode_step_kernel(const StepParams p) {
     skinny_fused_tiles<NT, kProNorm, kEpiPlain>(f, (p.V + kFuRows - 1) / kFuRows, gemv_smem, cta,
                                                 P, false);
   }
+  ++done;
+  stamp();
   // ---- the last CTA to leave resets the barrier for the next launch (every CTA has passed the
   // last barrier before it gets here, so nobody still reads the arrival counter)
   __syncthreads();
@@ -259,7 +314,7 @@ extern "C" int cretif_step_layer_fill(void* dst, const void* w_qkv, const void* 
 
 // ints: n_layers, B, H, I, nh, nkv, hd, gu_block, pairing, bt, window, n_splits, V, n_want
 // ptrs: layers, h, q, attn, act, part_o, part_ml, counters, tok_ids, tok_pos, tok_seq, seq_slot,
-//       cos, sin, embed, final_norm, head, want_rows, logits, barrier, fault
+//       cos, sin, embed, final_norm, head, want_rows, logits, barrier, fault, stamps (or null)
 extern "C" int cretif_decode_step(const int* ints, const float* floats, void* const* ptrs,
                                   int ctas, void* stream) {
   StepParams p = {};
@@ -276,6 +331,7 @@ extern "C" int cretif_decode_step(const int* ints, const float* floats, void* co
   p.final_norm = (const float*)ptrs[15]; p.head = (const __nv_bfloat16*)ptrs[16];
   p.want_rows = (const int*)ptrs[17]; p.logits = (float*)ptrs[18];
   p.barrier = (unsigned int*)ptrs[19]; p.fault = (unsigned int*)ptrs[20];
+  p.stamps = (unsigned long long*)ptrs[21];
   if (p.n_layers <= 0 || p.B <= 0 || p.B > 32 || p.n_want <= 0 || p.n_want > p.B ||
       p.H % 8 || p.I % 8 || p.H <= 0 || p.I <= 0 || p.nh <= 0 || p.nkv <= 0 || p.nh % p.nkv ||
       p.nh / p.nkv > 8 || p.hd % 16 || p.hd < 16 || p.hd > 128 || p.bt != kDmTile ||

@@ -131,19 +131,20 @@ def test_a_repeated_step_shape_is_replayed_as_a_graph(model_dirs, plain_logits, 
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_the_whole_step_kernel_equals_the_kernels_of_the_parts(engines, plain_logits, name):
-    """Decode steps of few sequences run as one persistent launch; switched off, the same steps
-    run through the parts' kernels.  Both are compared with the plain model and each other."""
+    """Decode steps of few sequences can run as one persistent launch (switched on here); by
+    default they run through the parts' kernels.  Both are compared with the plain model and
+    with each other."""
     from cretif_b200.engine import step_kernel
     eng = engines(name, "bfloat16")
     assert eng.model.step_kernel.ok, eng.model.step_kernel.reason
     reqs = [tiny.tokens(name, n + 20, 60 + i) for i, n in enumerate(LENGTHS[name][:4])]
     prompts = [len(r) - 20 for r in reqs]
-    with_kernel = run_batch(eng, reqs, prompts)
-    step_kernel.enable(False)
+    without = run_batch(eng, reqs, prompts)
+    step_kernel.enable(True)
     try:
-        without = run_batch(eng, reqs, prompts)
+        with_kernel = run_batch(eng, reqs, prompts)
     finally:
-        step_kernel.enable(True)
+        step_kernel.enable(False)
     for r, a, b in zip(reqs, with_kernel, without):
         want = plain_logits(name, r)
         assert rel_err(a, want) <= TOL["bfloat16"] and rel_err(b, want) <= TOL["bfloat16"]

@@ -48,12 +48,11 @@ template <int PRO, int EPI>
 static int dispatch_nt(const FusedParams& p, int tiles, cudaStream_t st) {
   if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
   if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
-  if (p.M <= 32) return launch_fused<4, PRO, EPI>(p, tiles, st);
-  return launch_fused<8, PRO, EPI>(p, tiles, st);
+  return launch_fused<4, PRO, EPI>(p, tiles, st);      // up to 32 rows
 }
 
 static bool common_ok(const FusedParams& p) {
-  return p.M > 0 && p.M <= 64 && p.K > 0 && p.K % 8 == 0 && p.ldw % 8 == 0 && p.ldw >= p.K &&
+  return p.M > 0 && p.M <= 32 && p.K > 0 && p.K % 8 == 0 && p.ldw % 8 == 0 && p.ldw >= p.K &&
          (((uintptr_t)p.W) & 15) == 0;
 }
 
@@ -124,6 +123,7 @@ extern "C" int cretif_set_dependent_launch(int on) {
 }
 
 extern "C" int cretif_fused_smem_ok(int M, int K, int norm_prologue) {
-  const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  if (M > 32) return 0;
+  const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
   return fused_smem(nt, norm_prologue ? kProNorm : kProPlain, M, K) <= 200 * 1024 ? 1 : 0;
 }

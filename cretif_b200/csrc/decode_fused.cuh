@@ -99,11 +99,56 @@ __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
   }
 }
 
+// What a tile's epilogue reads from memory besides the accumulator — the token's position,
+// its cache block and rotation, or the value it adds to — does not depend on the product.
+// It is asked for before the product runs, so that the epilogue does not wait for it.
+struct EpiAhead {
+  float old[2];        // plain, accumulate: the values to add to (two passes of 256 threads)
+  int pos, blk;        // rope
+  float cs, sn;
+};
+
+template <int EPI>
+__device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, EpiAhead& a) {
+  if (EPI == kEpiPlain) {
+    if (p.c_dt == kF32 && p.accumulate) {
+#pragma unroll
+      for (int it = 0; it < 2; ++it) {
+        const int i = threadIdx.x + it * kFuWarps * 32;
+        const int m = i / kFuRows, n = tile * kFuRows + (i - m * kFuRows);
+        a.old[it] = (m < p.M && n < p.N)
+                        ? __ldcg(reinterpret_cast<const float*>(p.C) + (size_t)m * p.ldc + n)
+                        : 0.f;
+      }
+    }
+  } else if (EPI == kEpiRope) {
+    const int i = threadIdx.x;
+    a.pos = 0; a.blk = -1; a.cs = 1.f; a.sn = 0.f;
+    if (i < 8 * p.M) {
+      const int m = i >> 3, pr = i & 7;
+      const int tiles_per_head = p.hd >> 4;
+      const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+      a.pos = p.tok_pos[m];
+      if (head >= p.nh && p.write_cache)
+        a.blk = p.table[(size_t)p.seq_slot[p.tok_seq[m]] * p.table_stride + a.pos / p.bt];
+      if (head < p.nh + p.nkv) {
+        const int j = t * 8 + pr;
+        a.cs = p.cos_t[(size_t)a.pos * (p.hd >> 1) + j];
+        a.sn = p.sin_t[(size_t)a.pos * (p.hd >> 1) + j];
+      }
+    }
+  }
+}
+
 template <int NT, int EPI>
 __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
-                                            float (*red)[kFuRows][8 * NT + 1]) {
+                                            float (*red)[kFuRows][8 * NT + 1],
+                                            const EpiAhead& ahead) {
   if (EPI == kEpiPlain) {
-    for (int i = threadIdx.x; i < kFuRows * p.M; i += kFuWarps * 32) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {         // 16 rows x up to 32 tokens = two passes at most
+      const int i = threadIdx.x + it * kFuWarps * 32;
+      if (i >= kFuRows * p.M) break;
       const int m = i / kFuRows, rr = i - m * kFuRows;
       const int n = tile * kFuRows + rr;
       if (n >= p.N) continue;
@@ -112,7 +157,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
       for (int w = 0; w < kFuWarps; ++w) sum += red[w][rr][m];
       if (p.c_dt == kF32) {
         float* out = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n;
-        if (p.accumulate) sum += __ldcg(out);
+        if (p.accumulate) sum += ahead.old[it];
         *out = sum;
       } else {
         reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum);
@@ -135,12 +180,11 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
       } else {
         const int tiles_per_head = p.hd >> 4;
         const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
-        const int pos = p.tok_pos[m];
+        const int pos = ahead.pos;
         size_t cache_row = 0;
         bool cache_ok = false;
         if (head >= p.nh && p.write_cache) {
-          const int slot = p.seq_slot[p.tok_seq[m]];
-          const int blk = p.table[(size_t)slot * p.table_stride + pos / p.bt];
+          const int blk = ahead.blk;
           if (blk < 0) atomicOr(p.fault, kFaultBlockTable);
           else {
             cache_ok = true;
@@ -160,8 +204,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
         // the unfused path stores q and k as bfloat16 before rotating them
         const float x0 = __bfloat162float(__float2bfloat16_rn(s0));
         const float x1 = __bfloat162float(__float2bfloat16_rn(s1));
-        const float cs = p.cos_t[(size_t)pos * (p.hd >> 1) + j];
-        const float sn = p.sin_t[(size_t)pos * (p.hd >> 1) + j];
+        const float cs = ahead.cs, sn = ahead.sn;
         const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
         const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
         if (head < p.nh) {
@@ -283,6 +326,8 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   }
 
   for (; tile < n_tiles; tile += tile_stride) {
+    EpiAhead ahead;
+    epi_prefetch<EPI>(p, tile, ahead);
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t)
@@ -337,7 +382,7 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
       red[warp][r + 8][t * 8 + 2 * c + 1] = acc[t][3];
     }
     __syncthreads();
-    finish_tile<NT, EPI>(p, tile, red);
+    finish_tile<NT, EPI>(p, tile, red, ahead);
     __syncthreads();
   }
 }

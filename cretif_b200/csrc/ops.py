@@ -365,7 +365,7 @@ def _decode_counters(device, n: int) -> torch.Tensor:
 def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:
     """Whether the fused kernel takes M rows of width K against w (``norm``: with the norm
     prologue, which keeps the normed rows in shared memory)."""
-    return (w.dtype == torch.bfloat16 and 0 < M <= 64 and K % 8 == 0 and w.stride(1) == 1
+    return (w.dtype == torch.bfloat16 and 0 < M <= 32 and K % 8 == 0 and w.stride(1) == 1
             and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
             and bool(lib().cretif_fused_smem_ok(M, K, int(norm))))
 

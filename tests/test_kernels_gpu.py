@@ -128,7 +128,7 @@ def _norm_bf16(h, w, eps, rows=None):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1000, 576), (5, 50, 104), (16, 333, 200),
-                                   (33, 96, 72), (64, 130, 576)])
+                                   (17, 96, 72), (32, 130, 576)])
 def test_fused_norm_linear_and_add(ops, M, N, K):
     eps = 1e-5
     h, nw = rnd(M + 3, K), rnd(K, seed=1) * 0.1 + 1

@@ -233,3 +233,25 @@ def test_trace_run_program(model_dirs, plain_models, tmp_path, dtype):
     assert rel_err(read(1), la[38:39]) <= tol
     assert rel_err(read(2), la[39:40]) <= tol
     assert rel_err(read(3), lc) <= tol
+
+
+def test_command_line(model_dirs, plain_models, tmp_path):
+    """python -m cretif_b200 <model> <prompt ids> <max_tokens>, and --dump-logits."""
+    cfg, w = plain_models["A"]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    run = lambda *a: subprocess.run([sys.executable, "-m", "cretif_b200", model_dirs["A"], *a],
+                                    capture_output=True, text=True, env=env, timeout=600, cwd=ROOT)
+    proc = run("5,17,3,9", "6", "--dtype", "float32")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    want = pl.greedy(cfg, w, [5, 17, 3, 9], 6, stop_ids={7})
+    assert f"generated ids: {want}" in proc.stdout and "tok/s" in proc.stdout
+    dump = tmp_path / "top.json"
+    proc = run("5 17 3 9", "--dump-logits", str(dump), "--dtype", "float32")
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    doc = json.loads(dump.read_text())
+    logits = pl.forward(cfg, w, [5, 17, 3, 9])[-1]
+    assert doc["num_input_tokens"] == 4 and doc["logits_position"] == 3 and doc["top_k"] == 20
+    assert doc["top_logits"][0]["token_id"] == int(torch.argmax(logits))
+    assert abs(doc["top_logits"][0]["logit_value"] - float(logits.max())) < 1e-4
+    bad = run("hello there")
+    assert bad.returncode != 0 and "token ids" in (bad.stderr + bad.stdout)

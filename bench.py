@@ -31,12 +31,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SMOLLM2_135M = {
-    "architectures": ["LlamaForCausalLM"], "hidden_size": 576, "num_hidden_layers": 30,
-    "num_attention_heads": 9, "num_key_value_heads": 3, "head_dim": 64,
-    "intermediate_size": 1536, "vocab_size": 49152, "rope_theta": 100000.0,
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192,
-}
+from cretif_b200.config.presets import preset as _preset  # noqa: E402
+
+SMOLLM2_135M = _preset("smollm2-135m")
+SIZES = {"135m": "smollm2-135m", "360m": "smollm2-360m", "1.7b": "smollm2-1.7b"}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -234,6 +232,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--size", default="135m", choices=sorted(SIZES),
+                    help="layer sizes: SmolLM2-135M (the headline), 360M or 1.7B")
     ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
                     help="run a few eager steps of one phase and print their time (for "
                          "profilers); no JSON line")
@@ -258,7 +258,7 @@ def main() -> int:
     from cretif_b200.engine import Engine
     from cretif_b200.weights.random_model import write_random_model
 
-    cfg = dict(SMOLLM2_135M)
+    cfg = _preset(SIZES[args.size])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
@@ -304,17 +304,17 @@ def main() -> int:
     e2e = run_e2e(engine, args.batch, min(steps, 512), PROMPT_LEN)
 
     line = {
-        "metric": "decode tokens/s (SmolLM2-135M sizes, random weights, batch 8, context "
-                  "2048->4096)",
+        "metric": f"decode tokens/s (SmolLM2-{args.size.upper()} sizes, random weights, batch "
+                  f"{args.batch}, context 2048->4096)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "SmolLM2-135M sizes (Llama)", "layers": layers,
+        "config": {"model": f"SmolLM2-{args.size.upper()} sizes (Llama)", "layers": layers,
                    "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
                    "heads": nh, "kv_heads": cfg["num_key_value_heads"], "head_dim": hd,
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "tied_head": True, "global_batch": args.batch, "prompt_len": PROMPT_LEN,
+                   "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch, "prompt_len": PROMPT_LEN,
                    "seq_len": CONTEXT, "mean_context_timed": mean_ctx, "parallelism": "none",
                    "weights": "random N(0,0.02), seed 1234", "cache_block_tokens": 64,
                    "l2": "weights+cache read per step exceed L2, no flush",

@@ -12,8 +12,9 @@ of its last position as JSON (:242-301; default file ``cuinfer_logits.json``).
 
 Added options: ``--temperature``, ``--top-k``, ``--seed`` (the reference's
 ``generate`` arguments, which its program leaves at their defaults), ``--dtype``,
-``--cache-tokens``, and ``--random-weights SEED`` with ``--config FILE``, which first
-writes a model folder with seeded random weights to ``model_dir``.
+``--cache-tokens``, ``--stop-ids``, and ``--random-weights SEED`` with ``--preset NAME`` or
+``--config FILE``, which first writes a model folder with seeded random weights to
+``model_dir``.
 """
 from __future__ import annotations
 
@@ -64,14 +65,25 @@ def main(argv=None) -> int:
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="write a model folder with random weights to MODEL first")
     ap.add_argument("--config", default=None, help="config.json to use with --random-weights")
+    ap.add_argument("--preset", default=None,
+                    help="named configuration to use with --random-weights (tiny-a, tiny-b, "
+                         "smollm2-135m, smollm2-360m, smollm2-1.7b)")
+    ap.add_argument("--stop-ids", default=None,
+                    help="comma-separated token ids that end generation (default: the model's "
+                         "eos_token_id)")
     args = ap.parse_args(argv)
 
     if args.random_weights is not None:
         from .weights.random_model import write_random_model
-        if not args.config:
-            raise SystemExit("--random-weights needs --config FILE (a config.json)")
-        with open(args.config, "r", encoding="utf-8") as f:
-            write_random_model(args.model, json.load(f), args.random_weights)
+        if args.preset:
+            from .config.presets import preset
+            raw = preset(args.preset)
+        elif args.config:
+            with open(args.config, "r", encoding="utf-8") as f:
+                raw = json.load(f)
+        else:
+            raise SystemExit("--random-weights needs --preset NAME or --config FILE")
+        write_random_model(args.model, raw, args.random_weights)
         print(f"wrote random weights (seed {args.random_weights}) to {args.model}")
 
     from .engine import Engine
@@ -116,8 +128,9 @@ def main(argv=None) -> int:
 
     torch.cuda.synchronize()
     t0 = time.time()
+    stops = None if args.stop_ids is None else [int(t) for t in args.stop_ids.split(",") if t]
     res = engine.generate([ids], max_tokens=args.max_tokens, temperature=args.temperature,
-                          top_k=args.top_k, seed=args.seed)[0]
+                          top_k=args.top_k, seed=args.seed, stop_ids=stops)[0]
     torch.cuda.synchronize()
     dt = time.time() - t0
     print(f"prompt ids: {ids}")

@@ -3,10 +3,11 @@ from .registry import (ConfigError, architecture_name, load_config, read_config_
                        register_architecture, registered_architectures, resolve_architecture)
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
+from .presets import PRESETS, preset
 
 __all__ = [
     "ConfigError", "architecture_name", "load_config", "read_config_json",
     "register_architecture", "registered_architectures", "resolve_architecture",
     "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
-    "LlamaConfig", "build_llama_spec", "llama_config_from_dict",
+    "LlamaConfig", "build_llama_spec", "llama_config_from_dict", "PRESETS", "preset",
 ]

@@ -5,7 +5,7 @@
 // Who needs it: code that runs where cudaMalloc is off limits — a plug-in inside a host
 // application that owns the whole device heap and hands out fixed buffers only, a hard
 // real-time loop that may not take the allocator's locks or its implicit synchronisation, or
-// a process started with a memory budget that is already spent on weights and cache.  Such a
+// a process whose device memory is already taken up by weights and cache.  Such a
 // caller can still provide the inputs and the output, but not the scratch memory that the
 // split-range decode attention needs for its partial results.  Here that scratch lives in a
 // fixed array inside the library.

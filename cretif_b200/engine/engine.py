@@ -13,8 +13,7 @@ of the context, :832-849) are made here on the host before anything is launched.
 from __future__ import annotations
 
 import collections
-import os
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import Dict, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch

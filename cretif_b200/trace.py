@@ -25,7 +25,6 @@ import os
 import sys
 from typing import Dict
 
-import numpy as np
 
 
 def replay(engine, lines, out_dir: str, report=print) -> int:

@@ -2,7 +2,7 @@
 
 Some users of the kernel library run where cudaMalloc is not an option: inside a host
 application that owns the device heap, in a real-time loop that must not touch the
-allocator, or with a memory budget already spent.  For them the library exports
+allocator, or with all device memory already taken.  For them the library exports
 ``cretif_attn_decode_noalloc``, whose scratch is a fixed 4 MiB array inside the library
 instead of caller-provided buffers.  This test calls it through its exported C symbol, as
 such a caller would, twice in a row with different inputs (the second call finds the first

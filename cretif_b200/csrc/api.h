@@ -96,7 +96,8 @@ int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const voi
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
                         const int* rows, float eps, const void* W, int ldw, void* C, int c_dt,
-                        int ldc, int accumulate, int M, int N, int K, void* stream);
+                        int ldc, int accumulate, int M, int N, int K, unsigned int* fault,
+                        void* stream);
 int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const void* Wqkv, int ldw,
                           void* Q, int ldq, const float* cos_t, const float* sin_t, int pairing,
                           int nh, int nkv, int hd, const int* tok_pos, const int* tok_seq,
@@ -104,10 +105,19 @@ int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const 
                           void* vc, int bt, int write_cache, int M, int K, unsigned int* fault,
                           void* stream);
 int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
-                              int ldw, void* act, int I, int gu_block, int M, int K, void* stream);
+                              int ldw, void* act, int I, int gu_block, int M, int K,
+                              unsigned int* fault, void* stream);
 int cretif_fused_smem_ok(int M, int K, int norm_prologue);
 // Programmatic dependent launch of the fused kernels on (default) or off; returns the old value.
 int cretif_set_dependent_launch(int on);
+// Matrices with at least k columns, or of at least min_bytes bytes (negative: unchanged), take
+// the shared-memory streaming variant (decode_stream.cuh); returns the old column threshold.
+int cretif_set_stream_min_k(int k, long long min_bytes);
+long long cretif_stream_min_bytes(void);
+// Depth of that variant's ring of stages (2..8); 0, the default, chooses per launch.  early
+// (>= 0; negative leaves it) is the number of stages whose weights are asked for before the
+// kernel waits for the one before it.  Returns the old depth.
+int cretif_set_stream_stages(int n, int early);
 
 // Causal attention for whole prompts on tcgen05 (bfloat16, head_dim a multiple of 16 up to
 // 128, 64-token cache blocks).  qkv rows hold the query heads first; sequence b brings the

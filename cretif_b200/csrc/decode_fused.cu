@@ -1,5 +1,5 @@
 // Host side of the fused decode projections; the kernels are in decode_fused.cuh.
-#include "decode_fused.cuh"
+#include "decode_stream.cuh"
 
 namespace cretif {
 
@@ -44,8 +44,81 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {
   return launch_status();
 }
 
+// Matrices at least this wide, or this large, stream through shared memory
+// (decode_stream.cuh); narrow small ones are latency and do better without the copy unit.
+static int g_stream_min_k = 768;
+static long long g_stream_min_bytes = 16LL << 20;
+// Depth of the streaming ring; 0: chosen per launch.
+static int g_stream_stages = 0;
+// Stages of weights asked for before the kernel waits for the kernel before it.
+static int g_stream_early = 1;
+
+template <int NT, int PRO, int EPI>
+static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // Depth of the ring.  With many tiles two CTAs share an SM if both fit (113 KB each), as
+  // deep as that allows; else, or with few tiles (a narrow output and a long K), one CTA per
+  // SM holds as many steps in flight as shared memory allows.
+  const int steps = (p.K + kStK - 1) / kStK;
+  constexpr size_t kHalfSm = 113 * 1024, kWholeSm = 200 * 1024;
+  int stages = kStMaxStages, per_sm = 1;
+  if (tiles > sm_count && stream_smem(NT, PRO, p.M, p.K, 3) <= kHalfSm) {
+    per_sm = 2;
+    while (stream_smem(NT, PRO, p.M, p.K, stages) > kHalfSm) --stages;
+  } else if (tiles <= sm_count && steps < stages) {
+    stages = steps < 3 ? 3 : steps;
+  }
+  if (g_stream_stages) stages = g_stream_stages;
+  while (stages > 2 && stream_smem(NT, PRO, p.M, p.K, stages) > kWholeSm) --stages;
+  const size_t smem = stream_smem(NT, PRO, p.M, p.K, stages);
+  if (smem > 200 * 1024) return launch_fused<NT, PRO, EPI>(p, tiles, st);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<NT, PRO, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  const int max_ctas = per_sm * sm_count;
+  const int grid = tiles < max_ctas ? tiles : max_ctas;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kStThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_dependent_launch;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int w_rows = EPI == kEpiPlain ? p.N : EPI == kEpiSilu ? 2 * p.I : (p.nh + 2 * p.nkv) * p.hd;
+  CUtensorMap map_w, map_x;
+  if (make_box_map_bf16(&map_w, p.W, w_rows, p.K, p.ldw, 8, kStBoxK, false))
+    return launch_fused<NT, PRO, EPI>(p, tiles, st);
+  if (PRO == kProPlain) {
+    if (make_box_map_bf16(&map_x, p.X, p.M, p.K, p.ldx, 8 * NT, kStBoxK, false))
+      return launch_fused<NT, PRO, EPI>(p, tiles, st);
+  } else {
+    map_x = map_w;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_stream_kernel<NT, PRO, EPI>, p, map_w, map_x,
+                                     tiles, stages, g_stream_early);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 template <int PRO, int EPI>
 static int dispatch_nt(const FusedParams& p, int tiles, cudaStream_t st) {
+  const long long w_bytes = 2LL * tiles * kFuRows * p.K;
+  if ((p.K >= g_stream_min_k || w_bytes >= g_stream_min_bytes) && p.M <= 16) {
+    if (p.M <= 8) return launch_stream<1, PRO, EPI>(p, tiles, st);
+    return launch_stream<2, PRO, EPI>(p, tiles, st);
+  }
   if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
   if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
   return launch_fused<4, PRO, EPI>(p, tiles, st);      // up to 32 rows
@@ -64,12 +137,12 @@ using namespace cretif;
 extern "C" int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
                                    const int* rows, float eps, const void* W, int ldw, void* C,
                                    int c_dt, int ldc, int accumulate, int M, int N, int K,
-                                   void* stream) {
+                                   unsigned int* fault, void* stream) {
   if (M <= 0 || N <= 0) return kOk;
   FusedParams p = {};
   p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K; p.ldw = ldw;
   p.X = (const __nv_bfloat16*)X; p.ldx = ldx; p.H = H; p.norm_w = norm_w; p.rows = rows;
-  p.eps = eps; p.C = C; p.ldc = ldc; p.c_dt = c_dt; p.accumulate = accumulate;
+  p.eps = eps; p.C = C; p.ldc = ldc; p.c_dt = c_dt; p.accumulate = accumulate; p.fault = fault;
   if (!common_ok(p) || ldc < N || (c_dt != kF32 && c_dt != kBF16) ||
       (c_dt == kBF16 && accumulate))
     return kBadArgument;
@@ -106,14 +179,30 @@ extern "C" int cretif_fused_qkv_rope(const float* H, const float* norm_w, float 
 // act = silu(norm(h) · Wg^T) * (norm(h) · Wu^T), Wgu = [Wg; Wu] stacked.
 extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps,
                                          const void* Wgu, int ldw, void* act, int I, int gu_block,
-                                         int M, int K, void* stream) {
+                                         int M, int K, unsigned int* fault, void* stream) {
   if (M <= 0) return kOk;
   FusedParams p = {};
   p.W = (const __nv_bfloat16*)Wgu; p.M = M; p.N = 2 * I; p.K = K; p.ldw = ldw;
-  p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I; p.gu_block = gu_block;
+  p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I; p.gu_block = gu_block; p.fault = fault;
   if (!common_ok(p) || !H || I <= 0 || gu_block < 0 || (gu_block && (I % gu_block || gu_block % 8)))
     return kBadArgument;
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
+}
+
+extern "C" int cretif_set_stream_min_k(int k, long long min_bytes) {
+  const int was = g_stream_min_k;
+  g_stream_min_k = k;
+  if (min_bytes >= 0) g_stream_min_bytes = min_bytes;
+  return was;
+}
+
+extern "C" long long cretif_stream_min_bytes(void) { return g_stream_min_bytes; }
+
+extern "C" int cretif_set_stream_stages(int n, int early) {
+  const int was = g_stream_stages;
+  g_stream_stages = n < 0 ? 0 : (n > kStMaxStages ? kStMaxStages : n);
+  if (early >= 0) g_stream_early = early;
+  return was;
 }
 
 extern "C" int cretif_set_dependent_launch(int on) {

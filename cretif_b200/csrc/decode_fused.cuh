@@ -220,6 +220,66 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
   }
 }
 
+// The norm prologue: x[m] = bf16(h[row m] * w * rsqrt(mean(h^2) + eps)) into shared memory, a
+// warp per token.  A row of up to 128 * REGS columns makes one trip from memory: the lane
+// keeps its REGS float4 in registers between the sum of squares and the scaling.
+template <int REGS>
+__device__ __forceinline__ void norm_rows_to_smem(const FusedParams& p, unsigned char* xs,
+                                                  int xs_stride, int warp, int lane) {
+  const int n4 = p.K >> 2;
+  const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+  for (int m = warp; m < p.M; m += kFuWarps) {
+    const float4* h4 = reinterpret_cast<const float4*>(p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K);
+    __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
+    if (n4 <= 32 * REGS) {
+      float4 v[REGS];
+      float ss = 0.f;
+#pragma unroll
+      for (int u = 0; u < REGS; ++u) {
+        const int i = u * 32 + lane;
+        v[u] = i < n4 ? __ldcg(h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < REGS; ++u)
+        ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll
+      for (int u = 0; u < REGS; ++u) {
+        const int i = u * 32 + lane;
+        if (i < n4) {
+          const float4 w = __ldg(w4 + i);
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * w.x * inv, v[u].y * w.y * inv);
+          __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * w.z * inv, v[u].w * w.w * inv);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+        }
+      }
+    } else {
+      float ss = 0.f;
+#pragma unroll 8
+      for (int i = lane; i < n4; i += 32) {
+        const float4 v = __ldcg(h4 + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll 4
+      for (int i = lane; i < n4; i += 32) {
+        const float4 v = __ldcg(h4 + i), w = __ldg(w4 + i);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * w.x * inv, v.y * w.y * inv);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * w.z * inv, v.w * w.w * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+      }
+    }
+  }
+}
+
 constexpr int kFuPre = 3;      // weight chunks per warp fetched ahead (covers K <= 768)
 
 template <int EPI>
@@ -272,56 +332,7 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   }
 
   if (PRO == kProNorm) {
-    const int n4 = p.K >> 2;
-    for (int m = warp; m < p.M; m += kFuWarps) {
-      const float4* h4 = reinterpret_cast<const float4*>(p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K);
-      const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
-      __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
-      if (n4 <= 256) {                       // the row fits in registers: one trip to memory
-        float4 v[8];
-        float ss = 0.f;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = u * 32 + lane;
-          v[u] = i < n4 ? __ldcg(h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)p.K + p.eps);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int i = u * 32 + lane;
-          if (i < n4) {
-            const float4 w = w4[i];
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * w.x * inv, v[u].y * w.y * inv);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * w.z * inv, v[u].w * w.w * inv);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
-          }
-        }
-      } else {
-        float ss = 0.f;
-        for (int i = lane; i < n4; i += 32) {
-          const float4 v = __ldcg(h4 + i);
-          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)p.K + p.eps);
-        for (int i = lane; i < n4; i += 32) {
-          const float4 v = __ldcg(h4 + i), w = w4[i];
-          __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * w.x * inv, v.y * w.y * inv);
-          __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * w.z * inv, v.w * w.w * inv);
-          uint2 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&lo);
-          pk.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
-        }
-      }
-    }
+    norm_rows_to_smem<8>(p, xs, xs_stride, warp, lane);
     __syncthreads();
   }
 

@@ -316,15 +316,16 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A [rows, cols] bf16 matrix with row stride ld (elements), tiles of box_rows x 64.
-// Encoding a map costs a few microseconds on the host, and weights, the cache and recycled
+// A [rows, cols] bf16 matrix with row stride ld (elements), boxes of box_rows x box_cols;
+// with the 128-byte swizzle a box is 64 columns wide.  Encoding a map costs a few microseconds on the host, and weights, the cache and recycled
 // activation buffers come back with the same address and shape, so recent maps are kept.
 struct MapKey {
   const void* base;
-  int rows, cols, ld, box_rows;
+  int rows, cols, ld, box_rows, box_cols;
+  bool swizzle;
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
-           box_rows == o.box_rows;
+           box_rows == o.box_rows && box_cols == o.box_cols && swizzle == o.swizzle;
   }
 };
 constexpr int kMapCacheSize = 1024;
@@ -333,11 +334,15 @@ static CUtensorMap g_map_vals[kMapCacheSize];
 static bool g_map_used[kMapCacheSize];
 static std::mutex g_map_mutex;
 
-int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
-                       int box_rows) {
-  const MapKey key = {base, rows, cols, ld, box_rows};
+int make_box_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows,
+                      int box_cols, bool swizzle) {
+  if (box_rows < 1 || box_rows > 256 || box_cols < 8 || box_cols > 256 ||
+      (swizzle && box_cols != 64))
+    return kBadArgument;
+  const MapKey key = {base, rows, cols, ld, box_rows, box_cols, swizzle};
   size_t hsh = (size_t)((uintptr_t)base >> 4) * 1000003u ^ (size_t)rows * 8191u ^
-               (size_t)cols * 131u ^ (size_t)ld * 31u ^ (size_t)box_rows;
+               (size_t)cols * 131u ^ (size_t)ld * 31u ^ (size_t)box_rows ^
+               (size_t)box_cols * 524287u ^ (size_t)swizzle;
   const int at = (int)(hsh % kMapCacheSize);
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -350,10 +355,11 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
   if (!fn) return kBadArgument;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1u, 1u};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return kBadArgument;
   std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -361,6 +367,11 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
   g_map_vals[at] = *map;
   g_map_used[at] = true;
   return 0;
+}
+
+int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
+                       int box_rows) {
+  return make_box_map_bf16(map, base, rows, cols, ld, box_rows, 64, true);
 }
 
 template <int BN, int EPI, typename TC>

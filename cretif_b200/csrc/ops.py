@@ -8,6 +8,7 @@ library, or with a tensor that is not on a CUDA device, the call fails.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -34,6 +35,13 @@ def lib():
         L = load_library()
         L.cretif_uniform01.restype = ctypes.c_float
         L.cretif_uniform01.argtypes = [ctypes.c_ulonglong, ctypes.c_longlong, ctypes.c_int]
+        tune = os.environ.get("CRETIF_STREAM_MIN_K")       # tuning knob, see set_stream_min_k
+        if tune:
+            L.cretif_set_stream_min_k(int(tune), ctypes.c_longlong(
+                int(os.environ.get("CRETIF_STREAM_MIN_BYTES", "-1"))))
+        tune = os.environ.get("CRETIF_STREAM_STAGES")
+        if tune:
+            L.cretif_set_stream_stages(int(tune), int(os.environ.get("CRETIF_STREAM_EARLY", "-1")))
         _lib = L
     return _lib
 
@@ -370,6 +378,26 @@ def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:
             and bool(lib().cretif_fused_smem_ok(M, K, int(norm))))
 
 
+def set_stream_min_k(k: int, min_bytes: int = -1) -> int:
+    """The fused product streams weights through shared memory for matrices of at least k
+    columns or (if not negative) at least min_bytes bytes; returns the old column count."""
+    return int(lib().cretif_set_stream_min_k(int(k), ctypes.c_longlong(int(min_bytes))))
+
+
+def stream_min_bytes() -> int:
+    """The size threshold of set_stream_min_k."""
+    fn = lib().cretif_stream_min_bytes
+    fn.restype = ctypes.c_longlong
+    return int(fn())
+
+
+def set_stream_stages(n: int, early: int = -1) -> int:
+    """Depth of the streaming variant's ring (2..8; 0: chosen per launch) and, if not
+    negative, how many stages of weights it asks for before waiting for the kernel before
+    it; returns the old depth."""
+    return int(lib().cretif_set_stream_stages(int(n), int(early)))
+
+
 def set_dependent_launch(on: bool) -> bool:
     """Programmatic dependent launch of the fused kernels on or off; returns the old setting."""
     return bool(lib().cretif_set_dependent_launch(int(on)))
@@ -386,7 +414,8 @@ def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool
         raise KernelError("fused_norm_linear: shapes do not fit")
     _check(lib().cretif_fused_linear(None, 0, _p(h), _p(norm_w), _p(rows), ctypes.c_float(eps),
                                      _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
-                                     int(accumulate), M, N, K, _stream()), "fused_norm_linear")
+                                     int(accumulate), M, N, K, _p(fault_word(h.device)),
+                                     _stream()), "fused_norm_linear")
 
 
 def fused_linear_add(x, w, h) -> None:
@@ -399,7 +428,7 @@ def fused_linear_add(x, w, h) -> None:
         raise KernelError("fused_linear_add: shapes do not fit")
     _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
                                      _p(w), _rows(w, "w"), _p(h), F32, _rows(h, "h"), 1, M, N, K,
-                                     _stream()), "fused_linear_add")
+                                     _p(fault_word(h.device)), _stream()), "fused_linear_add")
 
 
 def fused_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, cos, sin, pairing: int, nh: int,
@@ -431,7 +460,8 @@ def fused_gate_up_silu(h, norm_w, eps: float, w_gu, act, block: int = 0) -> None
         raise KernelError("fused_gate_up_silu: shapes do not fit")
     _check(lib().cretif_fused_gate_up_silu(_p(h), _p(norm_w), ctypes.c_float(eps), _p(w_gu),
                                            _rows(w_gu, "w_gu"), _p(act), I, block, M, K,
-                                           _stream()), "fused_gate_up_silu")
+                                           _p(fault_word(h.device)), _stream()),
+           "fused_gate_up_silu")
 
 
 def gemm_tc_silu(x, w_gu, act) -> None:

@@ -118,6 +118,18 @@ def test_gemm_tc(ops, M, N, K, bn):
 
 
 # ------------------------------------------------------------------ fused decode projections
+@pytest.fixture(params=[(1 << 20, 1 << 40), (64, 0)], ids=["registers", "streamed"])
+def fused_variant(request, ops):
+    """The fused product has two bodies: weights through registers (narrow, small matrices)
+    and through a shared-memory ring (wide or large ones).  Every fused test runs with
+    thresholds that keep the test matrices in registers, and with ones that send them
+    through the ring."""
+    old_bytes = ops.stream_min_bytes()
+    old_k = ops.set_stream_min_k(*request.param)
+    yield request.param[0]
+    ops.set_stream_min_k(old_k, old_bytes)
+
+
 def _norm_bf16(h, w, eps, rows=None):
     """bf16(rmsnorm(h[rows])) as the fused prologue stores it, in float64."""
     x = h.double().cpu()
@@ -128,18 +140,23 @@ def _norm_bf16(h, w, eps, rows=None):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1000, 576), (5, 50, 104), (16, 333, 200),
-                                   (17, 96, 72), (32, 130, 576)])
-def test_fused_norm_linear_and_add(ops, M, N, K):
+                                   (17, 96, 72), (32, 130, 576), (8, 200, 2048), (3, 64, 1544),
+                                   (16, 48, 8192), (13, 77, 3000)])
+def test_fused_norm_linear_and_add(ops, fused_variant, M, N, K):
     eps = 1e-5
     h, nw = rnd(M + 3, K), rnd(K, seed=1) * 0.1 + 1
     w = rnd(N, K, dtype=torch.bfloat16, seed=2)
-    assert ops.fused_supported(M, K, w)
     out = torch.empty(M, N, device=DEV)
-    ops.fused_norm_linear(h[:M].contiguous(), nw, eps, w, out)
-    close(out, _norm_bf16(h[:M], nw, eps) @ w.double().cpu().T, 3e-3)
-    rows = torch.tensor([(3 * i + 2) % (M + 3) for i in range(M)], dtype=torch.int32, device=DEV)
-    ops.fused_norm_linear(h, nw, eps, w, out, rows=rows)
-    close(out, _norm_bf16(h, nw, eps, rows.cpu().long()) @ w.double().cpu().T, 3e-3)
+    if ops.fused_supported(M, K, w):          # the normed rows must fit in shared memory
+        ops.fused_norm_linear(h[:M].contiguous(), nw, eps, w, out)
+        close(out, _norm_bf16(h[:M], nw, eps) @ w.double().cpu().T, 3e-3)
+        rows = torch.tensor([(3 * i + 2) % (M + 3) for i in range(M)], dtype=torch.int32,
+                            device=DEV)
+        ops.fused_norm_linear(h, nw, eps, w, out, rows=rows)
+        close(out, _norm_bf16(h, nw, eps, rows.cpu().long()) @ w.double().cpu().T, 3e-3)
+    else:
+        assert (M, K) == (16, 8192)
+    assert ops.fused_supported(M, K, w, norm=False)
     x = rnd(M, K, dtype=torch.bfloat16, seed=4)
     base = rnd(M, N, seed=5)
     acc = base.clone()
@@ -147,8 +164,9 @@ def test_fused_norm_linear_and_add(ops, M, N, K):
     close(acc, base.double().cpu() + x.double().cpu() @ w.double().cpu().T, 1e-5)
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 1536, 576), (7, 173, 104), (20, 256, 96)])
-def test_fused_gate_up_silu_equals_the_separate_kernels(ops, M, I, K):
+@pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 1536, 576), (7, 173, 104), (20, 256, 96),
+                                   (8, 512, 2048), (12, 72, 1032)])
+def test_fused_gate_up_silu_equals_the_separate_kernels(ops, fused_variant, M, I, K):
     eps = 1e-6
     h, nw = rnd(M, K), rnd(K, seed=1) * 0.1 + 1
     w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
@@ -169,8 +187,8 @@ def test_fused_gate_up_silu_equals_the_separate_kernels(ops, M, I, K):
 
 @pytest.mark.parametrize("pairing", [0, 1])
 @pytest.mark.parametrize("nh,nkv,hd,K", [(4, 2, 16, 64), (9, 3, 64, 576), (3, 1, 32, 96),
-                                         (5, 5, 48, 104)])
-def test_fused_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K):
+                                         (5, 5, 48, 104), (4, 4, 64, 2048)])
+def test_fused_qkv_rope_equals_the_separate_kernels(ops, fused_variant, pairing, nh, nkv, hd, K):
     eps, theta, P = 1e-5, 10000.0, 256
     lens = [5, 70, 130]
     j = torch.arange(hd // 2, dtype=torch.float64)

@@ -84,7 +84,9 @@ int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, const void* k
                        unsigned int* fault, void* stream);
 
 // The same operation on the tensor cores (mma.sync, TMA-swizzled tiles), head_dim <= 128;
-// same scratch and counters.  n_blocks is the cache's block count.
+// same scratch and counters.  n_blocks is the cache's block count.  With part_o null and at
+// most 8 ranges, the ranges of a sequence form a thread-block cluster and are merged through
+// distributed shared memory: no scratch, no counters.
 int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const void* kc,
                            const void* vc, long long n_blocks, const int* table, int table_stride,
                            const int* tok_pos, const int* tok_seq, const int* seq_slot, int nh,

@@ -7,34 +7,61 @@
 
 namespace cretif {
 
-template <int HD16>
-static size_t dm_smem_bytes() {
-  return dm_smem_core<HD16>() + 1024;
-}
+// Tuning aid: a device buffer of 10 x 16 timestamps the next launches fill (see the kernel).
+static unsigned long long* g_dm_stamps = nullptr;
 
 template <int HD16>
+static size_t dm_smem_bytes(bool cluster) {
+  return dm_smem_core<HD16>(cluster) + 1024;
+}
+
+template <int HD16, bool CLUSTER>
 static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int ldq,
                      const int* table, int table_stride, const int* tok_pos, const int* tok_seq,
                      const int* seq_slot, int nh, int nkv, float scale_log2, int window,
                      float* part_o, float* part_ml, void* out, int ldo, int* counters,
                      unsigned int* fault, dim3 grid, cudaStream_t st) {
-  const size_t smem = dm_smem_bytes<HD16>();
+  const size_t smem = dm_smem_bytes<HD16>(CLUSTER);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD16>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD16, CLUSTER>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attn_decode_mma_kernel<HD16><<<grid, kDmThreads, smem, st>>>(
-      mk, mv, (const __nv_bfloat16*)q, ldq, table, table_stride, tok_pos, tok_seq, seq_slot, nh,
-      nkv, scale_log2, window, part_o, part_ml, (__nv_bfloat16*)out, ldo, counters, fault);
-  return launch_status();
+  // Launched as a programmatic dependent of the kernel before it: set-up, the block table and
+  // the first cache tiles run under that kernel's tail.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kDmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (CLUSTER) {                 // the ranges of one (sequence, kv head) are one cluster
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = grid.x;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e = cudaLaunchKernelEx(
+      &cfg, attn_decode_mma_kernel<HD16, CLUSTER>, mk, mv, (const __nv_bfloat16*)q, ldq, table,
+      table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,
+      (__nv_bfloat16*)out, ldo, counters, fault, g_dm_stamps);
+  return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 }  // namespace cretif
 
 using namespace cretif;
+
+extern "C" void cretif_attn_decode_stamps(unsigned long long* device_buffer) {
+  g_dm_stamps = device_buffer;
+}
 
 extern "C" int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const void* kc,
                                       const void* vc, long long n_blocks, const int* table,
@@ -57,11 +84,18 @@ extern "C" int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_splits, nkv, B);
   cudaStream_t st = (cudaStream_t)stream;
+  // Without scratch the ranges are merged inside a cluster (at most eight of them).
+  const bool cluster = part_o == nullptr;
+  if (cluster ? n_splits > kDmClusterMax : (!part_ml || !counters)) return kBadArgument;
 #define CRETIF_DM(N)                                                                          \
   case N:                                                                                     \
-    return launch_dm<N>(mk, mv, q, ldq, table, table_stride, tok_pos, tok_seq, seq_slot, nh,  \
-                        nkv, scale_log2, window, part_o, part_ml, out, ldo, counters, fault,  \
-                        grid, st)
+    return cluster                                                                            \
+               ? launch_dm<N, true>(mk, mv, q, ldq, table, table_stride, tok_pos, tok_seq,    \
+                                    seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,   \
+                                    out, ldo, counters, fault, grid, st)                      \
+               : launch_dm<N, false>(mk, mv, q, ldq, table, table_stride, tok_pos, tok_seq,   \
+                                     seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,  \
+                                     out, ldo, counters, fault, grid, st)
   switch (hd / 16) {
     CRETIF_DM(1); CRETIF_DM(2); CRETIF_DM(3); CRETIF_DM(4);
     CRETIF_DM(5); CRETIF_DM(6); CRETIF_DM(7); CRETIF_DM(8);

@@ -7,8 +7,14 @@
 // running maximum, sum and output for all query heads of the key/value head: the heads are
 // the rows of m16n8k16 products (S = Q K^T, then O += P V with P taken straight from the
 // accumulator registers), so the warps never synchronise inside the loop; their four partial
-// results are merged once at the end of the CTA.  Ranges of one sequence are merged by the
-// CTA that finishes last, as in attn_decode.cu (same scratch, same counters).
+// results are merged once at the end of the CTA.  Ranges of one sequence are merged in one of
+// two ways.  Up to eight ranges form a thread-block cluster: every CTA owns a share of the
+// (head, dim) outputs, each warp stores its partial results straight into the owners' shared
+// memory (distributed shared memory), and after one cluster barrier every CTA finishes its
+// share from its own memory: no trip through global memory, which costs most of the kernel's
+// time at short contexts.  More ranges (a long context with few sequences) go through global
+// scratch and are merged by the CTA that finishes last, as in attn_decode.cu (same scratch,
+// same counters).
 //
 // The reference walks positions serially with one block per head (src/attention.cu:410-494).
 #pragma once
@@ -30,6 +36,7 @@ constexpr int kDmWarps = 4;                 // consumer warps
 constexpr int kDmThreads = (kDmWarps + 1) * 32;
 constexpr int kDmTile = 64;
 constexpr int kDmStages = 3;
+constexpr int kDmClusterMax = 8;            // ranges merged inside one cluster (portable size)
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -60,7 +67,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // initialised once per kernel by dm_init(); `it_base` counts the tiles this CTA has pushed
 // through them so far, so that stage and phase carry on from item to item.
 // HD16 = head_dim / 16 (compile time: sizes the register arrays).
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Store into the shared memory of CTA `rank` of this cluster, at the address that
+// `local_addr` has in this CTA's.
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+// Floats of the region in which the warps' partial results meet (later reused for the weights
+// of the merge over ranges).
 template <int HD16>
+__host__ __device__ constexpr size_t dm_mrg_floats() {
+  constexpr int hd = HD16 * 16;
+  const size_t mrg = (size_t)(2 * kDmWarps * 8 + kDmWarps * 8 * hd);
+  const size_t wts = (size_t)(8 * kDmTile + 8);
+  return mrg > wts ? mrg : wts;
+}
+
+template <int HD16, bool CLUSTER = false>
 __device__ __forceinline__ void attn_decode_mma_item(
     unsigned char* smem, const CUtensorMap* map_k, const CUtensorMap* map_v,
     const __nv_bfloat16* __restrict__ q, int ldq, const int* __restrict__ table, int table_stride,
@@ -68,8 +99,20 @@ __device__ __forceinline__ void attn_decode_mma_item(
     const int* __restrict__ seq_slot, int nh, int nkv, float scale_log2, int window,
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
-    int n_splits, int kvh, int b, uint32_t& it_base) {
+    int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr) {
   constexpr int hd = HD16 * 16;
+  // Tuning aid: with a buffer given, lane 0 of every warp of the first CTA notes the time at
+  // which it passes each phase ([warp][16]); the CTA that merges notes its own at [8][..].
+  const bool stamping = stamps && split == 0 && kvh == 0 && b == 0;
+  auto stamp = [&](int row, int i) {
+    if ((threadIdx.x & 31) == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      stamps[row * 16 + i] = t;
+    }
+  };
+#define DM_STAMP(i) do { if (stamping) stamp(threadIdx.x >> 5, i); } while (0)
+  DM_STAMP(0);
   constexpr int kSub = (hd + 63) / 64;                 // 64-wide column groups of a tile
   constexpr int kTileBytes = kSub * kDmTile * 128;     // one of K or V
   unsigned char* ktiles = smem;
@@ -79,8 +122,22 @@ __device__ __forceinline__ void attn_decode_mma_item(
   volatile int* abort = reinterpret_cast<volatile int*>(empty + kDmStages);
   int* is_last = const_cast<int*>(abort) + 1;
   float* mrg = reinterpret_cast<float*>(const_cast<int*>(abort) + 4);   // warps' partials
+  // cluster merge: what the warps of all ranges send this CTA: [range][warp][8 heads]{m, l},
+  // then [range][warp][share] o
+  float* recv_ml = mrg + dm_mrg_floats<HD16>();
+  float* recv_o = recv_ml + kDmClusterMax * kDmWarps * 8 * 2;
 
   const int g = nh / nkv;
+  const int share = (g * hd + n_splits - 1) / n_splits;   // outputs a CTA of the cluster owns
+  // n / share and n / g for n < 65536 as a multiplication: a division in the merge's short
+  // dependent chains costs more than the stores it addresses
+  // (floor(n / d) = umulhi(n, ceil(2^32 / d)) for n, d < 65536, d > 1; the factor of 1 does
+  // not fit 32 bits)
+  const uint32_t share_magic = 0xffffffffu / (uint32_t)share + 1u;
+  const uint32_t g_magic = 0xffffffffu / (uint32_t)g + 1u;
+  auto div_by = [](int n, int d, uint32_t magic) {
+    return d == 1 ? n : (int)__umulhi((uint32_t)n, magic);
+  };
   const int nthreads = blockDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = tok_pos[b];
@@ -88,9 +145,11 @@ __device__ __forceinline__ void attn_decode_mma_item(
   const int* tab = table + (size_t)slot * table_stride;
   const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
   const int first_tile = first_key / kDmTile, n_tiles = pos / kDmTile + 1;
-  const int per = (n_tiles - first_tile + n_splits - 1) / n_splits;
-  const int t_begin = first_tile + split * per, t_end = min(n_tiles, t_begin + per);
-  const int my_tiles = max(0, t_end - t_begin);
+  // the tiles are dealt out evenly: the first (tiles % ranges) ranges take one more
+  const int span = n_tiles - first_tile, per = span / n_splits, extra = span - per * n_splits;
+  const int t_begin = first_tile + split * per + min(split, extra);
+  const int my_tiles = per + (split < extra ? 1 : 0);
+  if (stamping && my_tiles >= 0) stamp(threadIdx.x >> 5, 1);
 
   __syncthreads();                      // the previous item's readers of `mrg` are done
 
@@ -100,29 +159,54 @@ __device__ __forceinline__ void attn_decode_mma_item(
   float* mrg_o = mrg + 2 * kDmWarps * 8;
 
   if (warp > kDmWarps) {
-    // not needed for this item
+    if (CLUSTER) cluster_wait();          // not needed for this item
   } else if (warp == kDmWarps) {
     // ---------------- producer
-    if (lane == 0) {
-      for (int i = 0; i < my_tiles; ++i) {
+    // The block table, the positions and every cache tile but the one that holds the step's
+    // own token were written before this step's kernels began: the first tiles are asked for
+    // before the kernel waits for the one before it (programmatic dependent launch), the
+    // tile of the new token after.  Block ids are read 32 at a time.
+    bool waited = false;
+    for (int i0 = 0; i0 < my_tiles; i0 += 32) {
+      const int mine = i0 + lane < my_tiles ? tab[t_begin + i0 + lane] : 0;
+      const int n = min(32, my_tiles - i0);
+      if (stamping && mine >= -1) stamp(threadIdx.x >> 5, 2);
+      bool go = true;
+      for (int j = 0; j < n && go; ++j) {
+        const int i = i0 + j;
+        const int blk = __shfl_sync(0xffffffffu, mine, j);
         const uint32_t it = it_base + i;
         const int s = it % kDmStages;
-        if (it >= kDmStages && !tc::mbar_wait(&empty[s], (uint32_t)((it / kDmStages - 1) & 1), abort))
-          break;
-        const int blk = tab[t_begin + i];
-        if (blk < 0) atomicOr(fault, kFaultBlockTable);
-        const int row = (max(blk, 0) * nkv + kvh) * kDmTile;
-        tc::mbar_expect_tx(&full[s], 2u * kTileBytes);
-#pragma unroll
-        for (int sub = 0; sub < kSub; ++sub) {
-          tc::tma_load_2d(ktiles + s * kTileBytes + sub * kDmTile * 128, map_k, 64 * sub, row, &full[s]);
-          tc::tma_load_2d(vtiles + s * kTileBytes + sub * kDmTile * 128, map_v, 64 * sub, row, &full[s]);
+        if (!waited && (i >= kDmStages || t_begin + i == n_tiles - 1)) {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          waited = true;
         }
+        if (lane == 0) {
+          if (it >= kDmStages && !tc::mbar_wait(&empty[s], (uint32_t)((it / kDmStages - 1) & 1), abort)) {
+            go = false;
+          } else {
+            if (blk < 0) atomicOr(fault, kFaultBlockTable);
+            const int row = (max(blk, 0) * nkv + kvh) * kDmTile;
+            tc::mbar_expect_tx(&full[s], 2u * kTileBytes);
+#pragma unroll
+            for (int sub = 0; sub < kSub; ++sub) {
+              tc::tma_load_2d(ktiles + s * kTileBytes + sub * kDmTile * 128, map_k, 64 * sub, row, &full[s]);
+              tc::tma_load_2d(vtiles + s * kTileBytes + sub * kDmTile * 128, map_v, 64 * sub, row, &full[s]);
+            }
+          }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (i == 0) DM_STAMP(3);
       }
+      if (!go) break;
     }
+    DM_STAMP(4);
+    if (CLUSTER) cluster_wait();
   } else {
     // ---------------- consumers: warp w owns keys 16w .. 16w+15 of every tile
     const int r = lane >> 2, c = lane & 3;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // q comes from the kernel before
+    DM_STAMP(2);
     // Q as the A operand: rows = heads of this kv head (rows >= g are zero)
     uint32_t qa[HD16][2];
     {
@@ -133,6 +217,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
         qa[ks][1] = r < g ? __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * c)) : 0u;
       }
     }
+    if (stamping && qa[0][0] != 0x7fc07fc1u) stamp(threadIdx.x >> 5, 3);
     float o[HD16 * 2][2];                 // [8-dim tile][2 dims] of row r
 #pragma unroll
     for (int i = 0; i < HD16 * 2; ++i) o[i][0] = o[i][1] = 0.f;
@@ -143,6 +228,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
       const uint32_t it = it_base + i;
       const int s = it % kDmStages;
       if (!tc::mbar_wait(&full[s], (uint32_t)((it / kDmStages) & 1), abort)) { ok = false; break; }
+      if (i == 0) DM_STAMP(4);
       const uint32_t kbase = tc::smem_u32(ktiles + s * kTileBytes);
       const uint32_t vbase = tc::smem_u32(vtiles + s * kTileBytes);
       // ---- S = Q K^T for this warp's 16 keys
@@ -210,6 +296,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
       if (lane == 0) tc::mbar_arrive(&empty[s]);
     }
     (void)ok;
+    DM_STAMP(5);
     // ---- this warp's result for the merge
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
@@ -221,10 +308,82 @@ __device__ __forceinline__ void attn_decode_mma_item(
         mrg_o[((size_t)warp * 8 + r) * hd + i * 8 + 2 * c + 1] = o[i][1];
       }
     }
+    if (CLUSTER) {
+      // Every CTA of the cluster runs by now (they all arrived at the kernel's start): send
+      // m and l to all of them and each output's partial sum to the CTA that owns it.  The
+      // warp reads its results back from shared memory so that a store instruction carries
+      // 32 consecutive outputs to one owner (two at a border): a remote store costs per
+      // destination segment, and straight from the accumulator layout it had eight.
+      DM_STAMP(10);
+      cluster_wait();
+      __syncwarp();
+      DM_STAMP(11);
+      const uint32_t a_ml = tc::smem_u32(recv_ml + (size_t)(split * kDmWarps + warp) * 8 * 2);
+      const uint32_t a_o = tc::smem_u32(recv_o + (size_t)(split * kDmWarps + warp) * share);
+      for (int p = lane; p < n_splits * g; p += 32) {
+        const int rank = div_by(p, g, g_magic), row = p - rank * g;
+        st_cluster_f32(a_ml + row * 8, rank, mrg_m[warp * 8 + row]);
+        st_cluster_f32(a_ml + row * 8 + 4, rank, mrg_l[warp * 8 + row]);
+      }
+#pragma unroll 4
+      for (int idx = lane; idx < g * hd; idx += 32) {
+        const int owner = div_by(idx, share, share_magic);
+        st_cluster_f32(a_o + (idx - owner * share) * 4, owner, mrg_o[(size_t)warp * 8 * hd + idx]);
+      }
+      DM_STAMP(12);
+    }
   }
   it_base += (uint32_t)my_tiles;
   __syncthreads();
+  DM_STAMP(6);
   if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
+
+  if (CLUSTER) {
+    // ---- the ranges are the CTAs of one cluster; after the barrier this CTA holds what all
+    // warps of all ranges sent for its share of the outputs.  (A range without tiles sent
+    // m = -inf, l = 0.)  Nothing remote is touched after the barrier, so a CTA may leave
+    // as soon as it is done.
+    cluster_arrive();
+    cluster_wait();
+    DM_STAMP(7);
+    // Four lanes share an output, one per source warp; they meet by shuffles.
+    const int total = g * hd, w = threadIdx.x & 3;
+    for (int p0 = 0; p0 < share * kDmWarps; p0 += nthreads) {
+      const int t = (p0 + threadIdx.x) >> 2, i = split * share + t;
+      const bool live = t < share && i < total;
+      const int j = live ? i / hd : 0;
+      // all loads up front (at most kDmClusterMax ranges)
+      float mw[kDmClusterMax], lw[kDmClusterMax], ow[kDmClusterMax];
+#pragma unroll
+      for (int rank = 0; rank < kDmClusterMax; ++rank) {
+        const bool in = live && rank < n_splits;
+        const int sw = rank * kDmWarps + w;
+        mw[rank] = in ? recv_ml[(sw * 8 + j) * 2] : -INFINITY;
+        lw[rank] = in ? recv_ml[(sw * 8 + j) * 2 + 1] : 0.f;
+        ow[rank] = in ? recv_o[(size_t)sw * share + t] : 0.f;
+      }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int rank = 0; rank < kDmClusterMax; ++rank) mm = fmaxf(mm, mw[rank]);
+      mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
+      mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
+      float acc = 0.f, ll = 0.f;
+#pragma unroll
+      for (int rank = 0; rank < kDmClusterMax; ++rank) {
+        const float f = (mw[rank] == -INFINITY) ? 0.f : exp2f(mw[rank] - mm);
+        acc = fmaf(f, ow[rank], acc);
+        ll = fmaf(f, lw[rank], ll);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      ll += __shfl_xor_sync(0xffffffffu, ll, 1);
+      ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+      if (live && w == 0)
+        out[(size_t)b * ldo + (size_t)kvh * g * hd + i] = __float2bfloat16_rn(acc / ll);
+    }
+    DM_STAMP(8);
+    return;
+  }
 
   // ---- merge the four warps into this range's partial (unnormalised o, m, l)
   float* po = part_o + (((size_t)b * nh + (size_t)kvh * g) * n_splits + split) * hd;
@@ -248,15 +407,20 @@ __device__ __forceinline__ void attn_decode_mma_item(
 
   // ---- the CTA that finishes last for this (sequence, kv head) merges the ranges
   __syncthreads();
+  DM_STAMP(7);
   if (threadIdx.x == 0) {
     __threadfence();
+    DM_STAMP(8);
     int* ctr = counters + (size_t)b * nkv + kvh;
     const int prev = atomicAdd(ctr, 1);
     *is_last = prev == n_splits - 1;
     if (*is_last) { *ctr = 0; __threadfence(); }
   }
   __syncthreads();
+  DM_STAMP(9);
   if (!*is_last) return;
+  const bool stamping_last = stamps && kvh == 0 && b == 0;
+  if (stamping_last && threadIdx.x == 0) stamp(8, 0);
   float* wts = mrg;                       // [g][n_splits]
   float* inv_den = mrg + 8 * kDmTile;     // [g]
   const float* ml_base = part_ml + ((size_t)b * nh + (size_t)kvh * g) * n_splits * 2;
@@ -278,6 +442,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
     if (lane == 0) inv_den[j] = 1.0f / den;
   }
   __syncthreads();
+  if (stamping_last && threadIdx.x == 0) stamp(8, 1);
   for (int i = threadIdx.x; i < g * hd; i += nthreads) {
     const int j = i / hd, d = i - j * hd;
     float acc_o = 0.f;
@@ -292,19 +457,23 @@ __device__ __forceinline__ void attn_decode_mma_item(
     }
     out[(size_t)b * ldo + (size_t)(kvh * g + j) * hd + d] = __float2bfloat16_rn(acc_o * inv_den[j]);
   }
+  if (stamping_last && threadIdx.x == 0) stamp(8, 2);
+#undef DM_STAMP
 }
 
 
 // Shared-memory bytes of one CTA (without alignment slack) and the once-per-kernel set-up.
 template <int HD16>
-__host__ __device__ constexpr size_t dm_smem_core() {
+__host__ __device__ constexpr size_t dm_smem_core(bool cluster = false) {
   constexpr int hd = HD16 * 16;
   constexpr int kSub = (hd + 63) / 64;
   size_t bytes = (size_t)2 * kDmStages * kSub * kDmTile * 128;   // K and V stages
   bytes += 2 * kDmStages * 8 + 16;                                // barriers, abort, is_last
-  const size_t mrg = (size_t)(2 * kDmWarps * 8 + kDmWarps * 8 * hd) * 4;
-  const size_t wts = (size_t)(8 * kDmTile + 8) * 4;
-  return bytes + (mrg > wts ? mrg : wts);
+  bytes += dm_mrg_floats<HD16>() * 4;
+  if (cluster)     // m, l of every warp of every range; a share of the outputs from each
+    bytes += (size_t)kDmClusterMax * kDmWarps * 8 * 2 * 4 +
+             (size_t)kDmWarps * (8 * hd + kDmClusterMax) * 4;
+  return bytes;
 }
 
 template <int HD16>
@@ -323,7 +492,7 @@ __device__ __forceinline__ void dm_init(unsigned char* smem) {
   __syncthreads();
 }
 
-template <int HD16>
+template <int HD16, bool CLUSTER>
 __global__ void __launch_bounds__(kDmThreads)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v,
@@ -333,17 +502,23 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const int* __restrict__ seq_slot, int nh, int nkv, float scale_log2,
                        int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                        __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
-                       unsigned int* __restrict__ fault) {
+                       unsigned int* __restrict__ fault, unsigned long long* stamps) {
   extern __shared__ unsigned char smem_raw[];
+  if (stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    stamps[9 * 16] = t;
+  }
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   dm_init<HD16>(smem);
+  if (CLUSTER) cluster_arrive();      // "this CTA runs": waited for before anything is sent
   uint32_t it_base = 0;
-  attn_decode_mma_item<HD16>(smem, &map_k, &map_v, q, ldq, table, table_stride, tok_pos, tok_seq,
-                             seq_slot, nh, nkv, scale_log2, window, part_o, part_ml, out, ldo,
-                             counters, fault, blockIdx.x, gridDim.x, blockIdx.y, blockIdx.z,
-                             it_base);
+  attn_decode_mma_item<HD16, CLUSTER>(smem, &map_k, &map_v, q, ldq, table, table_stride, tok_pos,
+                                      tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o,
+                                      part_ml, out, ldo, counters, fault, blockIdx.x, gridDim.x,
+                                      blockIdx.y, blockIdx.z, it_base, stamps);
 }
 
 }  // namespace cretif

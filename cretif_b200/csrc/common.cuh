@@ -115,6 +115,10 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// Whether kernels that support it are launched as programmatic dependents of the kernel
+// before them (decode_fused.cu owns the switch).
+int dependent_launch_enabled();
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);

@@ -6,6 +6,7 @@ namespace cretif {
 // Launch the fused kernels with programmatic stream serialization (their weight fetch then
 // overlaps the tail of the kernel before them).
 static int g_dependent_launch = 1;
+int dependent_launch_enabled() { return g_dependent_launch; }
 
 template <int NT, int PRO, int EPI>
 static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {

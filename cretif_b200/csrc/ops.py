@@ -322,8 +322,30 @@ def decode_splits(B: int, nkv: int, max_context: int, device) -> int:
     return max(1, min(tiles, want, 64))
 
 
+CLUSTER_MAX_RANGES = 8
+
+
+def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
+    """(ranges per (sequence, kv head), merge inside a cluster?) for the decode attention.
+
+    Up to eight ranges can be one thread-block cluster, whose merge through distributed
+    shared memory is some 5 us shorter than the one through global scratch; a range is a
+    cache block or more, and a block costs about 0.3 us.  So the cluster is taken unless it
+    would make a CTA walk 16 blocks more than the plain split would (a long context with
+    few sequences)."""
+    tiles = max(1, -(-max_context // 64))
+    n_split = decode_splits(B, nkv, max_context, device)
+    if hd > 128 or _decode_simt_only:
+        return n_split, False
+    n_cluster = max(1, min(n_split, tiles, CLUSTER_MAX_RANGES))
+    if -(-tiles // n_cluster) - -(-tiles // n_split) < 16:
+        return n_cluster, True
+    return n_split, False
+
+
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
-                scale: float, window: int, block_tokens: int, n_splits: int, fault) -> None:
+                scale: float, window: int, block_tokens: int, n_splits: int, fault,
+                cluster: bool = False) -> None:
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
     B = q.shape[0]
@@ -332,6 +354,16 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
         raise KernelError("attn_decode: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
     if n_splits > 64:
         raise KernelError("attn_decode: at most 64 ranges per (sequence, kv head)")
+    if cluster:
+        if hd > 128 or _decode_simt_only or n_splits > CLUSTER_MAX_RANGES:
+            raise KernelError("attn_decode: the cluster merge takes head sizes up to 128 and at "
+                              f"most {CLUSTER_MAX_RANGES} ranges")
+        _check(lib().cretif_attn_decode_mma(
+            _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
+            ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
+            _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
+            None, None, None, _p(fault), _stream()), "attn_decode_mma")
+        return
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
     counters = _decode_counters(q.device, B * nkv)

@@ -138,10 +138,11 @@ class Attention(Part):
         if not _force_plain and self.dtype == torch.bfloat16:
             if ctx.is_decode and ops.attn_decode_supported(self.hd, kv.block_tokens,
                                                            self.nh // self.nkv):
-                splits = ops.decode_splits(ctx.B, self.nkv, ctx.max_context, q.device)
+                splits, cluster = ops.decode_plan(ctx.B, self.nkv, ctx.max_context, q.device,
+                                                  self.hd)
                 ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq,
                                 ctx.seq_slot, self.nh, self.nkv, self.hd, self.scale,
-                                self.window, kv.block_tokens, splits, ctx.fault)
+                                self.window, kv.block_tokens, splits, ctx.fault, cluster)
                 return
             if not ctx.is_decode and ops.attn_prefill_supported(self.hd, kv.block_tokens):
                 ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,

@@ -471,7 +471,30 @@ def test_attn_decode_split(ops, nh, nkv, hd, lens, window, splits, simt):
         ops.decode_attention_simt_only(False)
 
 
-def _attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
+@pytest.mark.parametrize("nh,nkv,hd,lens", [c for c in ATTN_CASES if c[2] <= 128]
+                         + [(9, 3, 64, [2048, 700, 1, 4096]), (16, 2, 128, [1000, 3])])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_attn_decode_cluster(ops, nh, nkv, hd, lens, window, splits):
+    """The ranges of a sequence as one thread-block cluster, merged through distributed
+    shared memory (ranges beyond a short sequence's blocks are empty CTAs of the cluster)."""
+    _attn_decode_split(ops, nh, nkv, hd, lens, window, splits, cluster=True)
+
+
+def test_decode_plan(ops):
+    # many sequences or a short context: few ranges, merged inside a cluster
+    n, cluster = ops.decode_plan(8, 3, 2100, DEV)
+    assert cluster and 1 <= n <= ops.CLUSTER_MAX_RANGES
+    n, cluster = ops.decode_plan(64, 3, 2100, DEV)
+    assert cluster and n <= 3
+    # one long sequence: more ranges than a cluster holds
+    n, cluster = ops.decode_plan(1, 1, 64 * 1024, DEV)
+    assert not cluster and n > ops.CLUSTER_MAX_RANGES
+    # head sizes the tensor-core kernel does not take never get a cluster
+    assert ops.decode_plan(8, 3, 2100, DEV, hd=256)[1] is False
+
+
+def _attn_decode_split(ops, nh, nkv, hd, lens, window, splits, cluster=False):
     scale = 1.0 / math.sqrt(hd)
     cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=4)
     B = len(lens)
@@ -482,7 +505,7 @@ def _attn_decode_split(ops, nh, nkv, hd, lens, window, splits):
     seq = torch.arange(B, dtype=torch.int32, device=DEV)
     fault = torch.zeros(1, dtype=torch.int32, device=DEV)
     ops.attn_decode(q, out, cache.k, cache.v, cache.table, pos, seq, cache.seq_slot, nh, nkv, hd,
-                    scale, window, 64, splits, fault)
+                    scale, window, 64, splits, fault, cluster)
     assert fault.item() == 0
     for b, n in enumerate(lens):
         k, v = cache.keys(b, n)
@@ -528,7 +551,8 @@ def test_attn_prefill_tc(ops, nh, nkv, hd, lens, news, window):
         close(out[cu[b]:cu[b + 1]].reshape(news[b], nh, hd), want, 1e-2)
 
 
-def test_attn_decode_finds_a_far_key(ops):
+@pytest.mark.parametrize("cluster", [False, True])
+def test_attn_decode_finds_a_far_key(ops, cluster):
     """One key among thousands is made to dominate; the output must be its value."""
     nh, nkv, hd, n = 4, 2, 64, 3000
     cache = ToyCache([n], nkv, hd, torch.bfloat16, seed=9)
@@ -543,7 +567,7 @@ def test_attn_decode_finds_a_far_key(ops):
     seq = torch.zeros(1, dtype=torch.int32, device=DEV)
     fault = torch.zeros(1, dtype=torch.int32, device=DEV)
     ops.attn_decode(q, out, cache.k, cache.v, cache.table, pos, seq, cache.seq_slot, nh, nkv, hd,
-                    1.0, 0, 64, 7, fault)
+                    1.0, 0, 64, 7, fault, cluster)
     for h in (0, 2):       # the heads whose own query was copied into the key
         close(out[0, h * hd:(h + 1) * hd], cache.v[blk, h // 2, target % 64, :], 2e-2)
 

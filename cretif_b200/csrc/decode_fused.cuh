@@ -223,22 +223,77 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
 // The norm prologue: x[m] = bf16(h[row m] * w * rsqrt(mean(h^2) + eps)) into shared memory, a
 // warp per token.  A row of up to 128 * REGS columns makes one trip from memory: the lane
 // keeps its REGS float4 in registers between the sum of squares and the scaling.
-template <int REGS>
-__device__ __forceinline__ void norm_rows_to_smem(const FusedParams& p, unsigned char* xs,
-                                                  int xs_stride, int warp, int lane) {
+//
+// The norm's weight depends on nothing that runs before the kernel.  For K <= 1024 N the
+// CTA's threads fetch it (N float4 each) before the kernel waits for the one before it
+// (norm_weight_fetch), and put it into shared memory (`nws`) once the first residual rows
+// have been asked for, so that its latency and theirs do not add up.
+template <int N>
+struct NormStash {
+  static constexpr int kMaxK = N * kFuWarps * 32 * 4;
+  float4 w[N];
+};
+
+template <int N>
+__device__ __forceinline__ void norm_weight_fetch(const FusedParams& p, NormStash<N>& st) {
   const int n4 = p.K >> 2;
   const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
-  for (int m = warp; m < p.M; m += kFuWarps) {
-    const float4* h4 = reinterpret_cast<const float4*>(p.H + (size_t)(p.rows ? p.rows[m] : m) * p.K);
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    const int i = threadIdx.x + u * kFuWarps * 32;
+    st.w[u] = (p.K <= NormStash<N>::kMaxK && i < n4) ? __ldg(w4 + i)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// Called by the kFuWarps * 32 threads that also called norm_weight_fetch; `sync` is the
+// barrier among exactly those threads, run once by each after its first loads are issued.
+template <int REGS, int N, typename Sync>
+__device__ __forceinline__ void norm_rows_to_smem(const FusedParams& p, unsigned char* xs,
+                                                  int xs_stride, int warp, int lane, float4* nws,
+                                                  const NormStash<N>& st, Sync sync) {
+  const int n4 = p.K >> 2;
+  const bool stash = p.K <= NormStash<N>::kMaxK;
+  const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+  bool first = true;
+  for (int m = warp; m < p.M || first; m += kFuWarps) {
+    const bool row = m < p.M;
+    const float4* h4 = reinterpret_cast<const float4*>(
+        p.H + (size_t)(row ? (p.rows ? p.rows[m] : m) : 0) * p.K);
     __nv_bfloat16* xr = reinterpret_cast<__nv_bfloat16*>(xs + (size_t)m * xs_stride);
-    if (n4 <= 32 * REGS) {
-      float4 v[REGS];
-      float ss = 0.f;
+    const bool fits = n4 <= 32 * REGS;
+    float4 v[REGS];
+    if (row && fits) {
 #pragma unroll
       for (int u = 0; u < REGS; ++u) {
         const int i = u * 32 + lane;
         v[u] = i < n4 ? __ldcg(h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+    }
+    if (first) {
+      first = false;
+      if (stash) {
+#pragma unroll
+        for (int u = 0; u < N; ++u) {
+          const int i = warp * 32 + lane + u * kFuWarps * 32;
+          if (i < n4) nws[i] = st.w[u];
+        }
+      }
+      sync();                 // always, and by every warp: the caller may count on it
+    }
+    if (!row) break;
+    auto weight = [&](int i) { return stash ? nws[i] : __ldg(w4 + i); };
+    auto put = [&](int i, const float4& t, float inv) {
+      const float4 w = weight(i);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * w.x * inv, t.y * w.y * inv);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(t.z * w.z * inv, t.w * w.w * inv);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
+    };
+    float ss = 0.f;
+    if (fits) {
 #pragma unroll
       for (int u = 0; u < REGS; ++u)
         ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
@@ -247,35 +302,18 @@ __device__ __forceinline__ void norm_rows_to_smem(const FusedParams& p, unsigned
 #pragma unroll
       for (int u = 0; u < REGS; ++u) {
         const int i = u * 32 + lane;
-        if (i < n4) {
-          const float4 w = __ldg(w4 + i);
-          __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * w.x * inv, v[u].y * w.y * inv);
-          __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * w.z * inv, v[u].w * w.w * inv);
-          uint2 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&lo);
-          pk.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
-        }
+        if (i < n4) put(i, v[u], inv);
       }
     } else {
-      float ss = 0.f;
 #pragma unroll 8
       for (int i = lane; i < n4; i += 32) {
-        const float4 v = __ldcg(h4 + i);
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        const float4 t = __ldcg(h4 + i);
+        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
       }
       ss = warp_sum(ss);
       const float inv = rsqrtf(ss / (float)p.K + p.eps);
 #pragma unroll 4
-      for (int i = lane; i < n4; i += 32) {
-        const float4 v = __ldcg(h4 + i), w = __ldg(w4 + i);
-        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * w.x * inv, v.y * w.y * inv);
-        __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * w.z * inv, v.w * w.w * inv);
-        uint2 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&lo);
-        pk.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(xr + 4 * i) = pk;
-      }
+      for (int i = lane; i < n4; i += 32) put(i, __ldcg(h4 + i), inv);
     }
   }
 }
@@ -326,13 +364,16 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   // Programmatic dependent launch: the kernel behind this one may start its own weight
   // fetch now, and this one goes on to read activations only when the kernel before it has
   // finished (a no-op when the launch was an ordinary one).
+  NormStash<1> stash;
+  if (PRO == kProNorm) norm_weight_fetch(p, stash);
   if (pdl) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
 
   if (PRO == kProNorm) {
-    norm_rows_to_smem<8>(p, xs, xs_stride, warp, lane);
+    float4* nws = reinterpret_cast<float4*>(xs + (size_t)p.M * xs_stride);
+    norm_rows_to_smem<8>(p, xs, xs_stride, warp, lane, nws, stash, [] { __syncthreads(); });
     __syncthreads();
   }
 
@@ -400,7 +441,7 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
 
 
 template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(kFuWarps * 32, NT <= 2 ? 3 : 2)
+__global__ void __launch_bounds__(kFuWarps * 32, 2)
 skinny_fused_kernel(const FusedParams p, int n_tiles) {
   extern __shared__ __align__(16) unsigned char fsmem_k[];
   skinny_fused_tiles<NT, PRO, EPI>(p, n_tiles, fsmem_k, blockIdx.x, gridDim.x, true);
@@ -408,7 +449,8 @@ skinny_fused_kernel(const FusedParams p, int n_tiles) {
 
 inline size_t fused_smem(int nt, int pro, int M, int K) {
   size_t bytes = sizeof(float) * kFuWarps * kFuRows * (8 * nt + 1) + 16;
-  if (pro == kProNorm) bytes += (size_t)M * (((K * 2 + 127) / 128) * 128 + 64);
+  if (pro == kProNorm)     // normed x, and the norm's weight when it is kept (kNormStashK)
+    bytes += (size_t)M * (((K * 2 + 127) / 128) * 128 + 64) + (K <= NormStash<1>::kMaxK ? (size_t)K * 4 : 0);
   return bytes;
 }
 

@@ -9,8 +9,10 @@ static int g_dependent_launch = 1;
 int dependent_launch_enabled() { return g_dependent_launch; }
 
 template <int NT, int PRO, int EPI>
-static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {
-  const size_t smem = fused_smem(NT, PRO, p.M, p.K);
+static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st, int groups = 1,
+                        int group_rows = 0) {
+  if (groups == 1) group_rows = p.M;
+  const size_t smem = fused_smem(NT, PRO, group_rows, p.K);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     if (smem > 200 * 1024) return kBadArgument;
@@ -24,12 +26,13 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    max_ctas = 4 * (sms > 0 ? sms : 148);
+    max_ctas = 2 * (sms > 0 ? sms : 148);      // two CTAs are resident per SM
   }
-  const int grid = tiles < max_ctas ? tiles : max_ctas;
+  const int per_group = max_ctas / groups > 0 ? max_ctas / groups : 1;
+  const dim3 grid(tiles < per_group ? tiles : per_group, groups);
   if (g_dependent_launch) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
+    cfg.gridDim = grid;
     cfg.blockDim = dim3(kFuWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -38,10 +41,11 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_fused_kernel<NT, PRO, EPI>, p, tiles);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_fused_kernel<NT, PRO, EPI>, p, tiles,
+                                       group_rows);
     return e == cudaSuccess ? launch_status() : (int)e;
   }
-  skinny_fused_kernel<NT, PRO, EPI><<<grid, kFuWarps * 32, smem, st>>>(p, tiles);
+  skinny_fused_kernel<NT, PRO, EPI><<<grid, kFuWarps * 32, smem, st>>>(p, tiles, group_rows);
   return launch_status();
 }
 
@@ -122,11 +126,15 @@ static int dispatch_nt(const FusedParams& p, int tiles, cudaStream_t st) {
   }
   if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
   if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
-  return launch_fused<4, PRO, EPI>(p, tiles, st);      // up to 32 rows
+  if (p.M <= kFuMaxGroupRows) return launch_fused<4, PRO, EPI>(p, tiles, st);
+  // more tokens: even groups of up to 32 rows, a multiple of 8 each
+  const int groups = (p.M + kFuMaxGroupRows - 1) / kFuMaxGroupRows;
+  const int group_rows = (((p.M + groups - 1) / groups) + 7) & ~7;
+  return launch_fused<4, PRO, EPI>(p, tiles, st, groups, group_rows);
 }
 
 static bool common_ok(const FusedParams& p) {
-  return p.M > 0 && p.M <= 32 && p.K > 0 && p.K % 8 == 0 && p.ldw % 8 == 0 && p.ldw >= p.K &&
+  return p.M > 0 && p.M <= kFuMaxRows && p.K > 0 && p.K % 8 == 0 && p.ldw % 8 == 0 && p.ldw >= p.K &&
          (((uintptr_t)p.W) & 15) == 0;
 }
 
@@ -213,7 +221,8 @@ extern "C" int cretif_set_dependent_launch(int on) {
 }
 
 extern "C" int cretif_fused_smem_ok(int M, int K, int norm_prologue) {
-  if (M > 32) return 0;
+  if (M > kFuMaxRows) return 0;
+  if (M > kFuMaxGroupRows) M = kFuMaxGroupRows;
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
   return fused_smem(nt, norm_prologue ? kProNorm : kProPlain, M, K) <= 200 * 1024 ? 1 : 0;
 }

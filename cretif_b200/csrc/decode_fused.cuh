@@ -440,11 +440,36 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
 }
 
 
+// The parameters of rows m0 .. m0 + n - 1 of a call as a call of their own: everything that
+// is indexed by the token moves along.
+__host__ __device__ inline FusedParams rows_of(const FusedParams& p, int m0, int n) {
+  FusedParams q = p;
+  q.M = n;
+  if (p.X) q.X = p.X + (size_t)m0 * p.ldx;
+  if (p.rows) q.rows = p.rows + m0;
+  else if (p.H) q.H = p.H + (size_t)m0 * p.K;
+  if (p.C)
+    q.C = static_cast<unsigned char*>(p.C) + (size_t)m0 * p.ldc * (p.c_dt == kF32 ? 4 : 2);
+  if (p.Q) q.Q = p.Q + (size_t)m0 * p.ldq;
+  if (p.tok_pos) q.tok_pos = p.tok_pos + m0;
+  if (p.tok_seq) q.tok_seq = p.tok_seq + m0;
+  if (p.act) q.act = p.act + (size_t)m0 * p.I;
+  return q;
+}
+
+// More than kFuMaxGroupRows tokens run as groups of rows along gridDim.y: every group reads
+// the whole matrix (the second time from L2), which for a few dozen tokens is still far
+// cheaper than a tensor-core tile of 128 tokens on a handful of CTAs.
+constexpr int kFuMaxGroupRows = 32;
+constexpr int kFuMaxRows = 128;
+
 template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(kFuWarps * 32, 2)
-skinny_fused_kernel(const FusedParams p, int n_tiles) {
+skinny_fused_kernel(const FusedParams p, int n_tiles, int group_rows) {
   extern __shared__ __align__(16) unsigned char fsmem_k[];
-  skinny_fused_tiles<NT, PRO, EPI>(p, n_tiles, fsmem_k, blockIdx.x, gridDim.x, true);
+  const int m0 = blockIdx.y * group_rows;            // one group: all rows from 0
+  const FusedParams q = rows_of(p, m0, min(group_rows, p.M - m0));
+  skinny_fused_tiles<NT, PRO, EPI>(q, n_tiles, fsmem_k, blockIdx.x, gridDim.x, true);
 }
 
 inline size_t fused_smem(int nt, int pro, int M, int K) {

@@ -402,10 +402,20 @@ def _decode_counters(device, n: int) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ fused decode projections
+FUSED_MAX_ROWS = 128     # the kernels' limit; the parts choose how far they use it
+# Beyond 32 rows the kernel reads the matrix once per group of 32: worth it while the matrix
+# is small (measured: 64 tokens at SmolLM2-135M sizes, where no matrix but the head exceeds
+# 4 MB, take 0.7 of the tensor-core path's time; at 1.7B sizes 1.4 times).
+FUSED_GROUPS_MAX_BYTES = 8 << 20
+
+
 def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:
     """Whether the fused kernel takes M rows of width K against w (``norm``: with the norm
     prologue, which keeps the normed rows in shared memory)."""
-    return (w.dtype == torch.bfloat16 and 0 < M <= 32 and K % 8 == 0 and w.stride(1) == 1
+    if M > 32 and w.numel() * w.element_size() > FUSED_GROUPS_MAX_BYTES:
+        return False
+    return (w.dtype == torch.bfloat16 and 0 < M <= FUSED_MAX_ROWS and K % 8 == 0
+            and w.stride(1) == 1
             and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
             and bool(lib().cretif_fused_smem_ok(M, K, int(norm))))
 

@@ -32,18 +32,20 @@ constexpr int kPfThreads = 320;   // producer, MMA issuer, eight softmax warps
 constexpr int kPfBQ = 128;       // queries per CTA
 constexpr int kPfBlk = 64;       // tokens per cache block
 constexpr int kPfBK = 128;       // keys per step: two cache blocks
-constexpr int kPfStages = 2;
+constexpr int kPfMaxStages = 3;   // ring of K/V stages: 3 for head sizes up to 64, else 2
 
 struct PfSmem {
   // byte offsets for a head size with n_sub 64-wide column groups
-  int q, p, k, v, bars, xch, total;
+  int q, p, k, v, bars, xch, total, stages, p_bufs;
   __host__ __device__ explicit PfSmem(int n_sub) {
+    stages = n_sub == 1 ? 3 : 2;
+    p_bufs = n_sub == 1 ? 2 : 1;      // two P tiles: the softmax runs one step ahead of P V
     q = 0;
     p = q + n_sub * kPfBQ * 128;
-    k = p + (kPfBK / 64) * kPfBQ * 128;
-    v = k + kPfStages * n_sub * kPfBK * 128;
-    bars = v + kPfStages * n_sub * kPfBK * 128;
-    xch = bars + (2 * kPfStages + 4) * 8 + 16;
+    k = p + p_bufs * (kPfBK / 64) * kPfBQ * 128;
+    v = k + stages * n_sub * kPfBK * 128;
+    bars = v + stages * n_sub * kPfBK * 128;
+    xch = bars + (2 * kPfMaxStages + 6) * 8 + 16;
     total = xch + 4 * kPfBQ * 4 + 1024;
   }
 };
@@ -80,19 +82,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        int ldo, const int* __restrict__ table, int table_stride,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
-                       int window, unsigned int* __restrict__ fault) {
+                       int window, unsigned int* __restrict__ fault,
+                       unsigned long long* stamps) {
   extern __shared__ unsigned char smem_raw[];
+  // Tuning aid: with a buffer given, the first CTA (the heaviest tile) notes the times at
+  // which its MMA thread and one softmax thread pass the phases of steps 0 .. 7:
+  // [step][16] nanoseconds.
+  const bool stamping = stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+  auto stamp = [&](int j, int i) {
+    if (stamping && j < 8) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      stamps[j * 16 + i] = t;
+    }
+  };
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int n_sub = (hd + 63) >> 6;
   const PfSmem L(n_sub);
+  const int kPfStages = L.stages;
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L.bars);
-  uint64_t* kv_empty = kv_full + kPfStages;
-  uint64_t* q_full = kv_empty + kPfStages;
-  uint64_t* s_full = q_full + 1;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* kv_empty = kv_full + kPfMaxStages;
+  uint64_t* q_full = kv_empty + kPfMaxStages;
+  uint64_t* s_full = q_full + 1;            // two: S is double-buffered in tensor memory
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_full = p_full + 1;            // two: so is P V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  // With two P tiles the softmax threads do not wait for a step's P V: they go on to the next
+  // step's scores and fold the product in one step later.
+  const bool defer = L.p_bufs == 2;
+  constexpr int kPBytes = (kPfBK / 64) * kPfBQ * 128;
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,15 +130,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
   const int blk_lo = key_lo / kPfBlk, blk_hi = pos_last / kPfBlk;      // cache blocks, inclusive
   const int n_tiles = (blk_hi - blk_lo + 2) / 2;                        // steps of two blocks
-  constexpr uint32_t kTmemCols = 256;
-  constexpr uint32_t kColS = 0, kColO = 128;
+  // Tensor memory: two score tiles (the product of step j + 1 runs under the softmax of
+  // step j) and two tiles of P V.
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;      // + 128 (j & 1) each
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPfStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
     tc::mbar_init(q_full, 1);
-    tc::mbar_init(s_full, 1);
+    tc::mbar_init(&s_full[0], 1);
+    tc::mbar_init(&s_full[1], 1);
     tc::mbar_init(p_full, 256);
-    tc::mbar_init(o_full, 1);
+    tc::mbar_init(&o_full[0], 1);
+    tc::mbar_init(&o_full[1], 1);
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_q);
@@ -134,6 +157,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // Programmatic dependent launch: the set-up above ran under the tail of the kernel before
+  // this one; the queries and this prompt's keys and values are that kernel's output.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     if (lane == 0) {
@@ -166,33 +193,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK);
       const uint32_t idesc_pv = tc::instr_desc_bf16(kPfBQ, hd) | (1u << 16);   // B is MN-major
       const int k_steps = hd >> 4;
-      bool ok = tc::mbar_wait(q_full, 0u, abort);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      auto scores = [&](int j) {            // S[j & 1] = Q K_j^T, once K_j has landed
         const int s = j % kPfStages;
-        ok = tc::mbar_wait(&kv_full[s], (uint32_t)((j / kPfStages) & 1), abort);
-        if (!ok) break;
+        if (!tc::mbar_wait(&kv_full[s], (uint32_t)((j / kPfStages) & 1), abort)) return false;
         tc::tc_fence_after();
         for (int kk = 0; kk < k_steps; ++kk) {
           const int sub = kk >> 2, in = kk & 3;
           const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + sub * kPfBQ * 128) + 2 * in;
           const uint64_t kd =
               tc::smem_desc_k_sw128(smem + L.k + (s * n_sub + sub) * kPfBK * 128) + 2 * in;
-          tc::umma_bf16(tmem + kColS, qd, kd, idesc_qk, kk != 0);
+          tc::umma_bf16(tmem + kColS + (uint32_t)(j & 1) * kPfBK, qd, kd, idesc_qk, kk != 0);
         }
-        tc::umma_commit(s_full);
+        tc::umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      bool ok = tc::mbar_wait(q_full, 0u, abort);
+      if (ok && n_tiles > 0) ok = scores(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kPfStages;
+        // The next step's scores go to the other buffer, which the softmax threads left
+        // before they signalled P of step j - 1 (waited for below, one step ago).
+        if (j + 1 < n_tiles && !(ok = scores(j + 1))) break;
+        stamp(j, 8);
         ok = tc::mbar_wait(p_full, (uint32_t)(j & 1), abort);
         if (!ok) break;
+        stamp(j, 9);
         tc::tc_fence_after();
         const uint64_t vd = smem_desc_mn_sw128(smem + L.v + s * n_sub * kPfBK * 128,
                                                (uint32_t)(kPfBK * 128));
 #pragma unroll
         for (int kk = 0; kk < kPfBK / 16; ++kk) {    // 16 keys = two 1024-byte atoms of V
-          const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p + (kk >> 2) * kPfBQ * 128) +
+          const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p + (defer ? (j & 1) * kPBytes : 0) +
+                                                    (kk >> 2) * kPfBQ * 128) +
                               2 * (kk & 3);
-          tc::umma_bf16(tmem + kColO, pd, vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
+          tc::umma_bf16(tmem + kColO + (uint32_t)(j & 1) * 128, pd, vd + (uint64_t)(kk * 128),
+                        idesc_pv, kk != 0);
         }
         tc::umma_commit(&kv_empty[s]);
-        tc::umma_commit(o_full);
+        tc::umma_commit(&o_full[j & 1]);
+        stamp(j, 10);
       }
     }
   } else {
@@ -214,18 +253,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
     for (int d = 0; d < HDMAX / 2; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    unsigned char* prow = smem + L.p + half * kPfBQ * 128 + row * 128;
+    unsigned char* prow0 = smem + L.p + half * kPfBQ * 128 + row * 128;
     float* xch = reinterpret_cast<float*>(smem + L.xch);              // [2 buffers][2][128]
     // A wait that gives up does not leave the loop: the pair's barriers must stay matched.
     // Later waits return at once (the abort flag is up) and the result is flagged, not used.
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      ok = tc::mbar_wait(s_full, (uint32_t)(j & 1), abort) && ok;
+    // o = o * a + (P V of step jj), once that product is in tensor memory
+    auto fold = [&](int jj, float a) {
+      ok = tc::mbar_wait(&o_full[jj & 1], (uint32_t)((jj >> 1) & 1), abort) && ok;
       tc::tc_fence_after();
+      if (warp == 2) stamp(jj, 5);
+#pragma unroll
+      for (int c0 = 0; c0 < HDMAX / 2; c0 += 32) {
+        if (c0 < ocols) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_addr + kColO + (uint32_t)(jj & 1) * 128 + obase + c0, r);
+          tc::tmem_load_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (c0 + e < HDMAX / 2) o[c0 + e] = fmaf(o[c0 + e], a, __uint_as_float(r[e]));
+        }
+      }
+      tc::tc_fence_before();
+      if (warp == 2) stamp(jj, 6);
+    };
+    float alpha_before = 0.f;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (warp == 2) stamp(j, 0);
+      unsigned char* prow = prow0 + (defer ? (j & 1) * kPBytes : 0);
+      ok = tc::mbar_wait(&s_full[j & 1], (uint32_t)((j >> 1) & 1), abort) && ok;
+      tc::tc_fence_after();
+      if (warp == 2) stamp(j, 1);
       uint32_t sa[32], sb[32];
-      tc::tmem_load_32(lane_addr + kColS + half * 64, sa);
-      tc::tmem_load_32(lane_addr + kColS + half * 64 + 32, sb);
+      const uint32_t s_col = kColS + (uint32_t)(j & 1) * kPfBK + half * 64;
+      tc::tmem_load_32(lane_addr + s_col, sa);
+      tc::tmem_load_32(lane_addr + s_col + 32, sb);
       tc::tmem_load_wait();
+      if (warp == 2) stamp(j, 2);
       const int key0 = (blk_lo + 2 * j) * kPfBlk + half * 64;
       // Raw scores stay in their registers; only steps that touch the diagonal, the
       // sequence's end or a window's edge pay for masking (uniform for the whole CTA).
@@ -250,6 +314,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       float* xb = xch + (j & 1) * 256;        // double-buffered: one barrier per step
       xb[half * 128 + row] = mine;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      if (warp == 2) stamp(j, 3);
       const float m_new = fmaxf(m, fmaxf(mine, xb[(half ^ 1) * 128 + row]));
       const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
       // p = 2^(s * scale - m); a masked score (-inf) gives 0, and a row with nothing to see
@@ -273,22 +338,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v4;
       }
       tc::fence_proxy_async();                // generic-proxy writes → visible to the MMA
+      tc::tc_fence_before();                  // and this step's reads of S are done
       tc::mbar_arrive(p_full);
-      ok = tc::mbar_wait(o_full, (uint32_t)(j & 1), abort) && ok;
-      tc::tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < HDMAX / 2; c0 += 32) {
-        if (c0 < ocols) {
-          uint32_t r[32];
-          tc::tmem_load_32(lane_addr + kColO + obase + c0, r);
-          tc::tmem_load_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c0 + e < HDMAX / 2) o[c0 + e] = fmaf(o[c0 + e], alpha, __uint_as_float(r[e]));
-        }
+      if (warp == 2) stamp(j, 4);
+      if (!defer) {
+        fold(j, alpha);
+      } else {
+        if (j > 0) fold(j - 1, alpha_before);
+        alpha_before = alpha;
       }
-      tc::tc_fence_before();
     }
+    if (defer && n_tiles > 0) fold(n_tiles - 1, alpha_before);
     // the row's sum is the two halves' sums (the buffer of step n_tiles was last read two
     // steps ago)
     float* xb = xch + (n_tiles & 1) * 256;
@@ -322,6 +382,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
 using namespace cretif;
 
+// Tuning aid: a device buffer of 8 x 16 timestamps that the next launches fill (see the kernel).
+static unsigned long long* g_pf_stamps = nullptr;
+extern "C" void cretif_attn_prefill_stamps(unsigned long long* device_buffer) {
+  g_pf_stamps = device_buffer;
+}
+
 extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo,
                                       const void* kc, const void* vc, long long n_blocks,
                                       const int* table, int table_stride, const int* cu_seqlens,
@@ -343,7 +409,16 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   const PfSmem L(n_sub);
   cudaStream_t st = (cudaStream_t)stream;
   const float scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid((max_new + kPfBQ - 1) / kPfBQ, nh, B);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((max_new + kPfBQ - 1) / kPfBQ, nh, B);
+  cfg.blockDim = dim3(kPfThreads);
+  cfg.dynamicSmemBytes = L.total;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   cudaError_t e;
   if (hd <= 64) {
     static int configured = 0;
@@ -353,9 +428,10 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
       if (e != cudaSuccess) return (int)e;
       configured = L.total;
     }
-    attn_prefill_tc_kernel<64><<<grid, kPfThreads, L.total, st>>>(
-        map_q, map_k, map_v, (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-        seq_slot, nh, nkv, hd, scale_log2, window, fault);
+    e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<64>, map_q, map_k, map_v,
+                           (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps);
+    if (e != cudaSuccess) return (int)e;
   } else {
     static int configured = 0;
     if (L.total > configured) {
@@ -364,9 +440,10 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
       if (e != cudaSuccess) return (int)e;
       configured = L.total;
     }
-    attn_prefill_tc_kernel<128><<<grid, kPfThreads, L.total, st>>>(
-        map_q, map_k, map_v, (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-        seq_slot, nh, nkv, hd, scale_log2, window, fault);
+    e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<128>, map_q, map_k, map_v,
+                           (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps);
+    if (e != cudaSuccess) return (int)e;
   }
   return launch_status();
 }

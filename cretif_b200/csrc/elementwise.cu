@@ -80,6 +80,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        int write_h) {
   __shared__ float scratch[33];
   constexpr int kKeep = 4;
+  // (a no-op pair unless the launch was a programmatic dependent one)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* hrow = h + (size_t)src * H;
@@ -255,15 +258,26 @@ static int add_rmsnorm_out(float* h, const TD* delta, const float* w, void* out,
   if (aligned) {
     const int n4 = H / 4;
     const int vthreads = n4 >= 512 ? 256 : (n4 >= 128 ? 128 : (n4 >= 64 ? 64 : 32));
+    // as a programmatic dependent of the kernel before it: its launch runs under that tail
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(R);
+    cfg.blockDim = dim3(vthreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
     if (out_dt == kF32)
-      add_rmsnorm_vec_kernel<TD, float><<<R, vthreads, 0, st>>>(h, delta, w, (float*)out, rows, H,
-                                                               eps, write_h);
+      e = cudaLaunchKernelEx(&cfg, add_rmsnorm_vec_kernel<TD, float>, h, delta, w, (float*)out,
+                             rows, H, eps, write_h);
     else if (out_dt == kBF16)
-      add_rmsnorm_vec_kernel<TD, __nv_bfloat16><<<R, vthreads, 0, st>>>(
-          h, delta, w, (__nv_bfloat16*)out, rows, H, eps, write_h);
+      e = cudaLaunchKernelEx(&cfg, add_rmsnorm_vec_kernel<TD, __nv_bfloat16>, h, delta, w,
+                             (__nv_bfloat16*)out, rows, H, eps, write_h);
     else
       return kBadDType;
-    return launch_status();
+    return e == cudaSuccess ? launch_status() : (int)e;
   }
   const int threads = H >= 2048 ? 512 : (H >= 256 ? 256 : 64);
   if (out_dt == kF32)

@@ -26,16 +26,28 @@ namespace cretif {
 constexpr int kTcBM = 128, kTcBK = 64;
 constexpr int kTcThreads = 192;
 
-// Narrow tiles take three stages so that two (BN = 128) or three (BN = 64) CTAs share an SM
-// and hide each other's fill and drain; the widest tile takes four.
+// The depth of the ring is chosen per launch.  With more tiles than SMs, narrow tiles take
+// three stages so that two (BN = 128) or three (BN = 64) CTAs share an SM and hide each
+// other's fill and drain, and the widest tile takes four.  A grid of at most one CTA per SM
+// has the SM to itself: the ring is as deep as the k-blocks or shared memory allow, so that a
+// short K (9 blocks at 576) is in flight almost at once.
+constexpr int kTcMaxStages = 8;
 template <int BN>
 struct TcSmem {
-  static constexpr int kStages = BN >= 256 ? 4 : 3;
   static constexpr int kATile = kTcBM * kTcBK * 2;
   static constexpr int kBTile = BN * kTcBK * 2;
   static constexpr int kStage = kATile + kBTile;
-  static constexpr int kBars = kStages * kStage;          // offset of the barriers
-  static constexpr int kTotal = kBars + (2 * kStages + 1) * 8 + 16 + 1024;  // + align slack
+  static constexpr int total(int stages) {     // barriers behind the stages, + align slack
+    return stages * kStage + (2 * kTcMaxStages + 1) * 8 + 16 + 1024;
+  }
+  static int stages_for(long long ctas, int num_kb, int sm_count) {
+    int stages = BN >= 256 ? 4 : 3;
+    if (ctas <= sm_count) {
+      stages = num_kb < kTcMaxStages ? (num_kb < 3 ? 3 : num_kb) : kTcMaxStages;
+      while (stages > 3 && total(stages) > 200 * 1024) --stages;
+    }
+    return stages;
+  }
 };
 
 // What the epilogue warps do with the accumulator.
@@ -66,17 +78,28 @@ __device__ __forceinline__ float round_bf16(float x) {
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault) {
+               const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
+               int kTcStages, unsigned long long* stamps) {
+  // Tuning aid: with a buffer given, lane 0 of each warp of the first CTA notes the time at
+  // which it passes its phases: [warp][8] nanoseconds.
+  const bool stamping = stamps && blockIdx.x + blockIdx.y == 0 && (threadIdx.x & 31) == 0;
+  auto stamp = [&](int i) {
+    if (stamping) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      stamps[(threadIdx.x >> 5) * 8 + i] = t;
+    }
+  };
+  stamp(0);
   TC* const C = reinterpret_cast<TC*>(ep.C);
   const int ldc = ep.ldc, accumulate = ep.accumulate;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TcSmem<BN>;
-  constexpr int kTcStages = L::kStages;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBars);
-  uint64_t* empty = full + kTcStages;
-  uint64_t* acc_full = empty + kTcStages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kTcStages * L::kStage);
+  uint64_t* empty = full + kTcMaxStages;
+  uint64_t* acc_full = empty + kTcMaxStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -100,14 +123,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  // Programmatic dependent launch: the kernel behind this one may begin its own set-up.  The
+  // weights do not depend on the kernel before this one, so the first stages' W tiles are
+  // asked for before the wait; A, and everything the epilogue reads or writes, after it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  stamp(1);
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const int early = num_kb < kTcStages ? num_kb : kTcStages;
+      for (int kb = 0; kb < early; ++kb) {
+        tc::mbar_expect_tx(&full[kb], (uint32_t)L::kStage);
+        tc::tma_load_2d(smem + kb * L::kStage + L::kATile, &map_w, kb * kTcBK, n0, &full[kb]);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      stamp(2);
+      for (int kb = 0; kb < early; ++kb)
+        tc::tma_load_2d(smem + kb * L::kStage, &map_a, kb * kTcBK, m0, &full[kb]);
+      stamp(3);
+      for (int kb = early; kb < num_kb; ++kb) {
         const int s = kb % kTcStages;
-        if (kb >= kTcStages &&
-            !tc::mbar_wait(&empty[s], (uint32_t)((kb / kTcStages - 1) & 1), abort))
-          break;
+        if (!tc::mbar_wait(&empty[s], (uint32_t)((kb / kTcStages - 1) & 1), abort)) break;
         unsigned char* stage = smem + s * L::kStage;
         tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
         tc::tma_load_2d(stage, &map_a, kb * kTcBK, m0, &full[s]);
@@ -123,6 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         ok = tc::mbar_wait(&full[s], (uint32_t)((kb / kTcStages) & 1), abort);
         if (!ok) break;
         tc::tc_fence_after();
+        if (kb == 0) stamp(2);
         unsigned char* stage = smem + s * L::kStage;
         const uint64_t a_desc = tc::smem_desc_k_sw128(stage);
         const uint64_t b_desc = tc::smem_desc_k_sw128(stage + L::kATile);
@@ -132,13 +169,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc::umma_commit(&empty[s]);                // frees the stage when these MMAs are done
       }
       tc::umma_commit(acc_full);                   // accumulator complete
+      stamp(3);
     }
   } else {
     // ---- epilogue: thread = one row of the tile, TMEM lanes 32*(warp%4) ..
     const int quad = warp & 3;
     const int m = m0 + quad * 32 + lane;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(2);
     const bool ok = tc::mbar_wait(acc_full, 0u, abort);
     tc::tc_fence_after();
+    stamp(3);
     const uint32_t lane_acc = tmem_acc + ((uint32_t)(quad * 32) << 16);
     if (ok && EPI == kTcStore) {
 #pragma unroll 1
@@ -289,6 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
+  stamp(4);
   if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
   tc::tc_fence_before();
   __syncthreads();
@@ -296,6 +338,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncwarp();
     tc::tmem_dealloc(tmem_acc, BN);
   }
+  stamp(5);
 }
 
 // ---------------------------------------------------------------- host side
@@ -322,10 +365,11 @@ static EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* base;
   int rows, cols, ld, box_rows, box_cols;
-  bool swizzle;
+  bool swizzle, f32;
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
-           box_rows == o.box_rows && box_cols == o.box_cols && swizzle == o.swizzle;
+           box_rows == o.box_rows && box_cols == o.box_cols && swizzle == o.swizzle &&
+           f32 == o.f32;
   }
 };
 constexpr int kMapCacheSize = 1024;
@@ -334,15 +378,16 @@ static CUtensorMap g_map_vals[kMapCacheSize];
 static bool g_map_used[kMapCacheSize];
 static std::mutex g_map_mutex;
 
-int make_box_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows,
-                      int box_cols, bool swizzle) {
-  if (box_rows < 1 || box_rows > 256 || box_cols < 8 || box_cols > 256 ||
-      (swizzle && box_cols != 64))
+static int make_box_map(CUtensorMap* map, const void* base, int rows, int cols, int ld,
+                        int box_rows, int box_cols, bool swizzle, bool f32) {
+  const int elem_bytes = f32 ? 4 : 2;
+  if (box_rows < 1 || box_rows > 256 || box_cols < 4 || box_cols > 256 ||
+      (swizzle && box_cols * elem_bytes != 128))
     return kBadArgument;
-  const MapKey key = {base, rows, cols, ld, box_rows, box_cols, swizzle};
+  const MapKey key = {base, rows, cols, ld, box_rows, box_cols, swizzle, f32};
   size_t hsh = (size_t)((uintptr_t)base >> 4) * 1000003u ^ (size_t)rows * 8191u ^
                (size_t)cols * 131u ^ (size_t)ld * 31u ^ (size_t)box_rows ^
-               (size_t)box_cols * 524287u ^ (size_t)swizzle;
+               (size_t)box_cols * 524287u ^ (size_t)swizzle ^ ((size_t)f32 << 1);
   const int at = (int)(hsh % kMapCacheSize);
   {
     std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -354,10 +399,11 @@ int make_box_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, in
   EncodeTiledFn fn = encode_fn();
   if (!fn) return kBadArgument;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1u, 1u};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+  CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims,
                   strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -369,10 +415,18 @@ int make_box_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, in
   return 0;
 }
 
+int make_box_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows,
+                      int box_cols, bool swizzle) {
+  return make_box_map(map, base, rows, cols, ld, box_rows, box_cols, swizzle, false);
+}
+
 int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, int ld,
                        int box_rows) {
   return make_box_map_bf16(map, base, rows, cols, ld, box_rows, 64, true);
 }
+
+// Tuning aid: a device buffer of 6 x 8 timestamps that the next launches fill (see the kernel).
+static unsigned long long* g_tc_stamps = nullptr;
 
 template <int BN, int EPI, typename TC>
 static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N, int K, int lda,
@@ -380,18 +434,37 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   CUtensorMap map_a, map_w;
   if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
   if (make_tile_map_bf16(&map_w, W, N, K, ldw, BN)) return kBadArgument;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         TcSmem<BN>::kTotal);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
   }
-  dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
-  gemm_tc_kernel<BN, EPI, TC><<<grid, kTcThreads, TcSmem<BN>::kTotal, st>>>(map_a, map_w, ep, M, N,
-                                                                           K, fault);
-  return launch_status();
+  const dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
+  const int stages = TcSmem<BN>::stages_for((long long)grid.x * grid.y, (K + kTcBK - 1) / kTcBK,
+                                            sm_count);
+  const int smem = TcSmem<BN>::total(stages);
+  static int configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, map_a, map_w, ep, M, N, K,
+                                     fault, stages, g_tc_stamps);
+  return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, int ldw) {
@@ -402,6 +475,10 @@ static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, 
 }  // namespace cretif
 
 using namespace cretif;
+
+extern "C" void cretif_gemm_tc_stamps(unsigned long long* device_buffer) {
+  g_tc_stamps = device_buffer;
+}
 
 extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K,
                               int lda, int ldw, int ldc, int accumulate, int bn,

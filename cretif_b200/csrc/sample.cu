@@ -95,10 +95,21 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     // ---- greedy: arg-max with the lowest id among equals
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += kSampleThreads) {
-      const float v = x[i];
+    auto take = [&](float v, int i) {
       if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    };
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {       // 16-byte loads, eight in flight
+      const float4* x4 = reinterpret_cast<const float4*>(x);
+      const int n4 = V >> 2;
+#pragma unroll 8
+      for (int i = tid; i < n4; i += kSampleThreads) {
+        const float4 v = __ldg(x4 + i);
+        take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
+      }
+      done = n4 << 2;
     }
+    for (int i = done + tid; i < V; i += kSampleThreads) take(x[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);

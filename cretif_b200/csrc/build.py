@@ -1,11 +1,13 @@
 """Building and loading the kernel library.
 
-The ``.cu`` files beside this module are compiled with ``nvcc`` for sm_100a into one
-shared library that is loaded with ``ctypes``.  The library's file name carries a hash
-of the sources and flags, so an edited source is never served by a stale build.  The
-library is looked for, and built at first need, in ``_build/`` beside the sources; if
-that folder cannot be written (a read-only installation) a per-user folder under the
-system's temporary directory is used instead.  While compiling, a line is printed to
+The ``.cu`` files beside this module are compiled with ``nvcc`` for sm_100a into shared
+libraries that are loaded with ``ctypes``: ``kernels`` holds everything a model's steps use,
+``step`` the optional whole-step kernel (``decode_step.cu``, half a minute of compile time
+on its own, off by default), which is built only when somebody asks for it.  A library's
+file name carries a hash of its sources and flags, so an edited source is never served by a
+stale build.  Libraries are looked for, and built at first need, in ``_build/`` beside the
+sources; if that folder cannot be written (a read-only installation) a per-user folder under
+the system's temporary directory is used instead.  While compiling, a line is printed to
 stderr for every file so that a first call does not look hung.
 """
 from __future__ import annotations
@@ -26,16 +28,26 @@ _ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 _NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
                "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
-_lib: Optional[ctypes.CDLL] = None
-_lib_path: Optional[str] = None
+_OPTIONAL = {"step": ["decode_step.cu"]}       # group -> its sources; the rest is "kernels"
+_libs: dict = {}
+_lib_paths: dict = {}
 
 
 class KernelBuildError(RuntimeError):
     """The kernel library could not be built or loaded."""
 
 
-def sources() -> List[str]:
-    return sorted(f for f in os.listdir(_HERE) if f.endswith(".cu"))
+def groups() -> List[str]:
+    return ["kernels"] + sorted(_OPTIONAL)
+
+
+def sources(group: str = "kernels") -> List[str]:
+    if group in _OPTIONAL:
+        return sorted(_OPTIONAL[group])
+    if group != "kernels":
+        raise KeyError(f"no kernel library {group!r}; there are {groups()}")
+    taken = {f for fs in _OPTIONAL.values() for f in fs}
+    return sorted(f for f in os.listdir(_HERE) if f.endswith(".cu") and f not in taken)
 
 
 def _headers() -> List[str]:
@@ -51,9 +63,9 @@ def _find_nvcc() -> str:
                            "/usr/local/cuda/bin); the kernels cannot be compiled")
 
 
-def source_hash() -> str:
+def source_hash(group: str = "kernels") -> str:
     h = hashlib.sha256()
-    for name in sources() + _headers():
+    for name in sources(group) + _headers():
         h.update(name.encode())
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(f.read())
@@ -83,9 +95,9 @@ def _writable_dir(path: str) -> bool:
         return False
 
 
-def library_path(build: bool = True, verbose: bool = True) -> str:
+def library_path(build: bool = True, verbose: bool = True, group: str = "kernels") -> str:
     """Path of the built library for the present sources; builds it if it is missing."""
-    name = f"libcretif_kernels_{source_hash()}.so"
+    name = f"libcretif_{group}_{source_hash(group)}.so"
     for d in _build_dirs():
         p = os.path.join(d, name)
         if os.path.isfile(p):
@@ -94,7 +106,7 @@ def library_path(build: bool = True, verbose: bool = True) -> str:
         raise KernelBuildError(f"{name} has not been built")
     for d in _build_dirs():
         if _writable_dir(d):
-            return _compile(d, name, verbose)
+            return _compile(d, name, verbose, group)
     raise KernelBuildError("no writable folder to build the kernel library in; "
                            f"tried {_build_dirs()}")
 
@@ -104,10 +116,10 @@ def _say(msg: str, verbose: bool) -> None:
         print(f"[cretif_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def _compile(build_dir: str, name: str, verbose: bool) -> str:
+def _compile(build_dir: str, name: str, verbose: bool, group: str) -> str:
     nvcc = _find_nvcc()
-    srcs = sources()
-    tag = name[len("libcretif_kernels_"):-3]
+    srcs = sources(group)
+    tag = name[len("libcretif_"):-3]
     obj_dir = os.path.join(build_dir, f"obj_{tag}")
     os.makedirs(obj_dir, exist_ok=True)
     _say(f"compiling {len(srcs)} CUDA files for sm_100a into {build_dir} (first use only)",
@@ -140,26 +152,29 @@ def _compile(build_dir: str, name: str, verbose: bool) -> str:
     os.replace(tmp, out)
     for old in os.listdir(build_dir):          # builds of earlier sources are of no use
         path = os.path.join(build_dir, old)
-        if old.startswith("libcretif_kernels_") and old.endswith(".so") and old != name:
+        if old.startswith(f"libcretif_{group}_") and old.endswith(".so") and old != name:
             os.remove(path)
-        elif old.startswith("obj_") and old != f"obj_{tag}":
+        elif old.startswith(f"obj_{group}_") and old != f"obj_{tag}":
             shutil.rmtree(path, ignore_errors=True)
     _say(f"built {name} in {time.time() - t0:.0f} s", verbose)
     return out
 
 
-def load_library(verbose: bool = True) -> ctypes.CDLL:
-    """The kernel library, built on first use.  Raises KernelBuildError if that fails."""
-    global _lib, _lib_path
-    if _lib is None:
-        path = library_path(build=True, verbose=verbose)
+def load_library(verbose: bool = True, group: str = "kernels") -> ctypes.CDLL:
+    """A kernel library, built on first use.  Raises KernelBuildError if that fails.  An
+    optional library uses host functions of ``kernels``, which is therefore loaded first and
+    with its symbols visible to later loads."""
+    if group not in _libs:
+        if group != "kernels":
+            load_library(verbose, "kernels")
+        path = library_path(build=True, verbose=verbose, group=group)
         try:
-            _lib = ctypes.CDLL(path)
+            _libs[group] = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
         except OSError as e:
             raise KernelBuildError(f"cannot load {path}: {e}") from None
-        _lib_path = path
-    return _lib
+        _lib_paths[group] = path
+    return _libs[group]
 
 
-def loaded_library_path() -> Optional[str]:
-    return _lib_path
+def loaded_library_path(group: str = "kernels") -> Optional[str]:
+    return _lib_paths.get(group)

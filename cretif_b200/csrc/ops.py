@@ -46,6 +46,12 @@ def lib():
     return _lib
 
 
+def step_lib():
+    """The optional library with the whole-step kernel, built when it is first asked for."""
+    lib()
+    return load_library(group="step")
+
+
 _launches = 0
 
 

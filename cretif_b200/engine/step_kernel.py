@@ -48,10 +48,26 @@ class StepKernel:
 
     def __init__(self, model, cache):
         self.model, self.cache = model, cache
-        self.reason = self._qualifies()
-        self.ok = self.reason is None
-        if self.ok:
-            self._build()
+        self._checked = False
+        self._reason: Optional[str] = None
+
+    # The kernel lives in a library of its own that takes half a minute to compile, so nothing
+    # here touches it before somebody switches the kernel on or asks whether the model fits.
+    def _ensure(self) -> None:
+        if not self._checked:
+            self._checked = True
+            self._reason = self._qualifies()
+            if self._reason is None:
+                self._build()
+
+    @property
+    def reason(self) -> Optional[str]:
+        self._ensure()
+        return self._reason
+
+    @property
+    def ok(self) -> bool:
+        return self.reason is None
 
     # -- does the model fit the kernel? ------------------------------------------------
     def _qualifies(self) -> Optional[str]:
@@ -80,7 +96,7 @@ class StepKernel:
             elif key != first:
                 return "layers differ in their sizes or constants"
         a = m.layers[m.spec.schedule[0].layer].mixer
-        if a.nh // a.nkv > 8 or not ops.lib().cretif_decode_step_supported(1, a.hd):
+        if a.nh // a.nkv > 8 or not ops.step_lib().cretif_decode_step_supported(1, a.hd):
             return "head size or group size outside the kernel's range"
         if self.cache.block_tokens != 64:
             return "cache blocks are not 64 tokens"
@@ -90,7 +106,7 @@ class StepKernel:
 
     # -- per-visit records ---------------------------------------------------------------
     def _build(self) -> None:
-        m, cache, L = self.model, self.cache, ops.lib()
+        m, cache, L = self.model, self.cache, ops.step_lib()
         dev = m.device
         size = L.cretif_step_layer_bytes()
         sched = m.spec.schedule
@@ -114,7 +130,7 @@ class StepKernel:
                 ctypes.c_void_p(kv.table.data_ptr()), kv.table.stride(0),
                 int(entry.cache is None))
             if rc != 0:
-                self.ok, self.reason = False, f"layer record {i} refused (status {rc})"
+                self._reason = f"layer record {i} refused (status {rc})"
                 return
         self.layers_dev = host.to(dev)
         a = m.layers[sched[0].layer].mixer
@@ -143,7 +159,7 @@ class StepKernel:
 
     def takes(self, ctx) -> bool:
         return (_enabled and self.ok and ctx.is_decode and ctx.T <= MAX_TOKENS
-                and bool(ops.lib().cretif_decode_step_supported(ctx.T, self.a.hd)))
+                and bool(ops.step_lib().cretif_decode_step_supported(ctx.T, self.a.hd)))
 
     def run(self, ctx, want_rows) -> torch.Tensor:
         """Logits [wanted, vocab] of a decode step (every sequence brings one token)."""
@@ -174,6 +190,6 @@ class StepKernel:
             0 if want_rows is None else want_rows.data_ptr(), logits.data_ptr(),
             self.barrier.data_ptr(), ctx.fault.data_ptr(),
             0 if self.stamps is None else self.stamps.data_ptr())
-        ops._check(ops.lib().cretif_decode_step(ints, floats, ptrs, self.ctas, ops._stream()),
+        ops._check(ops.step_lib().cretif_decode_step(ints, floats, ptrs, self.ctas, ops._stream()),
                    "decode_step")
         return logits

@@ -94,6 +94,10 @@ int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const voi
                            float* part_o, float* part_ml, int* counters, unsigned int* fault,
                            void* stream);
 
+// Tuning aid: depth of that kernel's ring of K/V stages (2..6; 0, the default, chooses per
+// launch).  Returns the old setting.
+int cretif_attn_decode_stages(int n);
+
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,

@@ -9,10 +9,12 @@ namespace cretif {
 
 // Tuning aid: a device buffer of 10 x 16 timestamps the next launches fill (see the kernel).
 static unsigned long long* g_dm_stamps = nullptr;
+// Tuning aid: depth of the K/V ring (3..6); 0 chooses per launch.
+static int g_dm_stages = 0;
 
 template <int HD16>
-static size_t dm_smem_bytes(bool cluster) {
-  return dm_smem_core<HD16>(cluster) + 1024;
+static size_t dm_smem_bytes(bool cluster, int n_stages) {
+  return dm_smem_core<HD16>(cluster, n_stages) + 1024;
 }
 
 template <int HD16, bool CLUSTER>
@@ -21,13 +23,27 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
                      const int* seq_slot, int nh, int nkv, float scale_log2, int window,
                      float* part_o, float* part_ml, void* out, int ldo, int* counters,
                      unsigned int* fault, dim3 grid, cudaStream_t st) {
-  const size_t smem = dm_smem_bytes<HD16>(CLUSTER);
-  static bool configured = false;
-  if (!configured) {
+  // Few CTAs (at most two per SM) walk many tiles each: a deeper ring keeps more of the cache
+  // in flight per CTA, as long as two CTAs still fit an SM.
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  int n_stages = g_dm_stages ? g_dm_stages : kDmStages;
+  if (!g_dm_stages && (long long)grid.x * grid.y * grid.z <= 2LL * sm_count) {
+    n_stages = kDmMaxStages;
+    while (n_stages > kDmStages && dm_smem_bytes<HD16>(CLUSTER, n_stages) > 112 * 1024) --n_stages;
+  }
+  const size_t smem = dm_smem_bytes<HD16>(CLUSTER, n_stages);
+  static size_t configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD16, CLUSTER>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   // Launched as a programmatic dependent of the kernel before it: set-up, the block table and
   // the first cache tiles run under that kernel's tail.
@@ -51,7 +67,7 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, attn_decode_mma_kernel<HD16, CLUSTER>, mk, mv, (const __nv_bfloat16*)q, ldq, table,
       table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,
-      (__nv_bfloat16*)out, ldo, counters, fault, g_dm_stamps);
+      (__nv_bfloat16*)out, ldo, counters, fault, g_dm_stamps, n_stages);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 
@@ -61,6 +77,12 @@ using namespace cretif;
 
 extern "C" void cretif_attn_decode_stamps(unsigned long long* device_buffer) {
   g_dm_stamps = device_buffer;
+}
+
+extern "C" int cretif_attn_decode_stages(int n) {
+  const int was = g_dm_stages;
+  g_dm_stages = n <= 0 ? 0 : (n < 2 ? 2 : (n > kDmMaxStages ? kDmMaxStages : n));
+  return was;
 }
 
 extern "C" int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const void* kc,

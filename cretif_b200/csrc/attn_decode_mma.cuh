@@ -35,7 +35,8 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
 constexpr int kDmWarps = 4;                 // consumer warps
 constexpr int kDmThreads = (kDmWarps + 1) * 32;
 constexpr int kDmTile = 64;
-constexpr int kDmStages = 3;
+constexpr int kDmStages = 3;                // ring of K/V stages by default ...
+constexpr int kDmMaxStages = 6;             // ... and at most (a launch with few CTAs goes deeper)
 constexpr int kDmClusterMax = 8;            // ranges merged inside one cluster (portable size)
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -99,7 +100,8 @@ __device__ __forceinline__ void attn_decode_mma_item(
     const int* __restrict__ seq_slot, int nh, int nkv, float scale_log2, int window,
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
-    int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr) {
+    int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr,
+    int n_stages = kDmStages) {
   constexpr int hd = HD16 * 16;
   // Tuning aid: with a buffer given, lane 0 of every warp of the first CTA notes the time at
   // which it passes each phase ([warp][16]); the CTA that merges notes its own at [8][..].
@@ -116,10 +118,10 @@ __device__ __forceinline__ void attn_decode_mma_item(
   constexpr int kSub = (hd + 63) / 64;                 // 64-wide column groups of a tile
   constexpr int kTileBytes = kSub * kDmTile * 128;     // one of K or V
   unsigned char* ktiles = smem;
-  unsigned char* vtiles = smem + kDmStages * kTileBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * kDmStages * kTileBytes);
-  uint64_t* empty = full + kDmStages;
-  volatile int* abort = reinterpret_cast<volatile int*>(empty + kDmStages);
+  unsigned char* vtiles = smem + n_stages * kTileBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * n_stages * kTileBytes);
+  uint64_t* empty = full + kDmMaxStages;
+  volatile int* abort = reinterpret_cast<volatile int*>(empty + kDmMaxStages);
   int* is_last = const_cast<int*>(abort) + 1;
   float* mrg = reinterpret_cast<float*>(const_cast<int*>(abort) + 4);   // warps' partials
   // cluster merge: what the warps of all ranges send this CTA: [range][warp][8 heads]{m, l},
@@ -167,6 +169,9 @@ __device__ __forceinline__ void attn_decode_mma_item(
     // before the kernel waits for the one before it (programmatic dependent launch), the
     // tile of the new token after.  Block ids are read 32 at a time.
     bool waited = false;
+    // stage and turn of the ring for tile i (carried on from earlier items; stepped, not
+    // divided, per tile)
+    int st = (int)(it_base % (uint32_t)n_stages), turn = (int)(it_base / (uint32_t)n_stages);
     for (int i0 = 0; i0 < my_tiles; i0 += 32) {
       const int mine = i0 + lane < my_tiles ? tab[t_begin + i0 + lane] : 0;
       const int n = min(32, my_tiles - i0);
@@ -175,14 +180,13 @@ __device__ __forceinline__ void attn_decode_mma_item(
       for (int j = 0; j < n && go; ++j) {
         const int i = i0 + j;
         const int blk = __shfl_sync(0xffffffffu, mine, j);
-        const uint32_t it = it_base + i;
-        const int s = it % kDmStages;
-        if (!waited && (i >= kDmStages || t_begin + i == n_tiles - 1)) {
+        const int s = st;
+        if (!waited && (i >= n_stages || t_begin + i == n_tiles - 1)) {
           asm volatile("griddepcontrol.wait;" ::: "memory");
           waited = true;
         }
         if (lane == 0) {
-          if (it >= kDmStages && !tc::mbar_wait(&empty[s], (uint32_t)((it / kDmStages - 1) & 1), abort)) {
+          if (turn > 0 && !tc::mbar_wait(&empty[s], (uint32_t)((turn - 1) & 1), abort)) {
             go = false;
           } else {
             if (blk < 0) atomicOr(fault, kFaultBlockTable);
@@ -195,6 +199,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
             }
           }
         }
+        if (++st == n_stages) { st = 0; ++turn; }
         go = __shfl_sync(0xffffffffu, go, 0);
         if (i == 0) DM_STAMP(3);
       }
@@ -224,10 +229,9 @@ __device__ __forceinline__ void attn_decode_mma_item(
     float m = -INFINITY, l = 0.f;         // of row r (partial over this thread's keys for l)
     const int mat = lane >> 3, rin = lane & 7;
     bool ok = true;
+    int s = (int)(it_base % (uint32_t)n_stages), turn = (int)(it_base / (uint32_t)n_stages);
     for (int i = 0; i < my_tiles; ++i) {
-      const uint32_t it = it_base + i;
-      const int s = it % kDmStages;
-      if (!tc::mbar_wait(&full[s], (uint32_t)((it / kDmStages) & 1), abort)) { ok = false; break; }
+      if (!tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort)) { ok = false; break; }
       if (i == 0) DM_STAMP(4);
       const uint32_t kbase = tc::smem_u32(ktiles + s * kTileBytes);
       const uint32_t vbase = tc::smem_u32(vtiles + s * kTileBytes);
@@ -294,6 +298,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
       }
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&empty[s]);
+      if (++s == n_stages) { s = 0; ++turn; }
     }
     (void)ok;
     DM_STAMP(5);
@@ -464,11 +469,11 @@ __device__ __forceinline__ void attn_decode_mma_item(
 
 // Shared-memory bytes of one CTA (without alignment slack) and the once-per-kernel set-up.
 template <int HD16>
-__host__ __device__ constexpr size_t dm_smem_core(bool cluster = false) {
+__host__ __device__ constexpr size_t dm_smem_core(bool cluster = false, int n_stages = kDmStages) {
   constexpr int hd = HD16 * 16;
   constexpr int kSub = (hd + 63) / 64;
-  size_t bytes = (size_t)2 * kDmStages * kSub * kDmTile * 128;   // K and V stages
-  bytes += 2 * kDmStages * 8 + 16;                                // barriers, abort, is_last
+  size_t bytes = (size_t)2 * n_stages * kSub * kDmTile * 128;    // K and V stages
+  bytes += 2 * kDmMaxStages * 8 + 16;                             // barriers, abort, is_last
   bytes += dm_mrg_floats<HD16>() * 4;
   if (cluster)     // m, l of every warp of every range; a share of the outputs from each
     bytes += (size_t)kDmClusterMax * kDmWarps * 8 * 2 * 4 +
@@ -477,15 +482,15 @@ __host__ __device__ constexpr size_t dm_smem_core(bool cluster = false) {
 }
 
 template <int HD16>
-__device__ __forceinline__ void dm_init(unsigned char* smem) {
+__device__ __forceinline__ void dm_init(unsigned char* smem, int n_stages = kDmStages) {
   constexpr int hd = HD16 * 16;
   constexpr int kSub = (hd + 63) / 64;
   constexpr int kTileBytes = kSub * kDmTile * 128;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * kDmStages * kTileBytes);
-  uint64_t* empty = full + kDmStages;
-  int* abort = reinterpret_cast<int*>(empty + kDmStages);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * n_stages * kTileBytes);
+  uint64_t* empty = full + kDmMaxStages;
+  int* abort = reinterpret_cast<int*>(empty + kDmMaxStages);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kDmStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], kDmWarps); }
+    for (int s = 0; s < n_stages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], kDmWarps); }
     *abort = 0;
     tc::fence_barrier_init();
   }
@@ -502,7 +507,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        const int* __restrict__ seq_slot, int nh, int nkv, float scale_log2,
                        int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                        __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
-                       unsigned int* __restrict__ fault, unsigned long long* stamps) {
+                       unsigned int* __restrict__ fault, unsigned long long* stamps,
+                       int n_stages) {
   extern __shared__ unsigned char smem_raw[];
   if (stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
     unsigned long long t;
@@ -512,13 +518,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  dm_init<HD16>(smem);
+  dm_init<HD16>(smem, n_stages);
   if (CLUSTER) cluster_arrive();      // "this CTA runs": waited for before anything is sent
   uint32_t it_base = 0;
   attn_decode_mma_item<HD16, CLUSTER>(smem, &map_k, &map_v, q, ldq, table, table_stride, tok_pos,
                                       tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o,
                                       part_ml, out, ldo, counters, fault, blockIdx.x, gridDim.x,
-                                      blockIdx.y, blockIdx.z, it_base, stamps);
+                                      blockIdx.y, blockIdx.z, it_base, stamps, n_stages);
 }
 
 }  // namespace cretif

@@ -168,11 +168,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int sub = 0; sub < n_sub; ++sub)
         tc::tma_load_2d(smem + L.q + sub * kPfBQ * 128, &map_q, h * hd + 64 * sub, tok0 + q0,
                         q_full);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % kPfStages;
-        if (j >= kPfStages &&
-            !tc::mbar_wait(&kv_empty[s], (uint32_t)((j / kPfStages - 1) & 1), abort))
-          break;
+      // (the ring's stage and turn are stepped, not divided: its depth is a run-time value)
+      for (int j = 0, s = 0, turn = 0; j < n_tiles; ++j, s = s + 1 == kPfStages ? 0 : s + 1,
+               turn += s == 0) {
+        if (turn > 0 && !tc::mbar_wait(&kv_empty[s], (uint32_t)((turn - 1) & 1), abort)) break;
         tc::mbar_expect_tx(&kv_full[s], (uint32_t)(2 * n_sub * kPfBK * 128));
         for (int half = 0; half < 2; ++half) {
           // a step past the last block loads that block again: its keys are masked, and the
@@ -193,9 +192,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK);
       const uint32_t idesc_pv = tc::instr_desc_bf16(kPfBQ, hd) | (1u << 16);   // B is MN-major
       const int k_steps = hd >> 4;
+      int sc_s = 0, sc_turn = 0;            // stage and turn of the next call of scores()
       auto scores = [&](int j) {            // S[j & 1] = Q K_j^T, once K_j has landed
-        const int s = j % kPfStages;
-        if (!tc::mbar_wait(&kv_full[s], (uint32_t)((j / kPfStages) & 1), abort)) return false;
+        const int s = sc_s;
+        if (!tc::mbar_wait(&kv_full[s], (uint32_t)(sc_turn & 1), abort)) return false;
+        if (++sc_s == kPfStages) { sc_s = 0; ++sc_turn; }
         tc::tc_fence_after();
         for (int kk = 0; kk < k_steps; ++kk) {
           const int sub = kk >> 2, in = kk & 3;
@@ -209,8 +210,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       };
       bool ok = tc::mbar_wait(q_full, 0u, abort);
       if (ok && n_tiles > 0) ok = scores(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kPfStages;
+      for (int j = 0, s = 0; j < n_tiles && ok; ++j, s = s + 1 == kPfStages ? 0 : s + 1) {
         // The next step's scores go to the other buffer, which the softmax threads left
         // before they signalled P of step j - 1 (waited for below, one step ago).
         if (j + 1 < n_tiles && !(ok = scores(j + 1))) break;

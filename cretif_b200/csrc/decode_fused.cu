@@ -152,7 +152,7 @@ extern "C" int cretif_fused_linear(const void* X, int ldx, const float* H, const
   p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K; p.ldw = ldw;
   p.X = (const __nv_bfloat16*)X; p.ldx = ldx; p.H = H; p.norm_w = norm_w; p.rows = rows;
   p.eps = eps; p.C = C; p.ldc = ldc; p.c_dt = c_dt; p.accumulate = accumulate; p.fault = fault;
-  if (!common_ok(p) || ldc < N || (c_dt != kF32 && c_dt != kBF16) ||
+  if (!common_ok(p) || !derive_fields(p) || ldc < N || (c_dt != kF32 && c_dt != kBF16) ||
       (c_dt == kBF16 && accumulate))
     return kBadArgument;
   const int tiles = (N + kFuRows - 1) / kFuRows;
@@ -179,8 +179,8 @@ extern "C" int cretif_fused_qkv_rope(const float* H, const float* norm_w, float 
   p.seq_slot = seq_slot; p.table = table; p.table_stride = table_stride;
   p.kc = (__nv_bfloat16*)kc; p.vc = (__nv_bfloat16*)vc; p.bt = bt; p.write_cache = write_cache;
   p.fault = fault;
-  if (!common_ok(p) || !H || nh <= 0 || nkv <= 0 || hd % 16 || hd <= 0 || bt <= 0 ||
-      ldq < nh * hd)
+  if (!common_ok(p) || !derive_fields(p) || !H || nh <= 0 || nkv <= 0 || hd % 16 || hd <= 0 ||
+      bt <= 0 || ldq < nh * hd)
     return kBadArgument;
   return dispatch_nt<kProNorm, kEpiRope>(p, p.N / kFuRows, (cudaStream_t)stream);
 }
@@ -193,7 +193,8 @@ extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, fl
   FusedParams p = {};
   p.W = (const __nv_bfloat16*)Wgu; p.M = M; p.N = 2 * I; p.K = K; p.ldw = ldw;
   p.H = H; p.norm_w = norm_w; p.eps = eps; p.act = (__nv_bfloat16*)act; p.I = I; p.gu_block = gu_block; p.fault = fault;
-  if (!common_ok(p) || !H || I <= 0 || gu_block < 0 || (gu_block && (I % gu_block || gu_block % 8)))
+  if (!common_ok(p) || !derive_fields(p) || !H || I <= 0 || gu_block < 0 ||
+      (gu_block && (I % gu_block || gu_block % 8)))
     return kBadArgument;
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
 }

@@ -32,6 +32,27 @@ constexpr int kFuRows = 16;
 enum Prologue : int { kProPlain = 0, kProNorm = 1 };
 enum Epilogue : int { kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2 };
 
+// n / d for 0 <= n < 65536 without a division instruction (an integer division in the short
+// dependent chains of these kernels costs about 0.1 us): a shift for powers of two, else a
+// multiplication by ceil(2^32 / d), exact for n, d < 65536.
+struct FastDiv {
+  int d, shift;
+  uint32_t magic;
+};
+__host__ __device__ inline FastDiv make_fast_div(int d) {
+  FastDiv f = {d > 0 ? d : 1, -1, 0u};
+  if ((f.d & (f.d - 1)) == 0) {
+    f.shift = 0;
+    while ((1 << f.shift) < f.d) ++f.shift;
+  } else {
+    f.magic = 0xffffffffu / (uint32_t)f.d + 1u;
+  }
+  return f;
+}
+__device__ __forceinline__ int fast_div(const FastDiv& f, int n) {
+  return f.shift >= 0 ? n >> f.shift : (int)__umulhi((uint32_t)n, f.magic);
+}
+
 struct FusedParams {
   // product
   const __nv_bfloat16* W;   // [N, K]
@@ -64,6 +85,9 @@ struct FusedParams {
   // epilogue silu
   __nv_bfloat16* act;       // [M, I]
   int I, gu_block;          // gu_block > 0: gate/up rows interleaved in groups of that size
+  // set by the launcher from the above
+  FastDiv gu_div, tph_div;  // by gu_block; by tiles per head (hd / 16)
+  int bt_shift;             // log2 of bt (a power of two)
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -73,6 +97,20 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Fills the derived fields; false if a size is outside what they can express.
+__host__ __device__ inline bool derive_fields(FusedParams& p) {
+  p.gu_div = make_fast_div(p.gu_block > 0 ? p.gu_block : 1);
+  p.tph_div = make_fast_div(p.hd >= 16 ? p.hd >> 4 : 1);
+  p.bt_shift = 0;
+  if (p.bt > 0) {
+    if (p.bt & (p.bt - 1)) return false;                 // cache blocks are powers of two
+    while ((1 << p.bt_shift) < p.bt) ++p.bt_shift;
+  }
+  // the multiplication that stands for a division is exact below 65536
+  if (p.gu_div.shift < 0 && (p.I >= 65536 || p.gu_block >= 65536)) return false;
+  return true;
 }
 
 // Weight row of tile row r (0..15) of CTA `tile`; -1 if beyond the matrix.
@@ -85,13 +123,14 @@ __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
     const int i = tile * 8 + (r & 7);
     if (i >= p.I) return -1;
     if (p.gu_block) {
-      const int g = (i / p.gu_block) * 2 * p.gu_block + i % p.gu_block;
+      const int blk = fast_div(p.gu_div, i);        // i = blk * gu_block + rest
+      const int g = i + blk * p.gu_block;           // = blk * 2 gu_block + rest
       return r < 8 ? g : g + p.gu_block;
     }
     return r < 8 ? i : p.I + i;
   } else {
     const int tiles_per_head = p.hd >> 4;
-    const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+    const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
     if (head >= p.nh + p.nkv) return head * p.hd + t * 16 + r;        // v: plain rows
     const int j = t * 8 + (r & 7);                                    // rotary pair index
     if (p.pairing) return head * p.hd + 2 * j + (r >> 3);
@@ -127,10 +166,10 @@ __device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, Epi
     if (i < 8 * p.M) {
       const int m = i >> 3, pr = i & 7;
       const int tiles_per_head = p.hd >> 4;
-      const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+      const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
       a.pos = p.tok_pos[m];
       if (head >= p.nh && p.write_cache)
-        a.blk = p.table[(size_t)p.seq_slot[p.tok_seq[m]] * p.table_stride + a.pos / p.bt];
+        a.blk = p.table[(size_t)p.seq_slot[p.tok_seq[m]] * p.table_stride + (a.pos >> p.bt_shift)];
       if (head < p.nh + p.nkv) {
         const int j = t * 8 + pr;
         a.cs = p.cos_t[(size_t)a.pos * (p.hd >> 1) + j];
@@ -179,7 +218,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
         p.act[(size_t)m * p.I + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
       } else {
         const int tiles_per_head = p.hd >> 4;
-        const int head = tile / tiles_per_head, t = tile - head * tiles_per_head;
+        const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
         const int pos = ahead.pos;
         size_t cache_row = 0;
         bool cache_ok = false;
@@ -189,7 +228,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
           else {
             cache_ok = true;
             const int kvh = head < p.nh + p.nkv ? head - p.nh : head - p.nh - p.nkv;
-            cache_row = (((size_t)blk * p.nkv + kvh) * p.bt + (pos % p.bt)) * p.hd;
+            cache_row = (((size_t)blk * p.nkv + kvh) * p.bt + (pos & (p.bt - 1))) * p.hd;
           }
         }
         if (head >= p.nh + p.nkv) {                      // v: rows t*16 + pr and + 8, no rotation

@@ -179,6 +179,7 @@ decode_step_kernel(const StepParams p) {
       f.nh = p.nh; f.nkv = p.nkv; f.hd = p.hd; f.tok_pos = p.tok_pos; f.tok_seq = p.tok_seq;
       f.seq_slot = p.seq_slot; f.table = L.table; f.table_stride = L.table_stride;
       f.kc = L.kc; f.vc = L.vc; f.bt = p.bt; f.write_cache = L.write_cache; f.fault = p.fault;
+      derive_fields(f);
       skinny_fused_tiles<NT, kProNorm, kEpiRope>(f, qkv_rows / kFuRows, gemv_smem, cta, P, false);
     }
     grid_barrier(p.barrier, ++done * P, p.fault, true);
@@ -202,6 +203,7 @@ decode_step_kernel(const StepParams p) {
       FusedParams f = {};
       f.W = L.w_o; f.M = p.B; f.N = p.H; f.K = q_dim; f.ldw = q_dim;
       f.X = p.attn; f.ldx = q_dim; f.C = p.h; f.ldc = p.H; f.c_dt = kF32; f.accumulate = 1;
+      derive_fields(f);
       skinny_fused_tiles<NT, kProPlain, kEpiPlain>(f, (p.H + kFuRows - 1) / kFuRows, gemv_smem,
                                                    cta, P, false);
     }
@@ -212,6 +214,7 @@ decode_step_kernel(const StepParams p) {
       f.W = L.w_gu; f.M = p.B; f.N = 2 * p.I; f.K = p.H; f.ldw = p.H;
       f.H = p.h; f.norm_w = L.norm2; f.eps = L.eps2; f.act = p.act; f.I = p.I;
       f.gu_block = p.gu_block;
+      derive_fields(f);
       skinny_fused_tiles<NT, kProNorm, kEpiSilu>(f, (p.I + 7) / 8, gemv_smem, cta, P, false);
     }
     grid_barrier(p.barrier, ++done * P, p.fault);
@@ -220,6 +223,7 @@ decode_step_kernel(const StepParams p) {
       FusedParams f = {};
       f.W = L.w_down; f.M = p.B; f.N = p.H; f.K = p.I; f.ldw = p.I;
       f.X = p.act; f.ldx = p.I; f.C = p.h; f.ldc = p.H; f.c_dt = kF32; f.accumulate = 1;
+      derive_fields(f);
       skinny_fused_tiles<NT, kProPlain, kEpiPlain>(f, (p.H + kFuRows - 1) / kFuRows, gemv_smem,
                                                    cta, P, false);
     }
@@ -231,6 +235,7 @@ decode_step_kernel(const StepParams p) {
     f.W = p.head; f.M = p.n_want; f.N = p.V; f.K = p.H; f.ldw = p.H;
     f.H = p.h; f.norm_w = p.final_norm; f.rows = p.want_rows; f.eps = p.eps_final;
     f.C = p.logits; f.ldc = p.V; f.c_dt = kF32; f.accumulate = 0;
+    derive_fields(f);
     skinny_fused_tiles<NT, kProNorm, kEpiPlain>(f, (p.V + kFuRows - 1) / kFuRows, gemv_smem, cta,
                                                 P, false);
   }

@@ -50,7 +50,7 @@ __device__ __forceinline__ void tile_groups(const FusedParams& p, int tile, int&
                                             bool& paired) {
   paired = false;
   row_a = tile_row<EPI>(p, tile, 0);
-  if (EPI == kEpiRope && p.pairing && tile / (p.hd >> 4) < p.nh + p.nkv) {
+  if (EPI == kEpiRope && p.pairing && fast_div(p.tph_div, tile) < p.nh + p.nkv) {
     row_b = row_a + 8;       // interleaved pairs: tile row r is weight row 2 (r & 7) + (r >> 3)
     paired = true;
   } else {
@@ -98,22 +98,35 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
     // An SM serves its requests in order, so what is asked for after the wait (x, or the
     // residual rows of the norm prologue) arrives behind every weight copy issued before it:
     // only n_early stages of weights go ahead, the rest follow the step's own inputs.
-    auto fill = [&](int it, bool weights, bool xrows) {
-      const int tile = blockIdx.x + (it / n_steps) * gridDim.x, step = it % n_steps;
-      const int s = it % n_stages, k0 = step * kStK;
-      const int boxes = min(kStBoxes, (p.K - k0 + kStBoxK - 1) / kStBoxK);
+    // Where a fill goes is kept in a cursor that only ever steps forward (tile, step, stage,
+    // turn of the ring): nothing on this thread's path divides.
+    struct Cursor {
+      int tile, step, s, turn, row_a, row_b;
+    };
+    auto rows_of_tile = [&](Cursor& c) {
+      bool paired;
+      if (c.tile < n_tiles) tile_groups<EPI>(p, c.tile, c.row_a, c.row_b, paired);
+    };
+    auto advance = [&](Cursor& c) {
+      if (++c.s == n_stages) { c.s = 0; ++c.turn; }
+      if (++c.step == n_steps) {
+        c.step = 0;
+        c.tile += gridDim.x;
+        rows_of_tile(c);
+      }
+    };
+    auto fill = [&](const Cursor& c, bool weights, bool xrows) {
+      const int s = c.s, k0 = c.step * kStK;
+      const int boxes = min(kStBoxes, (p.K - k0 + kStBoxK - 1) / kStBoxK);   // by a constant
       if (weights) {
         // a box is counted whole, whatever part of it lies beyond the matrix
         const int per_box = 2 * kStGroup + (PRO == kProPlain ? NT * kStGroup : 0);
         tc::mbar_expect_tx(&full[s], (uint32_t)(boxes * per_box));
-        int row_a, row_b;
-        bool paired;
-        tile_groups<EPI>(p, tile, row_a, row_b, paired);
         unsigned char* ws = wst + (size_t)s * kStW;
         for (int b = 0; b < boxes; ++b) {
-          tc::tma_load_2d(ws + (size_t)b * kStGroup, &map_w, k0 + b * kStBoxK, row_a, &full[s]);
+          tc::tma_load_2d(ws + (size_t)b * kStGroup, &map_w, k0 + b * kStBoxK, c.row_a, &full[s]);
           tc::tma_load_2d(ws + (size_t)(kStBoxes + b) * kStGroup, &map_w, k0 + b * kStBoxK,
-                          row_b, &full[s]);
+                          c.row_b, &full[s]);
         }
       }
       if (PRO == kProPlain && xrows) {
@@ -124,20 +137,23 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
       }
     };
     const int ahead = min(total, n_stages), early = min(ahead, n_early);
+    Cursor cur = {(int)blockIdx.x, 0, 0, 0, 0, 0};
+    rows_of_tile(cur);
+    Cursor first = cur;
     if (lane == 0) {
       tc::tma_prefetch_descriptor(&map_w);
       if (PRO == kProPlain) tc::tma_prefetch_descriptor(&map_x);
-      for (int it = 0; it < early; ++it) fill(it, true, false);     // weights need nobody
+      for (int it = 0; it < early; ++it, advance(cur)) fill(cur, true, false);   // weights need nobody
     }
     __syncwarp();
     asm volatile("griddepcontrol.wait;" ::: "memory");               // x comes from the kernel before
     if (PRO == kProNorm) asm volatile("bar.sync 2, %0;" ::"n"(kStThreads) : "memory");
     if (lane == 0) {
-      for (int it = 0; it < ahead; ++it) fill(it, it >= early, true);
-      for (int it = ahead; it < total; ++it) {
-        if (!tc::mbar_wait(&empty[it % n_stages], (uint32_t)((it / n_stages - 1) & 1), abort))
-          break;
-        fill(it, true, true);
+      cur = first;
+      for (int it = 0; it < ahead; ++it, advance(cur)) fill(cur, it >= early, true);
+      for (int it = ahead; it < total; ++it, advance(cur)) {
+        if (!tc::mbar_wait(&empty[cur.s], (uint32_t)((cur.turn - 1) & 1), abort)) break;
+        fill(cur, true, true);
       }
     }
   } else {
@@ -212,13 +228,13 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
     } else {
       asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    int it = 0;
+    int s = 0, turn = 0;                         // the ring's stage and how often it has turned
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       EpiAhead ahead;
       epi_prefetch<EPI>(p, tile, ahead);
       // where this lane's two weight rows (tile rows r and r + 8) lie within a stage
       int off_a = r * kStRowB, off_b = kStBoxes * kStGroup + r * kStRowB;
-      if (EPI == kEpiRope && p.pairing && tile / (p.hd >> 4) < p.nh + p.nkv) {
+      if (EPI == kEpiRope && p.pairing && fast_div(p.tph_div, tile) < p.nh + p.nkv) {
         const int wa = 2 * r, wb = 2 * r + 1;
         off_a = (wa >> 3) * kStBoxes * kStGroup + (wa & 7) * kStRowB;
         off_b = (wb >> 3) * kStBoxes * kStGroup + (wb & 7) * kStRowB;
@@ -228,9 +244,9 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
       for (int t = 0; t < NT; ++t)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
-      for (int step = 0; step < n_steps; ++step, ++it) {
-        const int s = it % n_stages, k0 = step * kStK;
-        tc::mbar_wait(&full[s], (uint32_t)((it / n_stages) & 1), abort);   // bounded; see abort
+      for (int step = 0; step < n_steps; ++step) {
+        const int k0 = step * kStK;
+        tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort);   // bounded; see abort
         const unsigned char* ws = wst + (size_t)s * kStW;
 #pragma unroll
         for (int j = 0; j < kStK / (32 * kFuWarps); ++j) {   // chunks of 32 columns, two per warp
@@ -259,6 +275,7 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
         }
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&empty[s]);
+        if (++s == n_stages) { s = 0; ++turn; }
       }
 #pragma unroll
       for (int t = 0; t < NT; ++t) {

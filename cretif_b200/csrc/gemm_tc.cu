@@ -141,22 +141,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int kb = 0; kb < early; ++kb)
         tc::tma_load_2d(smem + kb * L::kStage, &map_a, kb * kTcBK, m0, &full[kb]);
       stamp(3);
+      // (stage and turn of the ring are stepped, not divided: the depth is a run-time value)
+      int s = early == kTcStages ? 0 : early, turn = early == kTcStages ? 1 : 0;
       for (int kb = early; kb < num_kb; ++kb) {
-        const int s = kb % kTcStages;
-        if (!tc::mbar_wait(&empty[s], (uint32_t)((kb / kTcStages - 1) & 1), abort)) break;
+        if (!tc::mbar_wait(&empty[s], (uint32_t)((turn - 1) & 1), abort)) break;
         unsigned char* stage = smem + s * L::kStage;
         tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
         tc::tma_load_2d(stage, &map_a, kb * kTcBK, m0, &full[s]);
         tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, n0, &full[s]);
+        if (++s == kTcStages) { s = 0; ++turn; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc_bf16(kTcBM, BN);
       bool ok = true;
+      int s = 0, turn = 0;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % kTcStages;
-        ok = tc::mbar_wait(&full[s], (uint32_t)((kb / kTcStages) & 1), abort);
+        ok = tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort);
         if (!ok) break;
         tc::tc_fence_after();
         if (kb == 0) stamp(2);
@@ -167,6 +169,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int k = 0; k < kTcBK / 16; ++k)       // 16 bf16 = 32 bytes = 2 descriptor units
           tc::umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
         tc::umma_commit(&empty[s]);                // frees the stage when these MMAs are done
+        if (++s == kTcStages) { s = 0; ++turn; }
       }
       tc::umma_commit(acc_full);                   // accumulator complete
       stamp(3);

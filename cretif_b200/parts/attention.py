@@ -122,7 +122,8 @@ class Attention(Part):
         if (_force_plain or not fused_steps_enabled() or self.dtype != torch.bfloat16
                 or ctx.T > FUSED_MAX_TOKENS or type(norm) is not RMSNorm
                 or type(self.position) is not Rotary or self.position.rot_dim != self.hd
-                or cache.kv is None or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
+                or cache.kv is None or cache.kv.block_tokens & (cache.kv.block_tokens - 1)
+                or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
                 or not ops.fused_supported(ctx.T, self.q_dim, self.w_o, norm=False)):
             return False
         kv = cache.kv

@@ -180,6 +180,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m = m0 + quad * 32 + lane;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(2);
+    // Rotary epilogue: where this thread's row goes (position → cache block → address) is a
+    // chain of dependent loads that does not need the product: it runs while the product does.
+    const int head = EPI == kTcRope ? n0 / ep.hd : 0, half = ep.hd >> 1;
+    int pos = 0;
+    __nv_bfloat16* dst = nullptr;             // where this row's head goes
+    if (EPI == kTcRope && m < M) {
+      pos = ep.tok_pos[m];
+      if (head < ep.nh) {
+        dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
+      } else if (ep.write_cache) {
+        const int slot = ep.seq_slot[ep.tok_seq[m]];
+        const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
+        if (blk < 0) {
+          atomicOr(fault, kFaultBlockTable);
+        } else {
+          const bool is_k = head < ep.nh + ep.nkv;
+          const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
+          dst = (is_k ? ep.kc : ep.vc) +
+                (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
+        }
+      }
+    }
     const bool ok = tc::mbar_wait(acc_full, 0u, abort);
     tc::tc_fence_after();
     stamp(3);
@@ -244,26 +266,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
     if (ok && EPI == kTcRope) {
-      const int head = n0 / ep.hd, half = ep.hd >> 1;
-      const bool valid = m < M;
-      const int pos = valid ? ep.tok_pos[m] : 0;
-      __nv_bfloat16* dst = nullptr;           // where this row's head goes
-      if (valid) {
-        if (head < ep.nh) {
-          dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
-        } else if (ep.write_cache) {
-          const int slot = ep.seq_slot[ep.tok_seq[m]];
-          const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
-          if (blk < 0) {
-            atomicOr(fault, kFaultBlockTable);
-          } else {
-            const bool is_k = head < ep.nh + ep.nkv;
-            const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
-            dst = (is_k ? ep.kc : ep.vc) +
-                  (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
-          }
-        }
-      }
       const bool rotate = head < ep.nh + ep.nkv;
       const float* cs = ep.cos_t + (size_t)pos * half;
       const float* sn = ep.sin_t + (size_t)pos * half;

@@ -405,6 +405,15 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   // finished (a no-op when the launch was an ordinary one).
   NormStash<1> stash;
   if (PRO == kProNorm) norm_weight_fetch(p, stash);
+  // Positions, the block table and the rotation table are not the work of the kernel before
+  // this one either: the first tile's epilogue operands are on their way before the wait
+  // (a chain of four dependent loads that the short product would not hide).
+  EpiAhead ahead;
+  bool have_ahead = false;
+  if (EPI == kEpiRope) {
+    epi_prefetch<EPI>(p, tile, ahead);
+    have_ahead = true;
+  }
   if (pdl) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -417,8 +426,8 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   }
 
   for (; tile < n_tiles; tile += tile_stride) {
-    EpiAhead ahead;
-    epi_prefetch<EPI>(p, tile, ahead);
+    if (!have_ahead) epi_prefetch<EPI>(p, tile, ahead);
+    have_ahead = false;
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t)

@@ -160,6 +160,13 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
     // ---------------- consumer warps
     const int r = lane >> 2, c = lane & 3;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    // the first tile's rotary operands (positions, block table, angles) do not wait either
+    EpiAhead ahead;
+    bool have_ahead = false;
+    if (EPI == kEpiRope && (int)blockIdx.x < n_tiles) {
+      epi_prefetch<EPI>(p, blockIdx.x, ahead);
+      have_ahead = true;
+    }
     if (PRO == kProNorm) {
       // The norm's weight depends on nothing: it is in shared memory before the wait ends.
       // After it a warp asks for its token's whole residual row at once and tells the
@@ -230,8 +237,8 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
     }
     int s = 0, turn = 0;                         // the ring's stage and how often it has turned
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      EpiAhead ahead;
-      epi_prefetch<EPI>(p, tile, ahead);
+      if (!have_ahead) epi_prefetch<EPI>(p, tile, ahead);
+      have_ahead = false;
       // where this lane's two weight rows (tile rows r and r + 8) lie within a stage
       int off_a = r * kStRowB, off_b = kStBoxes * kStGroup + r * kStRowB;
       if (EPI == kEpiRope && p.pairing && fast_div(p.tph_div, tile) < p.nh + p.nkv) {

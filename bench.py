@@ -116,7 +116,7 @@ def run_decode(engine, batch, steps, warmup, prompt_len, seed=0):
     from cretif_b200.sampling import SamplingParams
     rng = np.random.default_rng(seed)
     prompts = [rng.integers(0, engine.vocab_size, size=prompt_len).tolist() for _ in range(batch)]
-    be = EngineBackend(engine, SamplingParams(0.0, 0, 42), use_graph=True)
+    be = EngineBackend(engine, SamplingParams(0.0, 0, 42), use_graph=True, run_ahead=False)
     total = prompt_len + warmup + steps + 1
     be.start_batch(list(range(batch)), prompts, [total] * batch)
     try:

@@ -205,19 +205,42 @@ class DecodeRunner:
 
 
 class EngineBackend:
-    """Runs the loop's decisions on an :class:`Engine`."""
+    """Runs the loop's decisions on an :class:`Engine`.
 
-    def __init__(self, engine, params: SamplingParams, use_graph: bool = True):
+    Decode steps run ahead of the host: ``decode`` hands the loop the tokens of the oldest
+    step in flight and keeps ``depth`` further steps launched, so the device never waits for
+    the host to look at tokens, to do the cache's bookkeeping or to launch.  Ids and positions
+    advance on the device, so a step needs nothing from the host as long as the batch's
+    make-up stays the same.  Which sequences have room for another token is known without
+    looking at tokens; what the loop decides from tokens (a stop token) comes one or two steps
+    late: that sequence's part of the steps in flight is dropped, its slot is given back
+    once they have finished, and before a step with another make-up is launched the steps in
+    flight are waited for, because their tokens are that step's input.
+    """
+
+    def __init__(self, engine, params: SamplingParams, use_graph: bool = True,
+                 run_ahead: bool = True):
         self.engine = engine
         self.sampler = Sampler(params, engine.vocab_size)
         self.runner = DecodeRunner(engine, self.sampler, use_graph)
+        self.depth = 2 if run_ahead else 0
         self._loaded: Optional[tuple] = None
+        self._queue: List[dict] = []              # launched, oldest first
+        self._ready: List[Dict[int, int]] = []    # finished and read, not yet handed out
+        self._to_free: List[int] = []
 
     def start_batch(self, request_ids, prompts, reserve_lens) -> None:
         eng = self.engine
         self.request_ids = list(request_ids)
         self.prompts = [list(p) for p in prompts]
+        self.reserve = [int(n) for n in reserve_lens]
         self.slots: List[Optional[int]] = []
+        self._queue, self._ready, self._to_free = [], [], []
+        # pinned buffers for the sampled ids, one per step that can be in flight
+        if len(getattr(self, "_hosts", [[]])[0]) < len(reserve_lens):
+            self._hosts = [torch.empty(len(reserve_lens), dtype=torch.int32).pin_memory()
+                           for _ in range(self.depth + 2)]
+        self._host_at = 0
         try:
             for n in reserve_lens:
                 s = eng.alloc_slot()
@@ -245,36 +268,98 @@ class EngineBackend:
             self.last[i], self.n_sampled[i] = t, 1
         return toks
 
-    def decode(self, active: Sequence[int]) -> List[int]:
-        eng, cache = self.engine, self.engine.cache
+    # -- one step: launch, and (later) collect -----------------------------------------
+    def _launch(self, active: Sequence[int]) -> None:
+        cache = self.engine.cache
         key = tuple(active)
         slots = np.asarray([self.slots[i] for i in active], dtype=np.int64)
         if key != self._loaded:
+            # the state on the device is that of another make-up: this one's comes from the
+            # host, which therefore has to have seen every earlier step
+            assert not self._queue
             self.runner.load(slots, np.asarray([self.last[i] for i in active]),
                              cache.lengths[slots],
                              np.asarray([self.request_ids[i] for i in active]),
                              np.asarray([self.n_sampled[i] for i in active]))
             self._loaded = key
-        cache.begin_step([(int(s), 1) for s in slots])
+        entries = [(int(s), 1) for s in slots]
+        cache.begin_step(entries)
         sampled = self.runner.run()
-        cache.end_step([(int(s), 1) for s in slots])
-        host = self.runner.bufs[len(active)]["host"]
+        cache.end_step(entries)
+        host = self._hosts[self._host_at][:len(active)]
+        self._host_at = (self._host_at + 1) % len(self._hosts)
         host.copy_(sampled, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        toks = host.tolist()
-        for i, t in zip(active, toks):
+        done = torch.cuda.Event()
+        done.record()
+        self._queue.append({"active": key, "host": host, "done": done})
+
+    def _collect(self) -> Dict[int, int]:
+        """Wait for the oldest step in flight; its tokens by position in the batch."""
+        fl = self._queue.pop(0)
+        fl["done"].synchronize()
+        toks = fl["host"].tolist()
+        for i, t in zip(fl["active"], toks):
             self.last[i] = t
             self.n_sampled[i] += 1
-        return toks
+        still = [pos for pos in self._to_free if self._in_flight(pos)]
+        for pos in self._to_free:            # ended by the loop while steps were running
+            if pos not in still:
+                self._free(pos)
+        self._to_free = still
+        return dict(zip(fl["active"], toks))
 
-    def release(self, pos: int) -> None:
+    def _in_flight(self, pos: int) -> bool:
+        return any(pos in fl["active"] for fl in self._queue)
+
+    def _has_room(self, pos: int) -> bool:
+        """Whether the next token sampled for ``pos`` can still be fed back (the cache's
+        lengths already count the steps in flight)."""
+        slot = self.slots[pos]
+        return slot is not None and int(self.engine.cache.lengths[slot]) + 1 <= self.reserve[pos]
+
+    def _run_ahead(self, active: Sequence[int]) -> None:
+        while len(self._queue) + len(self._ready) < self.depth:
+            nxt = tuple(i for i in active if self._has_room(i))
+            if not nxt:
+                return
+            if self._queue and nxt != self._queue[-1]["active"]:
+                if any(i not in self._queue[-1]["active"] for i in nxt):
+                    return                       # (cannot happen: sequences only ever leave)
+                while self._queue:               # another make-up: its input is their output
+                    self._ready.append(self._collect())
+                continue
+            self._launch(nxt)
+
+    def decode(self, active: Sequence[int]) -> List[int]:
+        if not self._ready and not self._queue:
+            self._launch(active)
+        toks = self._ready.pop(0) if self._ready else self._collect()
+        out = [toks[i] for i in active]
+        if self.depth:
+            self._run_ahead(active)
+        return out
+
+    def _free(self, pos: int) -> None:
         if self.slots[pos] is not None:
             self.engine.free_slot(self.slots[pos])
             self.slots[pos] = None
 
+    def release(self, pos: int) -> None:
+        if self._in_flight(pos):
+            if pos not in self._to_free:
+                self._to_free.append(pos)    # steps in flight still write to its slot
+        else:
+            self._free(pos)
+
     def end_batch(self) -> None:
+        try:
+            while getattr(self, "_queue", None):
+                self._collect()
+        except Exception:
+            self._queue = []
+        self._ready, self._to_free = [], []
         for pos in range(len(self.slots)):
-            self.release(pos)
+            self._free(pos)
         self._loaded = None
         self.engine.check_fault()
 

@@ -80,6 +80,38 @@ def test_stop_tokens_end_a_sequence_and_are_kept(engines, plain_models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_of_the_host_changes_no_token(engines, dtype):
+    """The backend launches the next decode step before it hands a step's tokens to the
+    loop.  Sequences that end on a stop token, at different times, are in the step in flight:
+    their part is dropped, their slots come back afterwards, the others' tokens are the same
+    as without running ahead, and no slot is lost."""
+    from cretif_b200.engine.generate import EngineBackend, GenerationLoop
+    from cretif_b200.sampling import SamplingParams
+    eng = engines("B", dtype)
+    prompts = [tiny.tokens("B", n, 70 + n) for n in (4, 11, 7, 19, 2)]
+
+    def run(ahead, stops, max_tokens):
+        be = EngineBackend(eng, SamplingParams(), use_graph=True, run_ahead=ahead)
+        loop = GenerationLoop(be, stops, eng.cache.max_tokens, eng.cache.max_len,
+                              eng.cache.block_tokens, max_batch=4)     # two batches
+        out = loop.run(prompts, max_tokens)
+        assert eng.cache.stats()["slots_live"] == 0
+        eng.cache.check()
+        return [(r.tokens, r.finish_reason) for r in out]
+
+    free = run(False, [], 24)
+    # stop tokens that some sequences meet early, some late and some never
+    stops = {free[0][0][5], free[2][0][14], free[3][0][1]}
+    plain = run(False, stops, 24)
+    assert any(reason == "stop" for _, reason in plain) and any(r == "length" for _, r in plain)
+    assert len({len(t) for t, _ in plain}) > 2
+    assert run(True, stops, 24) == plain
+    assert run(True, [], 24) == free
+    # a sequence that fills its reservation exactly is not stepped beyond it
+    assert run(True, stops, 3) == run(False, stops, 3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(engines, plain_models, dtype):
     """300 tokens fed one by one after a short prompt (crossing four cache blocks)."""
     eng = engines("C", dtype)

@@ -120,6 +120,9 @@ int cretif_set_dependent_launch(int on);
 // the shared-memory streaming variant (decode_stream.cuh); returns the old column threshold.
 int cretif_set_stream_min_k(int k, long long min_bytes);
 long long cretif_stream_min_bytes(void);
+// ... for calls of at most this many tokens (default 64; beyond 16 as groups of 16 rows).
+// Returns the old limit.
+int cretif_set_stream_max_rows(int rows);
 // Depth of that variant's ring of stages (2..8); 0, the default, chooses per launch.  early
 // (>= 0; negative leaves it) is the number of stages whose weights are asked for before the
 // kernel waits for the one before it.  Returns the old depth.

@@ -49,17 +49,34 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st, int gr
   return launch_status();
 }
 
+// The register variant for any number of rows up to kFuMaxRows.
+template <int PRO, int EPI>
+static int dispatch_registers(const FusedParams& p, int tiles, cudaStream_t st) {
+  if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
+  if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
+  if (p.M <= kFuMaxGroupRows) return launch_fused<4, PRO, EPI>(p, tiles, st);
+  // more tokens: even groups of up to 32 rows, a multiple of 8 each
+  const int groups = (p.M + kFuMaxGroupRows - 1) / kFuMaxGroupRows;
+  const int group_rows = (((p.M + groups - 1) / groups) + 7) & ~7;
+  return launch_fused<4, PRO, EPI>(p, tiles, st, groups, group_rows);
+}
+
 // Matrices at least this wide, or this large, stream through shared memory
 // (decode_stream.cuh); narrow small ones are latency and do better without the copy unit.
 static int g_stream_min_k = 768;
 static long long g_stream_min_bytes = 16LL << 20;
+// ... and up to this many tokens (beyond 16 as groups of 16 rows that each stream the matrix)
+static int g_stream_max_rows = 64;
 // Depth of the streaming ring; 0: chosen per launch.
 static int g_stream_stages = 0;
 // Stages of weights asked for before the kernel waits for the kernel before it.
 static int g_stream_early = 1;
 
 template <int NT, int PRO, int EPI>
-static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
+static int launch_stream(const FusedParams& whole, int tiles, cudaStream_t st) {
+  const int groups = (whole.M + 8 * NT - 1) / (8 * NT);
+  FusedParams p = whole;             // sizes of one group of rows
+  if (groups > 1) p.M = 8 * NT;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
@@ -82,7 +99,7 @@ static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
   if (g_stream_stages) stages = g_stream_stages;
   while (stages > 2 && stream_smem(NT, PRO, p.M, p.K, stages) > kWholeSm) --stages;
   const size_t smem = stream_smem(NT, PRO, p.M, p.K, stages);
-  if (smem > 200 * 1024) return launch_fused<NT, PRO, EPI>(p, tiles, st);
+  if (smem > 200 * 1024) return dispatch_registers<PRO, EPI>(whole, tiles, st);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<NT, PRO, EPI>,
@@ -90,10 +107,10 @@ static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  const int max_ctas = per_sm * sm_count;
+  const int max_ctas = per_sm * sm_count / groups > 0 ? per_sm * sm_count / groups : 1;
   const int grid = tiles < max_ctas ? tiles : max_ctas;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(grid, groups);
   cfg.blockDim = dim3(kStThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -105,14 +122,14 @@ static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
   const int w_rows = EPI == kEpiPlain ? p.N : EPI == kEpiSilu ? 2 * p.I : (p.nh + 2 * p.nkv) * p.hd;
   CUtensorMap map_w, map_x;
   if (make_box_map_bf16(&map_w, p.W, w_rows, p.K, p.ldw, 8, kStBoxK, false))
-    return launch_fused<NT, PRO, EPI>(p, tiles, st);
+    return dispatch_registers<PRO, EPI>(whole, tiles, st);
   if (PRO == kProPlain) {
-    if (make_box_map_bf16(&map_x, p.X, p.M, p.K, p.ldx, 8 * NT, kStBoxK, false))
-      return launch_fused<NT, PRO, EPI>(p, tiles, st);
+    if (make_box_map_bf16(&map_x, whole.X, whole.M, p.K, p.ldx, 8 * NT, kStBoxK, false))
+      return dispatch_registers<PRO, EPI>(whole, tiles, st);
   } else {
     map_x = map_w;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_stream_kernel<NT, PRO, EPI>, p, map_w, map_x,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_stream_kernel<NT, PRO, EPI>, whole, map_w, map_x,
                                      tiles, stages, g_stream_early);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
@@ -120,17 +137,11 @@ static int launch_stream(const FusedParams& p, int tiles, cudaStream_t st) {
 template <int PRO, int EPI>
 static int dispatch_nt(const FusedParams& p, int tiles, cudaStream_t st) {
   const long long w_bytes = 2LL * tiles * kFuRows * p.K;
-  if ((p.K >= g_stream_min_k || w_bytes >= g_stream_min_bytes) && p.M <= 16) {
+  if ((p.K >= g_stream_min_k || w_bytes >= g_stream_min_bytes) && p.M <= g_stream_max_rows) {
     if (p.M <= 8) return launch_stream<1, PRO, EPI>(p, tiles, st);
-    return launch_stream<2, PRO, EPI>(p, tiles, st);
+    return launch_stream<2, PRO, EPI>(p, tiles, st);      // groups of 16 rows beyond 16
   }
-  if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
-  if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
-  if (p.M <= kFuMaxGroupRows) return launch_fused<4, PRO, EPI>(p, tiles, st);
-  // more tokens: even groups of up to 32 rows, a multiple of 8 each
-  const int groups = (p.M + kFuMaxGroupRows - 1) / kFuMaxGroupRows;
-  const int group_rows = (((p.M + groups - 1) / groups) + 7) & ~7;
-  return launch_fused<4, PRO, EPI>(p, tiles, st, groups, group_rows);
+  return dispatch_registers<PRO, EPI>(p, tiles, st);
 }
 
 static bool common_ok(const FusedParams& p) {
@@ -207,6 +218,12 @@ extern "C" int cretif_set_stream_min_k(int k, long long min_bytes) {
 }
 
 extern "C" long long cretif_stream_min_bytes(void) { return g_stream_min_bytes; }
+
+extern "C" int cretif_set_stream_max_rows(int rows) {
+  const int was = g_stream_max_rows;
+  if (rows > 0) g_stream_max_rows = rows;
+  return was;
+}
 
 extern "C" int cretif_set_stream_stages(int n, int early) {
   const int was = g_stream_stages;

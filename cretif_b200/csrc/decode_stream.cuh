@@ -60,9 +60,13 @@ __device__ __forceinline__ void tile_groups(const FusedParams& p, int tile, int&
 
 template <int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(kStThreads, 2)
-skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap map_w,
+skinny_stream_kernel(const FusedParams whole, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_x, int n_tiles, int n_stages,
                      int n_early) {
+  // More than 8 NT tokens run as groups of 8 NT rows along gridDim.y (every group streams
+  // the whole matrix; the groups of a tile run side by side, so the second read is L2's).
+  const int m_first = blockIdx.y * 8 * NT;
+  const FusedParams p = rows_of(whole, m_first, min(8 * NT, whole.M - m_first));
   extern __shared__ __align__(128) unsigned char stsmem_raw[];
   unsigned char* stsmem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(stsmem_raw) + 127) & ~uintptr_t(127));
@@ -132,7 +136,7 @@ skinny_stream_kernel(const FusedParams p, const __grid_constant__ CUtensorMap ma
       if (PRO == kProPlain && xrows) {
         unsigned char* xst = xs + (size_t)s * kXStage;
         for (int b = 0; b < boxes; ++b)
-          tc::tma_load_2d(xst + (size_t)b * NT * kStGroup, &map_x, k0 + b * kStBoxK, 0,
+          tc::tma_load_2d(xst + (size_t)b * NT * kStGroup, &map_x, k0 + b * kStBoxK, m_first,
                           &full[s]);
       }
     };

@@ -39,6 +39,9 @@ def lib():
         if tune:
             L.cretif_set_stream_min_k(int(tune), ctypes.c_longlong(
                 int(os.environ.get("CRETIF_STREAM_MIN_BYTES", "-1"))))
+        tune = os.environ.get("CRETIF_STREAM_MAX_ROWS")
+        if tune:
+            L.cretif_set_stream_max_rows(int(tune))
         tune = os.environ.get("CRETIF_STREAM_STAGES")
         if tune:
             L.cretif_set_stream_stages(int(tune), int(os.environ.get("CRETIF_STREAM_EARLY", "-1")))
@@ -409,10 +412,11 @@ def _decode_counters(device, n: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------ fused decode projections
 FUSED_MAX_ROWS = 128     # the kernels' limit; the parts choose how far they use it
-# Beyond 32 rows the kernel reads the matrix once per group of 32: worth it while the matrix
-# is small (measured: 64 tokens at SmolLM2-135M sizes, where no matrix but the head exceeds
-# 4 MB, take 0.7 of the tensor-core path's time; at 1.7B sizes 1.4 times).
-FUSED_GROUPS_MAX_BYTES = 8 << 20
+# Beyond 32 rows the kernels read the matrix once per group of 16 or 32 rows: worth it while
+# the matrix is small (measured at 64 tokens: 0.7 of the tensor-core path's time at
+# SmolLM2-135M sizes, where no matrix but the head exceeds 4 MB, 0.83 at 360M sizes (up to
+# 10 MB), 1.2 at 1.7B sizes (25 to 67 MB)).
+FUSED_GROUPS_MAX_BYTES = int(os.environ.get("CRETIF_FUSED_GROUPS_MAX_BYTES", str(16 << 20)))
 
 
 def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:

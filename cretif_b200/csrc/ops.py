@@ -341,7 +341,9 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
     shared memory is some 5 us shorter than the one through global scratch; a range is a
     cache block or more, and a block costs about 0.3 us.  So the cluster is taken unless it
     would make a CTA walk 16 blocks more than the plain split would (a long context with
-    few sequences)."""
+    few sequences).  (Clusters of 16, which the hardware takes as an opt-in size, were
+    measured: no gain for one sequence, twice the time for eight: too few of them fit the
+    chip at once.)"""
     tiles = max(1, -(-max_context // 64))
     n_split = decode_splits(B, nkv, max_context, device)
     if hd > 128 or _decode_simt_only:

@@ -300,3 +300,155 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         for got, want in zip(outs, wants):
             assert rel_err(got, want) < 1e-4
     eng.cache.check()
+
+
+# ---------------------------------------------------------------------------------------
+# A second toy architecture: the library's attention with a position encoding defined here
+# (queries and keys are scaled channel by channel with a wave of the position) and a
+# feed-forward with routing defined here (the best of three small experts for each token,
+# router logits in 32-bit).  Neither becomes part of the framework.
+# ---------------------------------------------------------------------------------------
+def _wave(pos, hd, amp, freq, dtype=torch.float64):
+    """[len(pos), hd] factors 1 + amp · cos(pos · (j + 1) · freq)."""
+    j = torch.arange(1, hd + 1, dtype=torch.float64)
+    p = torch.as_tensor(pos, dtype=torch.float64)
+    return (1.0 + amp * torch.cos(p[:, None] * j[None, :] * freq)).to(dtype)
+
+
+def _register_routed_toy():
+    from cretif_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
+                                    register_architecture)
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.base import Part, register_part
+    from cretif_b200.weights.loader import WeightSpec
+
+    @register_part("position", "wave")
+    class Wave(Part):
+        """q and k of every head are multiplied by _wave(position); nothing is rotated."""
+
+        def load(self, tensors):
+            self.amp, self.freq = float(self.params["amp"]), float(self.params["freq"])
+
+        def prepare(self, max_positions):
+            z = torch.zeros((1, 1), dtype=torch.float32, device=self.device)
+            self._none = (z, z)
+
+        def rotate_and_store(self, qkv, ctx, cache, nh, nkv, hd):
+            w = _wave(ctx.tok_pos.cpu(), hd, self.amp, self.freq).to(qkv.device)
+            qk = qkv[:, :(nh + nkv) * hd].unflatten(1, (nh + nkv, hd))
+            qk.copy_((qk.double() * w[:, None, :]).to(qkv.dtype))
+            kv = cache.kv          # stored as they are now (rotary_dim 0 of the library's kernel)
+            ops.rope_kv_append(qkv, *self._none, 0, 0, nh, nkv, hd, ctx.tok_pos, ctx.tok_seq,
+                               ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens,
+                               cache.writes, ctx.fault)
+
+    @register_part("feed_forward", "best_expert")
+    class BestExpert(Part):
+        """y = W2[e] · relu(W1[e] · x) for e = argmax(router · x), the router in float32."""
+
+        @classmethod
+        def weight_specs(cls, params, hidden_size):
+            E, F = params["experts"], params["expert_size"]
+            return {"router": ("router", WeightSpec((E, hidden_size), init=(0.0, 1.0))),
+                    "w1": ("w1", WeightSpec((E, F, hidden_size))),
+                    "w2": ("w2", WeightSpec((E, hidden_size, F)))}
+
+        def load(self, tensors):
+            self.router = tensors["router"].to(self.device, torch.float32)
+            self.w1 = tensors["w1"].to(self.device, torch.float32)
+            self.w2 = tensors["w2"].to(self.device, torch.float32)
+
+        def forward(self, x, ctx):
+            x = x.float()
+            best = (x @ self.router.T).argmax(dim=-1)                       # [T]
+            hidden = torch.relu(torch.einsum("efh,th->tef", self.w1, x))    # every expert
+            ys = torch.einsum("ehf,tef->teh", self.w2, hidden)
+            return ys[torch.arange(x.shape[0], device=x.device), best]
+
+    def build_spec(cfg):
+        H, L, hd = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["head_dim"]
+        norm = lambda name: PartSpec("rmsnorm", {"eps": 1e-6, "name": name})
+        layers = [LayerSpec(
+            prefix=f"l{i}.",
+            mixer=PartSpec("attention", {
+                "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"], "head_dim": hd,
+                "scale": hd ** -0.5, "window": 0,
+                "position": {"kind": "wave", "amp": cfg["amp"], "freq": cfg["freq"]},
+                "names": {"q": "q", "k": "k", "v": "v", "o": "o"}}),
+            feed_forward=PartSpec("best_expert", {"experts": cfg["experts"],
+                                                  "expert_size": cfg["expert_size"]}),
+            mixer_norm=norm("n1"), feed_forward_norm=norm("n2")) for i in range(L)]
+        return ModelSpec(architecture="ToyRouted", vocab_size=cfg["vocab_size"], hidden_size=H,
+                         embedding=PartSpec("token_embedding", {"name": "emb"}),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(L)],
+                         final_norm=norm("final"),
+                         head=PartSpec("linear_head", {"tied": False, "name": "head",
+                                                       "tied_to": "emb"}),
+                         max_positions=cfg["max_positions"])
+    register_architecture("ToyRouted", lambda raw: dict(raw), build_spec)
+
+
+def _routed_toy_plain(cfg, w, ids):
+    """The second toy model on a whole sequence, in float64; also the router's margins."""
+    nh, nkv, hd, L = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
+    S = len(ids)
+    wave = _wave(list(range(S)), hd, cfg["amp"], cfg["freq"])
+    h = pl.embed(w["emb"], ids)
+    margin = math.inf
+    for i in range(L):
+        p = f"l{i}."
+        n = pl.rmsnorm(h, w[p + "n1"], 1e-6)
+        q = (n @ w[p + "q"].T).reshape(S, nh, hd) * wave[:, None, :]
+        k = (n @ w[p + "k"].T).reshape(S, nkv, hd) * wave[:, None, :]
+        v = (n @ w[p + "v"].T).reshape(S, nkv, hd)
+        h = h + pl.attention(q, k, v, hd ** -0.5).reshape(S, nh * hd) @ w[p + "o"].T
+        n = pl.rmsnorm(h, w[p + "n2"], 1e-6)
+        logits = n @ w[p + "router"].T
+        top2 = logits.topk(2, dim=-1).values
+        margin = min(margin, float((top2[:, 0] - top2[:, 1]).min()))
+        best = logits.argmax(dim=-1)
+        y = torch.stack([w[p + "w2"][e] @ torch.relu(w[p + "w1"][e] @ n[t])
+                         for t, e in enumerate(best.tolist())])
+        h = h + y
+    return pl.lm_head(pl.rmsnorm(h, w["final"], 1e-6), w["head"]), margin
+
+
+def test_a_toy_position_encoding_and_a_routed_feed_forward(tmp_path):
+    from replay_cuts import rel_err, run_batch, run_tail_by_one, run_whole
+    from cretif_b200.engine import Engine
+    from cretif_b200.weights.random_model import write_random_model
+    _register_routed_toy()
+    cfg = {"architectures": ["ToyRouted"], "hidden_size": 40, "num_hidden_layers": 2,
+           "heads": 3, "kv_heads": 1, "head_dim": 16, "experts": 3, "expert_size": 24,
+           "amp": 0.4, "freq": 0.37, "vocab_size": 90, "max_positions": 256}
+    from cretif_b200.weights import write_model_folder
+    d0, d = str(tmp_path / "routed_flat"), str(tmp_path / "routed")
+    write_random_model(d0, cfg, seed=11, dtype=torch.float32)
+    # Small random weights give nearly uniform attention, which would hide a wrong position
+    # factor: queries and keys are scaled up so that each query reads a few particular keys.
+    _, w = pl.read_model_folder(d0)
+    tensors = {k: v.to(torch.float32) for k, v in w.items()}
+    for i in range(cfg["num_hidden_layers"]):
+        for name in ("q", "k"):
+            tensors[f"l{i}.{name}"] = tensors[f"l{i}.{name}"] * 30.0
+    write_model_folder(d, cfg, tensors)
+    eng = Engine(d, dtype="float32", max_tokens=1024)
+    assert not eng.model.graph_safe          # parts from outside run eagerly unless they say otherwise
+    _, w = pl.read_model_folder(d)
+    rng = np.random.default_rng(5)
+    reqs = [rng.integers(0, 90, size=n).tolist() for n in (70, 9, 33)]
+    plain = [_routed_toy_plain(cfg, w, r) for r in reqs]
+    # a routing decision on a knife's edge could go either way in 32-bit: there is none here
+    assert min(m for _, m in plain) > 1e-3
+    wants = [o.numpy() for o, _ in plain]
+    for r, want in zip(reqs, wants):
+        assert rel_err(run_whole(eng, r), want) < 1e-4
+        assert rel_err(run_tail_by_one(eng, r, tail=12), want) < 1e-4
+    for _ in range(2):
+        for got, want in zip(run_batch(eng, reqs, [50, 3, 33]), wants):
+            assert rel_err(got, want) < 1e-4
+    eng.cache.check()
+    # the position encoding matters: without the wave the logits are others
+    flat = dict(cfg, amp=0.0)
+    other, _ = _routed_toy_plain(flat, w, reqs[0])
+    assert rel_err(other.numpy(), wants[0]) > 1e-2

@@ -38,7 +38,7 @@ struct TcSmem {
   static constexpr int kBTile = BN * kTcBK * 2;
   static constexpr int kStage = kATile + kBTile;
   static constexpr int total(int stages) {     // barriers behind the stages, + align slack
-    return stages * kStage + (2 * kTcMaxStages + 1) * 8 + 16 + 1024;
+    return stages * kStage + (2 * kTcMaxStages + 4) * 8 + 16 + 1024;
   }
   static int stages_for(long long ctas, int num_kb, int sm_count) {
     int stages = BN >= 256 ? 4 : 3;
@@ -79,10 +79,10 @@ template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
-               int kTcStages, unsigned long long* stamps) {
+               int kTcStages, unsigned long long* stamps, int n_n_tiles, int n_tiles) {
   // Tuning aid: with a buffer given, lane 0 of each warp of the first CTA notes the time at
-  // which it passes its phases: [warp][8] nanoseconds.
-  const bool stamping = stamps && blockIdx.x + blockIdx.y == 0 && (threadIdx.x & 31) == 0;
+  // which it passes the phases of its first tile: [warp][8] nanoseconds.
+  const bool stamping = stamps && blockIdx.x == 0 && (threadIdx.x & 31) == 0;
   auto stamp = [&](int i) {
     if (stamping) {
       unsigned long long t;
@@ -99,24 +99,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   using L = TcSmem<BN>;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kTcStages * L::kStage);
   uint64_t* empty = full + kTcMaxStages;
-  uint64_t* acc_full = empty + kTcMaxStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = empty + kTcMaxStages;       // two accumulators in tensor memory
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * BN;
   const int num_kb = (K + kTcBK - 1) / kTcBK;
+  // The CTA is persistent: it takes tiles blockIdx.x, + gridDim.x, ...  (n fastest, so that the
+  // CTAs running at one time share rows of A).  Tile coordinates are stepped, not divided.
+  struct Tile {
+    int mt, nt;
+  };
+  const int step_m = (int)gridDim.x / n_n_tiles, step_n = (int)gridDim.x - step_m * n_n_tiles;
+  const Tile first = {(int)blockIdx.x / n_n_tiles, (int)blockIdx.x % n_n_tiles};
+  auto next = [&](Tile& t) {
+    t.mt += step_m;
+    t.nt += step_n;
+    if (t.nt >= n_n_tiles) { t.nt -= n_n_tiles; ++t.mt; }
+  };
+  const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    tc::mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], 128); }
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_a);
     tc::tma_prefetch_descriptor(&map_w);
   }
-  if (warp == 1) {                       // one warp allocates the accumulator's columns
-    tc::tmem_alloc(tmem_slot, BN);
+  if (warp == 1) {                       // one warp allocates both accumulators' columns
+    tc::tmem_alloc(tmem_slot, 2 * BN);
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
@@ -130,26 +143,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   stamp(1);
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && my_tiles > 0) {
+      Tile t = first;
       const int early = num_kb < kTcStages ? num_kb : kTcStages;
       for (int kb = 0; kb < early; ++kb) {
         tc::mbar_expect_tx(&full[kb], (uint32_t)L::kStage);
-        tc::tma_load_2d(smem + kb * L::kStage + L::kATile, &map_w, kb * kTcBK, n0, &full[kb]);
+        tc::tma_load_2d(smem + kb * L::kStage + L::kATile, &map_w, kb * kTcBK, t.nt * BN, &full[kb]);
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       stamp(2);
       for (int kb = 0; kb < early; ++kb)
-        tc::tma_load_2d(smem + kb * L::kStage, &map_a, kb * kTcBK, m0, &full[kb]);
+        tc::tma_load_2d(smem + kb * L::kStage, &map_a, kb * kTcBK, t.mt * kTcBM, &full[kb]);
       stamp(3);
       // (stage and turn of the ring are stepped, not divided: the depth is a run-time value)
       int s = early == kTcStages ? 0 : early, turn = early == kTcStages ? 1 : 0;
-      for (int kb = early; kb < num_kb; ++kb) {
-        if (!tc::mbar_wait(&empty[s], (uint32_t)((turn - 1) & 1), abort)) break;
-        unsigned char* stage = smem + s * L::kStage;
-        tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
-        tc::tma_load_2d(stage, &map_a, kb * kTcBK, m0, &full[s]);
-        tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, n0, &full[s]);
-        if (++s == kTcStages) { s = 0; ++turn; }
+      bool ok = true;
+      for (int i = 0; i < my_tiles && ok; ++i, next(t)) {
+        for (int kb = i == 0 ? early : 0; kb < num_kb; ++kb) {
+          if (turn > 0 && !tc::mbar_wait(&empty[s], (uint32_t)((turn - 1) & 1), abort)) {
+            ok = false;
+            break;
+          }
+          unsigned char* stage = smem + s * L::kStage;
+          tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
+          tc::tma_load_2d(stage, &map_a, kb * kTcBK, t.mt * kTcBM, &full[s]);
+          tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, t.nt * BN, &full[s]);
+          if (++s == kTcStages) { s = 0; ++turn; }
+        }
       }
     }
   } else if (warp == 1) {
@@ -157,182 +177,201 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = tc::instr_desc_bf16(kTcBM, BN);
       bool ok = true;
       int s = 0, turn = 0;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        ok = tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort);
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int buf = i & 1;
+        // the epilogue warps have taken this accumulator's last tile (two tiles ago) out
+        if (i >= 2) ok = tc::mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1), abort);
         if (!ok) break;
         tc::tc_fence_after();
-        if (kb == 0) stamp(2);
-        unsigned char* stage = smem + s * L::kStage;
-        const uint64_t a_desc = tc::smem_desc_k_sw128(stage);
-        const uint64_t b_desc = tc::smem_desc_k_sw128(stage + L::kATile);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort);
+          if (!ok) break;
+          tc::tc_fence_after();
+          if (i == 0 && kb == 0) stamp(2);
+          unsigned char* stage = smem + s * L::kStage;
+          const uint64_t a_desc = tc::smem_desc_k_sw128(stage);
+          const uint64_t b_desc = tc::smem_desc_k_sw128(stage + L::kATile);
 #pragma unroll
-        for (int k = 0; k < kTcBK / 16; ++k)       // 16 bf16 = 32 bytes = 2 descriptor units
-          tc::umma_bf16(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
-        tc::umma_commit(&empty[s]);                // frees the stage when these MMAs are done
-        if (++s == kTcStages) { s = 0; ++turn; }
+          for (int k = 0; k < kTcBK / 16; ++k)       // 16 bf16 = 32 bytes = 2 descriptor units
+            tc::umma_bf16(tmem_acc + (uint32_t)(buf * BN), a_desc + 2 * k, b_desc + 2 * k, idesc,
+                          (kb | k) != 0);
+          tc::umma_commit(&empty[s]);                // frees the stage when these MMAs are done
+          if (++s == kTcStages) { s = 0; ++turn; }
+        }
+        if (ok) tc::umma_commit(&acc_full[buf]);     // accumulator complete
+        if (i == 0) stamp(3);
       }
-      tc::umma_commit(acc_full);                   // accumulator complete
-      stamp(3);
     }
   } else {
-    // ---- epilogue: thread = one row of the tile, TMEM lanes 32*(warp%4) ..
+    // ---- epilogue: thread = one row of the tile, TMEM lanes 32*(warp%4) ..; it works on one
+    // accumulator while the next tile's product fills the other
     const int quad = warp & 3;
-    const int m = m0 + quad * 32 + lane;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(2);
-    // Rotary epilogue: where this thread's row goes (position → cache block → address) is a
-    // chain of dependent loads that does not need the product: it runs while the product does.
-    const int head = EPI == kTcRope ? n0 / ep.hd : 0, half = ep.hd >> 1;
-    int pos = 0;
-    __nv_bfloat16* dst = nullptr;             // where this row's head goes
-    if (EPI == kTcRope && m < M) {
-      pos = ep.tok_pos[m];
-      if (head < ep.nh) {
-        dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
-      } else if (ep.write_cache) {
-        const int slot = ep.seq_slot[ep.tok_seq[m]];
-        const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
-        if (blk < 0) {
-          atomicOr(fault, kFaultBlockTable);
-        } else {
-          const bool is_k = head < ep.nh + ep.nkv;
-          const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
-          dst = (is_k ? ep.kc : ep.vc) +
-                (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
-        }
-      }
-    }
-    const bool ok = tc::mbar_wait(acc_full, 0u, abort);
-    tc::tc_fence_after();
-    stamp(3);
-    const uint32_t lane_acc = tmem_acc + ((uint32_t)(quad * 32) << 16);
-    if (ok && EPI == kTcStore) {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
-        tc::tmem_load_wait();
-        if (m < M && n0 + c0 < N) {
-          TC* out = C + (size_t)m * ldc + n0 + c0;
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-            const int n = n0 + c0 + j;
-            if (n + 8 <= N) {
-              if (accumulate) {
-                float old[8];
-                load8(out + j, old);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] += old[e];
-              }
-              store8(out + j, v);
-            } else {
-              for (int e = 0; e < 8 && n + e < N; ++e) {
-                float x = v[e];
-                if (accumulate) x += to_float(out[j + e]);
-                out[j + e] = from_float<TC>(x);
-              }
-            }
+    Tile t = first;
+    bool alive = true;
+    for (int i = 0; i < my_tiles; ++i, next(t)) {
+      const int buf = i & 1;
+      const int m0 = t.mt * kTcBM, n0 = t.nt * BN;
+      const int m = m0 + quad * 32 + lane;
+      // Rotary epilogue: where this thread's row goes (position → cache block → address) is a
+      // chain of dependent loads that does not need the product: it runs while the product does.
+      const int head = EPI == kTcRope ? n0 / ep.hd : 0, half = ep.hd >> 1;
+      int pos = 0;
+      __nv_bfloat16* dst = nullptr;             // where this row's head goes
+      if (EPI == kTcRope && m < M) {
+        pos = ep.tok_pos[m];
+        if (head < ep.nh) {
+          dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
+        } else if (ep.write_cache) {
+          const int slot = ep.seq_slot[ep.tok_seq[m]];
+          const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
+          if (blk < 0) {
+            atomicOr(fault, kFaultBlockTable);
+          } else {
+            const bool is_k = head < ep.nh + ep.nkv;
+            const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
+            dst = (is_k ? ep.kc : ep.vc) +
+                  (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
           }
         }
       }
-    }
-    if (ok && EPI == kTcSilu) {
-      // tile columns [0,64) are gate, [64,128) the matching up columns of act[:, n0/2 ..]
-      const int col0 = n0 >> 1;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t g[32], u[32];
-        tc::tmem_load_32(lane_acc + (uint32_t)c0, g);
-        tc::tmem_load_32(lane_acc + (uint32_t)(64 + c0), u);
-        tc::tmem_load_wait();
-        if (m < M && col0 + c0 < ep.I) {
-          __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              // gate and up pass through bfloat16 as they do when stored separately
-              const float gg = round_bf16(__uint_as_float(g[j + e]));
-              const float uu = round_bf16(__uint_as_float(u[j + e]));
-              v[e] = gg / (1.0f + expf(-gg)) * uu;
-            }
-            if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
-          }
-        }
-      }
-    }
-    if (ok && EPI == kTcRope) {
-      const bool rotate = head < ep.nh + ep.nkv;
-      const float* cs = ep.cos_t + (size_t)pos * half;
-      const float* sn = ep.sin_t + (size_t)pos * half;
-      if (!rotate) {
-#pragma unroll 1
+      // (a wait that gave up: later waits return at once, and nothing more is stored)
+      alive = tc::mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1), abort) && alive;
+      const bool ok = alive;
+      tc::tc_fence_after();
+      if (i == 0) stamp(3);
+      const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
+      if (ok && EPI == kTcStore) {
+  #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
           tc::tmem_load_wait();
-          if (dst) {
-#pragma unroll
+          if (m < M && n0 + c0 < N) {
+            TC* out = C + (size_t)m * ldc + n0 + c0;
+  #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float v[8];
-#pragma unroll
+  #pragma unroll
               for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-              store8(dst + c0 + j, v);
-            }
-          }
-        }
-      } else if (ep.pairing == 0) {            // pairs (j, j + head_dim/2)
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
-          uint32_t lo[32], hi[32];
-          tc::tmem_load_32(lane_acc + (uint32_t)c0, lo);
-          tc::tmem_load_32(lane_acc + (uint32_t)(BN / 2 + c0), hi);
-          tc::tmem_load_wait();
-          if (dst) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float c8[8], s8[8], y0[8], y1[8];
-              load8(cs + c0 + j, c8);
-              load8(sn + c0 + j, s8);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float x0 = round_bf16(__uint_as_float(lo[j + e]));
-                const float x1 = round_bf16(__uint_as_float(hi[j + e]));
-                y0[e] = x0 * c8[e] - x1 * s8[e];
-                y1[e] = x0 * s8[e] + x1 * c8[e];
+              const int n = n0 + c0 + j;
+              if (n + 8 <= N) {
+                if (accumulate) {
+                  float old[8];
+                  load8(out + j, old);
+  #pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] += old[e];
+                }
+                store8(out + j, v);
+              } else {
+                for (int e = 0; e < 8 && n + e < N; ++e) {
+                  float x = v[e];
+                  if (accumulate) x += to_float(out[j + e]);
+                  out[j + e] = from_float<TC>(x);
+                }
               }
-              store8(dst + c0 + j, y0);
-              store8(dst + half + c0 + j, y1);
-            }
-          }
-        }
-      } else {                                  // pairs (2j, 2j + 1)
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
-          tc::tmem_load_wait();
-          if (dst) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float y[8];
-#pragma unroll
-              for (int e = 0; e < 8; e += 2) {
-                const int jj = (c0 + j + e) >> 1;
-                const float x0 = round_bf16(__uint_as_float(r[j + e]));
-                const float x1 = round_bf16(__uint_as_float(r[j + e + 1]));
-                y[e] = x0 * cs[jj] - x1 * sn[jj];
-                y[e + 1] = x0 * sn[jj] + x1 * cs[jj];
-              }
-              store8(dst + c0 + j, y);
             }
           }
         }
       }
+      if (ok && EPI == kTcSilu) {
+        // tile columns [0,64) are gate, [64,128) the matching up columns of act[:, n0/2 ..]
+        const int col0 = n0 >> 1;
+  #pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t g[32], u[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, g);
+          tc::tmem_load_32(lane_acc + (uint32_t)(64 + c0), u);
+          tc::tmem_load_wait();
+          if (m < M && col0 + c0 < ep.I) {
+            __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
+  #pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float v[8];
+  #pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                // gate and up pass through bfloat16 as they do when stored separately
+                const float gg = round_bf16(__uint_as_float(g[j + e]));
+                const float uu = round_bf16(__uint_as_float(u[j + e]));
+                v[e] = gg / (1.0f + expf(-gg)) * uu;
+              }
+              if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
+            }
+          }
+        }
+      }
+      if (ok && EPI == kTcRope) {
+        const bool rotate = head < ep.nh + ep.nkv;
+        const float* cs = ep.cos_t + (size_t)pos * half;
+        const float* sn = ep.sin_t + (size_t)pos * half;
+        if (!rotate) {
+  #pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+            tc::tmem_load_wait();
+            if (dst) {
+  #pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+  #pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                store8(dst + c0 + j, v);
+              }
+            }
+          }
+        } else if (ep.pairing == 0) {            // pairs (j, j + head_dim/2)
+  #pragma unroll 1
+          for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+            uint32_t lo[32], hi[32];
+            tc::tmem_load_32(lane_acc + (uint32_t)c0, lo);
+            tc::tmem_load_32(lane_acc + (uint32_t)(BN / 2 + c0), hi);
+            tc::tmem_load_wait();
+            if (dst) {
+  #pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float c8[8], s8[8], y0[8], y1[8];
+                load8(cs + c0 + j, c8);
+                load8(sn + c0 + j, s8);
+  #pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float x0 = round_bf16(__uint_as_float(lo[j + e]));
+                  const float x1 = round_bf16(__uint_as_float(hi[j + e]));
+                  y0[e] = x0 * c8[e] - x1 * s8[e];
+                  y1[e] = x0 * s8[e] + x1 * c8[e];
+                }
+                store8(dst + c0 + j, y0);
+                store8(dst + half + c0 + j, y1);
+              }
+            }
+          }
+        } else {                                  // pairs (2j, 2j + 1)
+  #pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+            tc::tmem_load_wait();
+            if (dst) {
+  #pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float y[8];
+  #pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                  const int jj = (c0 + j + e) >> 1;
+                  const float x0 = round_bf16(__uint_as_float(r[j + e]));
+                  const float x1 = round_bf16(__uint_as_float(r[j + e + 1]));
+                  y[e] = x0 * cs[jj] - x1 * sn[jj];
+                  y[e + 1] = x0 * sn[jj] + x1 * cs[jj];
+                }
+                store8(dst + c0 + j, y);
+              }
+            }
+          }
+        }
+      }
+        tc::tc_fence_before();
+      tc::mbar_arrive(&acc_empty[buf]);        // this accumulator may be overwritten
     }
   }
   stamp(4);
@@ -341,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tc::tmem_dealloc(tmem_acc, BN);
+    tc::tmem_dealloc(tmem_acc, 2 * BN);
   }
   stamp(5);
 }
@@ -446,9 +485,10 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const dim3 grid((N + BN - 1) / BN, (M + kTcBM - 1) / kTcBM);
-  const int stages = TcSmem<BN>::stages_for((long long)grid.x * grid.y, (K + kTcBK - 1) / kTcBK,
-                                            sm_count);
+  const int n_n_tiles = (N + BN - 1) / BN;
+  const long long tiles = (long long)n_n_tiles * ((M + kTcBM - 1) / kTcBM);
+  if (tiles > 0x7fffffffLL) return kBadArgument;
+  const int stages = TcSmem<BN>::stages_for(tiles, (K + kTcBK - 1) / kTcBK, sm_count);
   const int smem = TcSmem<BN>::total(stages);
   static int configured = 0;
   if (smem > configured) {
@@ -457,6 +497,13 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
+  // Persistent CTAs: as many as fit the chip at once (by shared memory and by the 512 columns
+  // of tensor memory, of which a CTA holds two accumulators), each walking its share of tiles.
+  int per_sm = (227 * 1024) / smem;
+  if (per_sm > 512 / (2 * BN)) per_sm = 512 / (2 * BN);
+  if (per_sm < 1) per_sm = 1;
+  const long long resident = (long long)per_sm * sm_count;
+  const dim3 grid((unsigned)(tiles < resident ? tiles : resident));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kTcThreads);
@@ -468,7 +515,7 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, map_a, map_w, ep, M, N, K,
-                                     fault, stages, g_tc_stamps);
+                                     fault, stages, g_tc_stamps, n_n_tiles, (int)tiles);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 

@@ -214,26 +214,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int buf = i & 1;
       const int m0 = t.mt * kTcBM, n0 = t.nt * BN;
       const int m = m0 + quad * 32 + lane;
-      // Rotary epilogue: where this thread's row goes (position → cache block → address) is a
-      // chain of dependent loads that does not need the product: it runs while the product does.
-      const int head = EPI == kTcRope ? n0 / ep.hd : 0, half = ep.hd >> 1;
-      int pos = 0;
-      __nv_bfloat16* dst = nullptr;             // where this row's head goes
-      if (EPI == kTcRope && m < M) {
+      // Rotary epilogue: where this thread's row goes (position → slot → cache block) is a
+      // chain of dependent loads that does not need the product: it runs while the product
+      // does.  A tile holds BN / head_dim heads.
+      const int hd = ep.hd, half = hd >> 1;
+      const int head0 = EPI == kTcRope ? n0 / hd : 0;
+      const bool row_ok = EPI == kTcRope && m < M;
+      int pos = 0, blk = -1;
+      if (row_ok) {
         pos = ep.tok_pos[m];
-        if (head < ep.nh) {
-          dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * ep.hd;
-        } else if (ep.write_cache) {
+        if (ep.write_cache && head0 + BN / hd > ep.nh) {       // a key or value head is here
           const int slot = ep.seq_slot[ep.tok_seq[m]];
-          const int blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
-          if (blk < 0) {
-            atomicOr(fault, kFaultBlockTable);
-          } else {
-            const bool is_k = head < ep.nh + ep.nkv;
-            const int kvh = is_k ? head - ep.nh : head - ep.nh - ep.nkv;
-            dst = (is_k ? ep.kc : ep.vc) +
-                  (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * ep.hd;
-          }
+          blk = ep.table[(size_t)slot * ep.table_stride + pos / ep.bt];
+          if (blk < 0) atomicOr(fault, kFaultBlockTable);
         }
       }
       // (a wait that gave up: later waits return at once, and nothing more is stored)
@@ -243,24 +236,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (i == 0) stamp(3);
       const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
       if (ok && EPI == kTcStore) {
-  #pragma unroll 1
+#pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
           tc::tmem_load_wait();
           if (m < M && n0 + c0 < N) {
             TC* out = C + (size_t)m * ldc + n0 + c0;
-  #pragma unroll
+#pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float v[8];
-  #pragma unroll
+#pragma unroll
               for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
               const int n = n0 + c0 + j;
               if (n + 8 <= N) {
                 if (accumulate) {
                   float old[8];
                   load8(out + j, old);
-  #pragma unroll
+#pragma unroll
                   for (int e = 0; e < 8; ++e) v[e] += old[e];
                 }
                 store8(out + j, v);
@@ -278,7 +271,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (ok && EPI == kTcSilu) {
         // tile columns [0,64) are gate, [64,128) the matching up columns of act[:, n0/2 ..]
         const int col0 = n0 >> 1;
-  #pragma unroll 1
+#pragma unroll 1
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t g[32], u[32];
           tc::tmem_load_32(lane_acc + (uint32_t)c0, g);
@@ -286,10 +279,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc::tmem_load_wait();
           if (m < M && col0 + c0 < ep.I) {
             __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
-  #pragma unroll
+#pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float v[8];
-  #pragma unroll
+#pragma unroll
               for (int e = 0; e < 8; ++e) {
                 // gate and up pass through bfloat16 as they do when stored separately
                 const float gg = round_bf16(__uint_as_float(g[j + e]));
@@ -302,75 +295,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (ok && EPI == kTcRope) {
-        const bool rotate = head < ep.nh + ep.nkv;
         const float* cs = ep.cos_t + (size_t)pos * half;
         const float* sn = ep.sin_t + (size_t)pos * half;
-        if (!rotate) {
-  #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
-            tc::tmem_load_wait();
-            if (dst) {
-  #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-  #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                store8(dst + c0 + j, v);
-              }
+        for (int hh = 0; hh * hd < BN; ++hh) {
+          const int head = head0 + hh;                   // (the same for the whole warp)
+          if (head >= ep.nh + 2 * ep.nkv) break;
+          const uint32_t acc_h = lane_acc + (uint32_t)(hh * hd);
+          const bool rotate = head < ep.nh + ep.nkv;
+          __nv_bfloat16* dst = nullptr;                  // where this row's head goes
+          if (row_ok) {
+            if (head < ep.nh) {
+              dst = ep.Q + (size_t)m * ep.ldq + (size_t)head * hd;
+            } else if (blk >= 0) {
+              const int kvh = rotate ? head - ep.nh : head - ep.nh - ep.nkv;
+              dst = (rotate ? ep.kc : ep.vc) +
+                    (((size_t)blk * ep.nkv + kvh) * ep.bt + (pos % ep.bt)) * hd;
             }
           }
-        } else if (ep.pairing == 0) {            // pairs (j, j + head_dim/2)
-  #pragma unroll 1
-          for (int c0 = 0; c0 < BN / 2; c0 += 32) {
-            uint32_t lo[32], hi[32];
-            tc::tmem_load_32(lane_acc + (uint32_t)c0, lo);
-            tc::tmem_load_32(lane_acc + (uint32_t)(BN / 2 + c0), hi);
-            tc::tmem_load_wait();
-            if (dst) {
-  #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float c8[8], s8[8], y0[8], y1[8];
-                load8(cs + c0 + j, c8);
-                load8(sn + c0 + j, s8);
-  #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const float x0 = round_bf16(__uint_as_float(lo[j + e]));
-                  const float x1 = round_bf16(__uint_as_float(hi[j + e]));
-                  y0[e] = x0 * c8[e] - x1 * s8[e];
-                  y1[e] = x0 * s8[e] + x1 * c8[e];
+          if (!rotate) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < hd; c0 += 32) {
+              uint32_t r[32];
+              tc::tmem_load_32(acc_h + (uint32_t)c0, r);
+              tc::tmem_load_wait();
+              if (dst) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float v[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                  store8(dst + c0 + j, v);
                 }
-                store8(dst + c0 + j, y0);
-                store8(dst + half + c0 + j, y1);
               }
             }
-          }
-        } else {                                  // pairs (2j, 2j + 1)
-  #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
-            tc::tmem_load_wait();
-            if (dst) {
-  #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float y[8];
-  #pragma unroll
-                for (int e = 0; e < 8; e += 2) {
-                  const int jj = (c0 + j + e) >> 1;
-                  const float x0 = round_bf16(__uint_as_float(r[j + e]));
-                  const float x1 = round_bf16(__uint_as_float(r[j + e + 1]));
-                  y[e] = x0 * cs[jj] - x1 * sn[jj];
-                  y[e + 1] = x0 * sn[jj] + x1 * cs[jj];
+          } else if (ep.pairing == 0) {            // pairs (j, j + head_dim/2)
+#pragma unroll 1
+            for (int c0 = 0; c0 < half; c0 += 32) {
+              uint32_t lo[32], hi[32];
+              tc::tmem_load_32(acc_h + (uint32_t)c0, lo);
+              tc::tmem_load_32(acc_h + (uint32_t)(half + c0), hi);
+              tc::tmem_load_wait();
+              if (dst) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float c8[8], s8[8], y0[8], y1[8];
+                  load8(cs + c0 + j, c8);
+                  load8(sn + c0 + j, s8);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const float x0 = round_bf16(__uint_as_float(lo[j + e]));
+                    const float x1 = round_bf16(__uint_as_float(hi[j + e]));
+                    y0[e] = x0 * c8[e] - x1 * s8[e];
+                    y1[e] = x0 * s8[e] + x1 * c8[e];
+                  }
+                  store8(dst + c0 + j, y0);
+                  store8(dst + half + c0 + j, y1);
                 }
-                store8(dst + c0 + j, y);
+              }
+            }
+          } else {                                  // pairs (2j, 2j + 1)
+#pragma unroll 1
+            for (int c0 = 0; c0 < hd; c0 += 32) {
+              uint32_t r[32];
+              tc::tmem_load_32(acc_h + (uint32_t)c0, r);
+              tc::tmem_load_wait();
+              if (dst) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float y[8];
+#pragma unroll
+                  for (int e = 0; e < 8; e += 2) {
+                    const int jj = (c0 + j + e) >> 1;
+                    const float x0 = round_bf16(__uint_as_float(r[j + e]));
+                    const float x1 = round_bf16(__uint_as_float(r[j + e + 1]));
+                    y[e] = x0 * cs[jj] - x1 * sn[jj];
+                    y[e + 1] = x0 * sn[jj] + x1 * cs[jj];
+                  }
+                  store8(dst + c0 + j, y);
+                }
               }
             }
           }
         }
       }
-        tc::tc_fence_before();
+      tc::tc_fence_before();
       tc::mbar_arrive(&acc_empty[buf]);        // this accumulator may be overwritten
     }
   }
@@ -593,7 +601,10 @@ extern "C" int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q,
   ep.kc = (__nv_bfloat16*)kc; ep.vc = (__nv_bfloat16*)vc; ep.bt = bt; ep.write_cache = write_cache;
   const int N = (nh + 2 * nkv) * hd;
   cudaStream_t st = (cudaStream_t)stream;
-  if (hd == 64)
+  // A tile is a whole number of heads.  Small products want many narrow tiles; large ones
+  // (two rounds of 128-wide tiles and more) do more arithmetic per byte with wide ones.
+  const long long wide_tiles = (long long)((N + 127) / 128) * ((M + kTcBM - 1) / kTcBM);
+  if (hd == 64 && wide_tiles < 2 * 148)
     return launch_tc<64, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
   return launch_tc<128, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
 }

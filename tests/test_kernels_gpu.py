@@ -316,7 +316,10 @@ def test_gemm_tc_silu(ops, M, I, K):
 
 
 @pytest.mark.parametrize("pairing", [0, 1])
-@pytest.mark.parametrize("nh,nkv,hd,K", [(9, 3, 64, 576), (2, 1, 128, 96), (3, 3, 64, 72)])
+@pytest.mark.parametrize("nh,nkv,hd,K", [(9, 3, 64, 576), (2, 1, 128, 96), (3, 3, 64, 72),
+                                         # so many heads that a tile takes two of them (and
+                                         # the last tile only one)
+                                         (101, 25, 64, 72)])
 def test_gemm_tc_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K):
     theta, P = 10000.0, 512
     lens = [200, 70, 333]

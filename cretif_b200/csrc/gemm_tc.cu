@@ -269,27 +269,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (ok && EPI == kTcSilu) {
-        // tile columns [0,64) are gate, [64,128) the matching up columns of act[:, n0/2 ..]
-        const int col0 = n0 >> 1;
+        // every 128 tile columns are 64 gate columns and the 64 up columns that belong to
+        // them: act[:, n0/2 + 64 pair ..]
 #pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t g[32], u[32];
-          tc::tmem_load_32(lane_acc + (uint32_t)c0, g);
-          tc::tmem_load_32(lane_acc + (uint32_t)(64 + c0), u);
-          tc::tmem_load_wait();
-          if (m < M && col0 + c0 < ep.I) {
-            __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
+        for (int pair = 0; pair < BN / 128; ++pair) {
+          const int col0 = (n0 >> 1) + pair * 64;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t g[32], u[32];
+            tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + c0), g);
+            tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + 64 + c0), u);
+            tc::tmem_load_wait();
+            if (m < M && col0 + c0 < ep.I) {
+              __nv_bfloat16* out = ep.act + (size_t)m * ep.I + col0 + c0;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float v[8];
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                // gate and up pass through bfloat16 as they do when stored separately
-                const float gg = round_bf16(__uint_as_float(g[j + e]));
-                const float uu = round_bf16(__uint_as_float(u[j + e]));
-                v[e] = gg / (1.0f + expf(-gg)) * uu;
+                for (int e = 0; e < 8; ++e) {
+                  // gate and up pass through bfloat16 as they do when stored separately
+                  const float gg = round_bf16(__uint_as_float(g[j + e]));
+                  const float uu = round_bf16(__uint_as_float(u[j + e]));
+                  v[e] = gg / (1.0f + expf(-gg)) * uu;
+                }
+                if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
               }
-              if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
             }
           }
         }
@@ -578,6 +582,12 @@ extern "C" int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, in
   if (((uintptr_t)act) & 15) return kMisaligned;
   TcEpi ep = {};
   ep.act = (__nv_bfloat16*)act; ep.I = I;
+  // wide tiles (two gate|up pairs, one CTA per SM) once there are four rounds of them for the
+  // whole chip; with fewer, the last round's empty seats cost more than the wide tile saves
+  const long long wide_tiles = (long long)((2 * I + 255) / 256) * ((M + kTcBM - 1) / kTcBM);
+  if (wide_tiles >= 4 * 148)
+    return launch_tc<256, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
+                                                  (cudaStream_t)stream);
   return launch_tc<128, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
                                                 (cudaStream_t)stream);
 }

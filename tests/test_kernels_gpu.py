@@ -291,7 +291,8 @@ def _interleave(gate, up, b=64):
         2 * I, -1).contiguous()
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 1536, 576), (70, 192, 104), (2048, 256, 96)])
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 1536, 576), (70, 192, 104), (2048, 256, 96),
+                                   (2200, 4288, 72)])     # wide tiles of two gate|up pairs
 def test_gemm_tc_silu(ops, M, I, K):
     x = rnd(M, K, dtype=torch.bfloat16)
     gate = rnd(I, K, dtype=torch.bfloat16, seed=1, scale=0.3)

@@ -115,11 +115,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y;
+  const int b = blockIdx.z, h = blockIdx.x;
   const int kvh = h / (nh / nkv);
   const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
-  // heavy tiles (late queries, many keys) first
-  const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // heavy tiles (late queries, many keys) first, and of all heads before any lighter tile:
+  // CTAs are handed out with x fastest
+  const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int q0 = q_tile * kPfBQ;
   if (q0 >= n_new) return;
   const int start = seq_start[b];
@@ -396,7 +397,8 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
                                       unsigned int* fault, void* stream) {
   if (B <= 0 || T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
-      window < 0 || !(scale > 0.f) || max_new <= 0 || nh > 65535 || B > 65535 || ldq % 8 || ldo % 8)
+      window < 0 || !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
+      (max_new + kPfBQ - 1) / kPfBQ > 65535)
     return kBadArgument;
   if (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) & 15) return kMisaligned;
   const long long cache_rows = n_blocks * nkv * kPfBlk;
@@ -410,7 +412,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cudaStream_t st = (cudaStream_t)stream;
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((max_new + kPfBQ - 1) / kPfBQ, nh, B);
+  cfg.gridDim = dim3(nh, (max_new + kPfBQ - 1) / kPfBQ, B);
   cfg.blockDim = dim3(kPfThreads);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = st;

@@ -115,12 +115,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.x;
+  const int b = blockIdx.y, h = blockIdx.x;
   const int kvh = h / (nh / nkv);
   const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
-  // heavy tiles (late queries, many keys) first, and of all heads before any lighter tile:
-  // CTAs are handed out with x fastest
-  const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;
+  // heavy tiles (late queries, many keys) first, and of all heads and sequences before any
+  // lighter tile: CTAs are handed out with x fastest and z slowest
+  const int q_tile = (int)gridDim.z - 1 - (int)blockIdx.z;
   const int q0 = q_tile * kPfBQ;
   if (q0 >= n_new) return;
   const int start = seq_start[b];
@@ -412,7 +412,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cudaStream_t st = (cudaStream_t)stream;
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(nh, (max_new + kPfBQ - 1) / kPfBQ, B);
+  cfg.gridDim = dim3(nh, B, (max_new + kPfBQ - 1) / kPfBQ);
   cfg.blockDim = dim3(kPfThreads);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = st;

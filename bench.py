@@ -175,7 +175,8 @@ def run_e2e(engine, batch, steps, prompt_len):
     import torch
     rng = np.random.default_rng(3)
     prompts = [rng.integers(0, engine.vocab_size, size=prompt_len).tolist() for _ in range(batch)]
-    engine.generate(prompts, max_tokens=4, stop_ids=[])          # warm-up: builds the graph
+    for _ in range(2):      # warm-up: the decode graph, and the prefill step's on its second run
+        engine.generate(prompts, max_tokens=4, stop_ids=[])
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     res = engine.generate(prompts, max_tokens=steps, stop_ids=[])

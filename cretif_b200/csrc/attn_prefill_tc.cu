@@ -13,6 +13,12 @@
 //              maximum and sum in 32-bit, write P as bfloat16 into shared memory in the
 //              swizzled operand layout, then fold O_blk into their part of the output row,
 //              which stays in registers.
+// S, P and O_blk exist twice (for head sizes up to 64; larger heads have one P): the scores
+// of step j + 1 are computed while the softmax of step j runs, and the softmax threads fold
+// O_blk of step j in only after they have sent P of step j + 1, so they never wait for a
+// product.  What bounds a step then is the softmax itself: 128 x 128 exponentials at the
+// special-function unit's 16 a cycle.  Heavy query tiles (late queries) of all heads and
+// sequences are handed out before any lighter one.
 // The reference materialises [heads, S, kv_len] scores and transposes the cache for every
 // call (src/attention.cu:644-728); nothing of that exists here.
 //

@@ -1,15 +1,19 @@
 // C[M,N] (= or +=) A[M,K] · W[N,K]^T on the fifth-generation tensor cores (prefill).
 //
-// One CTA computes a 128 x BN tile.  Warp 0 is the producer: it moves 128x64 tiles of A and
-// BNx64 tiles of W from global to shared memory with TMA (128-byte swizzle; rows and
-// columns beyond the matrices are filled with zeros, so any M, N and K % 8 == 0 work)
-// through a ring of stages guarded by full/empty mbarriers.  One thread of warp 1 issues
-// tcgen05.mma (M=128, N=BN, K=16, bf16 in, f32 accumulate) on shared-memory descriptors
-// into a 128 x BN accumulator in tensor memory and commits each stage back to the producer.
-// Warps 2-5 read the accumulator with tcgen05.ld (each thread one row) and store it as
-// bfloat16 or float32, or add it into a float32 matrix (the residual stream).
-// Both operands are K-major exactly as activations [tokens, in] and weights [out, in] lie in
-// memory, so nothing is transposed.
+// A CTA is persistent: it computes 128 x BN tiles one after another (as many CTAs as fit the
+// chip, each taking every gridDim.x-th tile).  Warp 0 is the producer: it moves 128x64
+// tiles of A and BNx64 tiles of W from global to shared memory with TMA (128-byte swizzle;
+// rows and columns beyond the matrices are filled with zeros, so any M, N and K % 8 == 0
+// work) through a ring of stages guarded by full/empty mbarriers, which runs on from tile to
+// tile.  One thread of warp 1 issues tcgen05.mma (M=128, N=BN, K=16, bf16 in, f32
+// accumulate) on shared-memory descriptors into one of two 128 x BN accumulators in tensor
+// memory and commits each stage back to the producer.  Warps 2-5 read an accumulator with
+// tcgen05.ld (each thread one row) while the next tile's product fills the other, and store
+// it as bfloat16 or float32, add it into a float32 matrix (the residual stream), or run one
+// of the fused epilogues below.  Both operands are K-major exactly as activations
+// [tokens, in] and weights [out, in] lie in memory, so nothing is transposed.  The kernel is
+// a programmatic dependent of the one before it: set-up and the first W tiles precede the
+// wait.
 //
 // The reference runs every product on a 32x32-tile CUDA-core kernel
 // (src/kernels/matmul.cu:74-127); this kernel has no counterpart there.

@@ -110,8 +110,8 @@ static int launch_stream(const FusedParams& whole, int tiles, cudaStream_t st) {
   const int max_ctas = per_sm * sm_count / groups > 0 ? per_sm * sm_count / groups : 1;
   // every CTA the same number of tiles (to within one): 384 tiles on 296 seats run as
   // 192 CTAs of two tiles, not as 296 of which 88 work twice as long
-  const int rounds = (tiles + max_ctas - 1) / max_ctas;
-  const int grid = (tiles + rounds - 1) / rounds;
+  const int waves = (tiles + max_ctas - 1) / max_ctas;
+  const int grid = (tiles + waves - 1) / waves;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, groups);
   cfg.blockDim = dim3(kStThreads);

@@ -73,7 +73,7 @@ struct StepParams {
 
 constexpr unsigned kGridSpinLimit = 1u << 22;
 
-// Ask L2 for a matrix the grid will read soon (one 128-byte line per thread and round), so
+// Ask L2 for a matrix the grid will read soon (one 128-byte line per thread and pass), so
 // that the phase that needs it finds it on the chip: weights of the next layer travel while
 // this layer computes and waits at its barriers.
 __device__ __forceinline__ void prefetch_l2(const void* base, size_t bytes, int cta, int P) {

@@ -586,8 +586,8 @@ extern "C" int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, in
   if (((uintptr_t)act) & 15) return kMisaligned;
   TcEpi ep = {};
   ep.act = (__nv_bfloat16*)act; ep.I = I;
-  // wide tiles (two gate|up pairs, one CTA per SM) once there are four rounds of them for the
-  // whole chip; with fewer, the last round's empty seats cost more than the wide tile saves
+  // wide tiles (two gate|up pairs, one CTA per SM) once there are four waves of them for the
+  // whole chip; with fewer, the last wave's empty seats cost more than the wide tile saves
   const long long wide_tiles = (long long)((2 * I + 255) / 256) * ((M + kTcBM - 1) / kTcBM);
   if (wide_tiles >= 4 * 148)
     return launch_tc<256, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
@@ -616,7 +616,7 @@ extern "C" int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q,
   const int N = (nh + 2 * nkv) * hd;
   cudaStream_t st = (cudaStream_t)stream;
   // A tile is a whole number of heads.  Small products want many narrow tiles; large ones
-  // (two rounds of 128-wide tiles and more) do more arithmetic per byte with wide ones.
+  // (two waves of 128-wide tiles and more) do more arithmetic per byte with wide ones.
   const long long wide_tiles = (long long)((N + 127) / 128) * ((M + kTcBM - 1) / kTcBM);
   if (hd == 64 && wide_tiles < 2 * 148)
     return launch_tc<64, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);

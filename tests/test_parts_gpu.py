@@ -295,7 +295,7 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     for r, want in zip(reqs, wants):
         assert rel_err(run_whole(eng, r), want) < 1e-4
         assert rel_err(run_tail_by_one(eng, r, tail=10), want) < 1e-4
-    for _ in range(2):          # the second round takes the slots (and their state) again
+    for _ in range(2):          # the second pass takes the slots (and their state) again
         outs = run_batch(eng, reqs, [30, 2, 23])
         for got, want in zip(outs, wants):
             assert rel_err(got, want) < 1e-4

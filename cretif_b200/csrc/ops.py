@@ -341,14 +341,22 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
     shared memory is some 5 us shorter than the one through global scratch; a range is a
     cache block or more, and a block costs about 0.3 us.  So the cluster is taken unless it
     would make a CTA walk 16 blocks more than the plain split would (a long context with
-    few sequences).  (Clusters of 16, which the hardware takes as an opt-in size, were
-    measured: no gain for one sequence, twice the time for eight: too few of them fit the
-    chip at once.)"""
+    few sequences).  Cluster sizes are powers of two: at batch 16 and 32 of a 3-kv-head model
+    clusters of 6 and 3 took 13.8 and 20.0 us against 9.2 and 12.7 us for 4.  A grid beyond two
+    CTAs per SM runs with the shallow ring and in more than one wave, which ranges of up to
+    sixteen blocks do not pay for (batch 16 with 8 and 4 ranges: 11.0 and 9.2 us at a context
+    of 2,100, 14.3 and 11.5 us at 3,000, 16.4 and 13.7 us at 4,000), so a cluster of 8 becomes
+    one of 4 there (4 against 2 at batch 32: 12.7 and 14.3 us, so no further).  (Clusters of
+    16, which the hardware takes as an opt-in size, were measured: no gain for one sequence,
+    twice the time for eight: too few of them fit the chip at once.)"""
     tiles = max(1, -(-max_context // 64))
     n_split = decode_splits(B, nkv, max_context, device)
     if hd > 128 or _decode_simt_only:
         return n_split, False
     n_cluster = max(1, min(n_split, tiles, CLUSTER_MAX_RANGES))
+    n_cluster = 1 << (n_cluster.bit_length() - 1)     # clusters of 3, 6 or 7 CTAs place badly
+    if n_cluster > 4 and n_cluster * B * nkv > 2 * sm_count(device) and tiles <= 16 * n_cluster:
+        n_cluster //= 2
     if -(-tiles // n_cluster) - -(-tiles // n_split) < 16:
         return n_cluster, True
     return n_split, False

@@ -499,7 +499,10 @@ def test_decode_plan(ops):
     n, cluster = ops.decode_plan(8, 3, 2100, DEV)
     assert cluster and 1 <= n <= ops.CLUSTER_MAX_RANGES
     n, cluster = ops.decode_plan(64, 3, 2100, DEV)
-    assert cluster and n <= 3
+    assert cluster and n <= 2
+    for batch in (1, 5, 8, 12, 16, 24, 32, 48):        # cluster sizes are powers of two
+        n, cluster = ops.decode_plan(batch, 3, 2100, DEV)
+        assert cluster and n & (n - 1) == 0
     # one long sequence: more ranges than a cluster holds
     n, cluster = ops.decode_plan(1, 1, 64 * 1024, DEV)
     assert not cluster and n > ops.CLUSTER_MAX_RANGES

@@ -123,6 +123,10 @@ long long cretif_stream_min_bytes(void);
 // ... for calls of at most this many tokens (default 64; beyond 16 as groups of 16 rows).
 // Returns the old limit.
 int cretif_set_stream_max_rows(int rows);
+// The register variant with more than eight rows and a norm prologue shares the rows'
+// normalisation among the CTAs of a thread-block cluster of up to n (1: every CTA norms
+// every row itself; at most 4, the default).  Returns the old value; n < 1 leaves it.
+int cretif_set_fused_cluster(int n);
 // Depth of that variant's ring of stages (2..8); 0, the default, chooses per launch.  early
 // (>= 0; negative leaves it) is the number of stages whose weights are asked for before the
 // kernel waits for the one before it.  Returns the old depth.

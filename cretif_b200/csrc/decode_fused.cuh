@@ -357,6 +357,100 @@ __device__ __forceinline__ void norm_rows_to_smem(const FusedParams& p, unsigned
   }
 }
 
+// The same prologue shared by the CTAs of a thread-block cluster (all of one group of rows):
+// every CTA needs every row, and 192 CTAs that each pull 32 rows of float32 through L2 spend
+// more time on that than on their weights.  Here the cluster's warps take one row each
+// (row = rank * 8 + warp, then on by the cluster's warps), and store the normed row into
+// the shared memory of every CTA of the cluster; a cluster barrier ends the prologue.
+constexpr int kFuClusterMax = 4;
+
+template <int REGS, int N>
+__device__ __forceinline__ void norm_rows_to_cluster(const FusedParams& p, unsigned char* xs,
+                                                     int xs_stride, int warp, int lane,
+                                                     float4* nws, const NormStash<N>& st,
+                                                     uint32_t csize) {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int n4 = p.K >> 2;
+  const bool stash = p.K <= NormStash<N>::kMaxK;
+  const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+  const bool fits = n4 <= 32 * REGS;
+  const uint32_t local = (uint32_t)__cvta_generic_to_shared(xs);
+  uint32_t base[kFuClusterMax];
+#pragma unroll
+  for (uint32_t t = 0; t < (uint32_t)kFuClusterMax; ++t) {
+    base[t] = local;
+    if (t < csize)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base[t]) : "r"(local), "r"(t));
+  }
+  bool first = true;
+  for (int m = (int)rank * kFuWarps + warp; m < p.M || first; m += (int)csize * kFuWarps) {
+    const bool row = m < p.M;
+    const float4* h4 = reinterpret_cast<const float4*>(
+        p.H + (size_t)(row ? (p.rows ? p.rows[m] : m) : 0) * p.K);
+    float4 v[REGS];
+    if (row && fits) {
+#pragma unroll
+      for (int u = 0; u < REGS; ++u) {
+        const int i = u * 32 + lane;
+        v[u] = i < n4 ? __ldcg(h4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    if (first) {
+      first = false;
+      if (stash) {
+#pragma unroll
+        for (int u = 0; u < N; ++u) {
+          const int i = warp * 32 + lane + u * kFuWarps * 32;
+          if (i < n4) nws[i] = st.w[u];
+        }
+      }
+      __syncthreads();
+    }
+    if (!row) break;
+    const uint32_t row_off = (uint32_t)m * (uint32_t)xs_stride;
+    auto put = [&](int i, const float4& t, float inv) {
+      const float4 w = stash ? nws[i] : __ldg(w4 + i);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * w.x * inv, t.y * w.y * inv);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(t.z * w.z * inv, t.w * w.w * inv);
+      const uint32_t a = *reinterpret_cast<uint32_t*>(&lo), b = *reinterpret_cast<uint32_t*>(&hi);
+      const uint32_t off = row_off + 8u * (uint32_t)i;
+#pragma unroll
+      for (uint32_t t2 = 0; t2 < (uint32_t)kFuClusterMax; ++t2)
+        if (t2 < csize)
+          asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(base[t2] + off), "r"(a),
+                       "r"(b)
+                       : "memory");
+    };
+    float ss = 0.f;
+    if (fits) {
+#pragma unroll
+      for (int u = 0; u < REGS; ++u)
+        ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll
+      for (int u = 0; u < REGS; ++u) {
+        const int i = u * 32 + lane;
+        if (i < n4) put(i, v[u], inv);
+      }
+    } else {
+#pragma unroll 8
+      for (int i = lane; i < n4; i += 32) {
+        const float4 t = __ldcg(h4 + i);
+        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)p.K + p.eps);
+#pragma unroll 4
+      for (int i = lane; i < n4; i += 32) put(i, __ldcg(h4 + i), inv);
+    }
+  }
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 constexpr int kFuPre = 3;      // weight chunks per warp fetched ahead (covers K <= 768)
 
 template <int EPI>
@@ -421,8 +515,14 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
 
   if (PRO == kProNorm) {
     float4* nws = reinterpret_cast<float4*>(xs + (size_t)p.M * xs_stride);
-    norm_rows_to_smem<8>(p, xs, xs_stride, warp, lane, nws, stash, [] { __syncthreads(); });
-    __syncthreads();
+    uint32_t csize = 1;        // (launched without clusters: 1)
+    if (NT > 1) asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+    if (NT > 1 && csize > 1) {
+      norm_rows_to_cluster<8>(p, xs, xs_stride, warp, lane, nws, stash, csize);
+    } else {
+      norm_rows_to_smem<8>(p, xs, xs_stride, warp, lane, nws, stash, [] { __syncthreads(); });
+      __syncthreads();
+    }
   }
 
   for (; tile < n_tiles; tile += tile_stride) {

@@ -42,6 +42,9 @@ def lib():
         tune = os.environ.get("CRETIF_STREAM_MAX_ROWS")
         if tune:
             L.cretif_set_stream_max_rows(int(tune))
+        tune = os.environ.get("CRETIF_FUSED_CLUSTER")
+        if tune:
+            L.cretif_set_fused_cluster(int(tune))
         tune = os.environ.get("CRETIF_STREAM_STAGES")
         if tune:
             L.cretif_set_stream_stages(int(tune), int(os.environ.get("CRETIF_STREAM_EARLY", "-1")))
@@ -458,6 +461,12 @@ def set_stream_stages(n: int, early: int = -1) -> int:
     negative, how many stages of weights it asks for before waiting for the kernel before
     it; returns the old depth."""
     return int(lib().cretif_set_stream_stages(int(n), int(early)))
+
+
+def set_fused_cluster(n: int) -> int:
+    """Largest thread-block cluster that shares the norm prologue of the register variant
+    (more than eight rows; 1: none, at most 4); returns the old value."""
+    return int(lib().cretif_set_fused_cluster(int(n)))
 
 
 def set_dependent_launch(on: bool) -> bool:

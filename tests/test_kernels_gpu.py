@@ -118,16 +118,20 @@ def test_gemm_tc(ops, M, N, K, bn):
 
 
 # ------------------------------------------------------------------ fused decode projections
-@pytest.fixture(params=[(1 << 20, 1 << 40), (64, 0)], ids=["registers", "streamed"])
+@pytest.fixture(params=[(1 << 20, 1 << 40, 4), (1 << 20, 1 << 40, 1), (64, 0, 4)],
+                ids=["registers", "registers-no-cluster", "streamed"])
 def fused_variant(request, ops):
     """The fused product has two bodies: weights through registers (narrow, small matrices)
     and through a shared-memory ring (wide or large ones).  Every fused test runs with
     thresholds that keep the test matrices in registers, and with ones that send them
-    through the ring."""
+    through the ring; the register body with more than eight rows runs with its norm
+    prologue shared by a thread-block cluster, and with every CTA on its own."""
     old_bytes = ops.stream_min_bytes()
-    old_k = ops.set_stream_min_k(*request.param)
+    old_k = ops.set_stream_min_k(*request.param[:2])
+    old_cluster = ops.set_fused_cluster(request.param[2])
     yield request.param[0]
     ops.set_stream_min_k(old_k, old_bytes)
+    ops.set_fused_cluster(old_cluster)
 
 
 def _norm_bf16(h, w, eps, rows=None):

@@ -4,7 +4,8 @@
 //
 //   prologue NORM   x = bf16(h * w_norm * rsqrt(mean(h^2) + eps)) computed by every CTA from the
 //                   32-bit residual stream (a few KB for a decode batch) into shared memory,
-//                   optionally from gathered rows (the rows whose logits are wanted);
+//                   optionally from gathered rows (the rows whose logits are wanted); with
+//                   more than 8 rows the CTAs of a thread-block cluster share that work;
 //   epilogue ROPE   the stacked q|k|v product: rotary pairs of q and k are rotated in 32-bit,
 //                   q goes to the query buffer, rotated k and v go straight into the block
 //                   cache at each token's position;

@@ -56,6 +56,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
       row = ((unsigned long long)blk * nkv + kvh) * bt + (key % bt);
       const T* kp = kc + row * hd;
       float dot = 0.f;
+#pragma unroll 4
       for (int d = 0; d < hd; d += 8) {
         float kv[8];
         load8(kp + d, kv);
@@ -71,16 +72,33 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
 #pragma unroll
     for (int i = 0; i < kMaxHd / 32; ++i) acc[i] *= corr;
     m = m_new;
+    // Values: keys in ascending order, eight at a time so that their loads travel together
+    // (a decode step has one warp per head and nothing else to hide a load behind).  A key
+    // with p = 0 (masked, or underflowed) adds nothing and is not read.
     const int n_valid = min(32, pos + 1 - base);
-    for (int j = 0; j < n_valid; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const unsigned long long rj = __shfl_sync(0xffffffffu, row, j);
-      if (pj == 0.f) continue;        // masked, or underflowed: adds nothing
-      const T* vp = vc + rj * hd;
+    constexpr int kAhead = 8;
+    for (int j0 = 0; j0 < n_valid; j0 += kAhead) {
+      float pj[kAhead];
+      const T* vp[kAhead];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int j = min(j0 + u, 31);
+        const float pu = __shfl_sync(0xffffffffu, p, j);
+        const unsigned long long ru = __shfl_sync(0xffffffffu, row, j);
+        pj[u] = j0 + u < n_valid ? pu : 0.f;
+        vp[u] = vc + ru * hd;
+      }
 #pragma unroll
       for (int i = 0; i < kMaxHd / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, to_float(vp[d]), acc[i]);
+        if (d < hd) {
+          float v[kAhead];
+#pragma unroll
+          for (int u = 0; u < kAhead; ++u) v[u] = pj[u] != 0.f ? to_float(vp[u][d]) : 0.f;
+#pragma unroll
+          for (int u = 0; u < kAhead; ++u)
+            if (pj[u] != 0.f) acc[i] = fmaf(pj[u], v[u], acc[i]);
+        }
       }
     }
   }

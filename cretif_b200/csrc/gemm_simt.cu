@@ -30,15 +30,28 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
 #pragma unroll
     for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
+  // The next k-slab's operands are asked for while this one is multiplied (a product of few
+  // rows is a handful of CTAs with nothing else to hide a load behind); the order of the
+  // sums does not change.
+  const int am = m0 + lrow, wn = n0 + lrow;
+  float ra[4], rw[4];
+  auto fetch = [&](int k0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int k = k0 + lk + e;
-      const int am = m0 + lrow, wn = n0 + lrow;
-      As[lk + e][lrow] = (am < M && k < K) ? to_float(A[(size_t)am * lda + k]) : 0.f;
-      Ws[lk + e][lrow] = (wn < N && k < K) ? to_float(W[(size_t)wn * ldw + k]) : 0.f;
+      ra[e] = (am < M && k < K) ? to_float(A[(size_t)am * lda + k]) : 0.f;
+      rw[e] = (wn < N && k < K) ? to_float(W[(size_t)wn * ldw + k]) : 0.f;
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      As[lk + e][lrow] = ra[e];
+      Ws[lk + e][lrow] = rw[e];
     }
     __syncthreads();
+    if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float a[TM], w[TN];

@@ -1,4 +1,4 @@
-// Causal grouped-query attention over the block cache, one warp per (token, query head).
+// Causal grouped-query attention over the block cache, one CTA per (token, query head).
 //
 // The plain attention kernel: it serves prefill and decode alike, in 32-bit and in
 // bfloat16 storage, for any number of heads and groups, head sizes in steps of 8 up to
@@ -7,14 +7,19 @@
 // dot (src/attention.cu:690-692), keys after the query's position are masked (:60-77),
 // softmax with running maximum and sum in 32-bit as in the reference's decode kernel
 // (:451-493), query head h reads key/value head h / (heads / kv_heads) (:421-422).
-// A (token, head) is always reduced in the same order, so its output does not depend on
-// what else is in the batch or on how the tokens were cut into steps.
+// The CTA's eight warps take the keys in blocks of 32 in turn (warp w: blocks w, w + 8, ...),
+// each with its own running maximum, sum and output, and warp 0 folds the eight results
+// together in the order of the warps: a decode step, whose one query per head would otherwise
+// be one warp walking thousands of keys with every load's latency exposed, is eight chains
+// of an eighth the length.  A (token, head) is always reduced in the same order, so its
+// output does not depend on what else is in the batch or on how the tokens were cut into
+// steps.
 #include "api.h"
 #include "common.cuh"
 
 namespace cretif {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kMaxHd = 256;
 
 template <typename T>
@@ -25,10 +30,11 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
                  int window, int bt, int T_tokens) {
-  __shared__ float qs[kWarps][kMaxHd];
+  __shared__ float qs[kMaxHd];
+  __shared__ float part_acc[kWarps][kMaxHd];
+  __shared__ float part_m[kWarps], part_l[kWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarps + warp;
-  if (item >= (long long)T_tokens * nh) return;
+  const long long item = blockIdx.x;
   const int t = (int)(item / nh), h = (int)(item - (long long)t * nh);
   const int kvh = h / (nh / nkv);
   const int pos = tok_pos[t];
@@ -37,15 +43,15 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
 
   const T* qrow = q + (size_t)t * ldq + (size_t)h * hd;
-  for (int d = lane; d < hd; d += 32) qs[warp][d] = to_float(qrow[d]);
-  __syncwarp();
+  for (int d = threadIdx.x; d < hd; d += kWarps * 32) qs[d] = to_float(qrow[d]);
+  __syncthreads();
 
   float m = -INFINITY, l = 0.f;
   float acc[kMaxHd / 32];
 #pragma unroll
   for (int i = 0; i < kMaxHd / 32; ++i) acc[i] = 0.f;
 
-  for (int base = first; base <= pos; base += 32) {
+  for (int base = first + 32 * warp; base <= pos; base += 32 * kWarps) {
     const int key = base + lane;
     bool valid = key <= pos;
     float s = -INFINITY;
@@ -61,7 +67,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
         float kv[8];
         load8(kp + d, kv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qs[warp][d + e], kv[e], dot);
+        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
       }
       s = dot * scale;
     }
@@ -102,7 +108,37 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
       }
     }
   }
-  const float inv = 1.0f / l;
+  // the warps' results meet in shared memory; warp 0 folds them in the warps' order
+  if (lane == 0) {
+    part_m[warp] = m;
+    part_l[warp] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxHd / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < hd) part_acc[warp][d] = acc[i];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float m_all = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, part_m[w]);
+  float l_all = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxHd / 32; ++i) acc[i] = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const float mw = part_m[w];
+    if (mw == -INFINITY) continue;              // a warp without a visible key adds nothing
+    const float a = expf(mw - m_all);
+    l_all += part_l[w] * a;
+#pragma unroll
+    for (int i = 0; i < kMaxHd / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) acc[i] = fmaf(part_acc[w][d], a, acc[i]);
+    }
+  }
+  const float inv = 1.0f / l_all;
   T* orow = out + (size_t)t * ldo + (size_t)h * hd;
 #pragma unroll
   for (int i = 0; i < kMaxHd / 32; ++i) {
@@ -126,7 +162,8 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
     return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const long long items = (long long)T * nh;
-  const unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
+  if (items > 0x7fffffffLL) return kBadArgument;
+  const unsigned blocks = (unsigned)items;
   if (dt == kF32)
     attn_simt_kernel<float><<<blocks, kWarps * 32, 0, st>>>(
         (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, table,

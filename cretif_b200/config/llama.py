@@ -18,6 +18,10 @@ rms_norm_eps               default 1e-5 (src/gguf_parser.cpp:730-736)
 rope_theta                 default 10000 (src/gguf_parser.cpp:722-728)
 tie_word_embeddings        ``output.weight`` absent (src/gguf_parser.cpp:761-765)
 eos_token_id/bos_token_id  ``tokenizer.ggml.{eos,bos}_token_id``
+sliding_window             none (the reference attends to every earlier key); an
+                           integer W lets a query see the last W keys only
+layer_types                none; with ``sliding_window``, a list that names each
+                           layer ``"sliding_attention"`` or ``"full_attention"``
 =========================  ===================================================
 
 Validation follows src/attention.cu:517-540 (heads > 0, even head size, heads
@@ -30,7 +34,7 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
 from .registry import ConfigError, register_architecture
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .spec import ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
 
 _REQUIRED = ("hidden_size", "num_hidden_layers", "num_attention_heads",
              "intermediate_size", "vocab_size")
@@ -51,6 +55,8 @@ class LlamaConfig:
     rope_interleaved: bool = False
     tie_word_embeddings: bool = False
     hidden_act: str = "silu"
+    sliding_window: Optional[int] = None
+    layer_types: Optional[List[str]] = None
     eos_token_ids: List[int] = field(default_factory=list)
     bos_token_id: Optional[int] = None
     torch_dtype: Optional[str] = None
@@ -90,6 +96,27 @@ class LlamaConfig:
             raise ConfigError(f"rope_theta must be positive, got {self.rope_theta!r}")
         if self.hidden_act != "silu":
             raise ConfigError(f"hidden_act {self.hidden_act!r} is not supported (only 'silu')")
+        w = self.sliding_window
+        if w is not None and (not isinstance(w, int) or isinstance(w, bool) or w <= 0):
+            raise ConfigError(f"sliding_window must be a positive integer or null, got {w!r}")
+        if self.layer_types is not None:
+            kinds = ("full_attention", "sliding_attention")
+            if (not isinstance(self.layer_types, (list, tuple))
+                    or len(self.layer_types) != self.num_hidden_layers
+                    or any(t not in kinds for t in self.layer_types)):
+                raise ConfigError(f"layer_types must name each of the {self.num_hidden_layers} "
+                                  f"layers one of {kinds}, got {self.layer_types!r}")
+            if w is None and "sliding_attention" in self.layer_types:
+                raise ConfigError("layer_types asks for sliding_attention but sliding_window "
+                                  "is not given")
+
+    def window_of(self, layer: int) -> int:
+        """Keys a query of this layer sees (0: all of them)."""
+        if self.sliding_window is None:
+            return 0
+        if self.layer_types is not None and self.layer_types[layer] != "sliding_attention":
+            return 0
+        return int(self.sliding_window)
 
     def to_dict(self) -> Dict[str, Any]:
         """The config.json this configuration is read back from."""
@@ -114,6 +141,10 @@ class LlamaConfig:
         }
         if self.rope_interleaved:
             d["rope_interleaved"] = True
+        if self.sliding_window is not None:
+            d["sliding_window"] = self.sliding_window
+        if self.layer_types is not None:
+            d["layer_types"] = list(self.layer_types)
         if self.eos_token_ids:
             d["eos_token_id"] = (self.eos_token_ids[0] if len(self.eos_token_ids) == 1
                                  else list(self.eos_token_ids))
@@ -177,6 +208,8 @@ def llama_config_from_dict(raw: Dict[str, Any]) -> LlamaConfig:
         rope_interleaved=bool(raw.get("rope_interleaved", False)),
         tie_word_embeddings=bool(raw.get("tie_word_embeddings", False)),
         hidden_act=str(raw.get("hidden_act", "silu")),
+        sliding_window=raw.get("sliding_window"),
+        layer_types=raw.get("layer_types"),
         eos_token_ids=eos_ids,
         bos_token_id=raw.get("bos_token_id"),
         torch_dtype=raw.get("torch_dtype"),
@@ -194,16 +227,17 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
     norm = PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps})
     position = {"kind": "rotary", "theta": cfg.rope_theta, "rotary_dim": cfg.head_dim,
                 "pairing": "interleaved" if cfg.rope_interleaved else "half"}
-    mixer = PartSpec("attention", {
-        "num_heads": cfg.num_attention_heads,
-        "num_kv_heads": cfg.num_key_value_heads,
-        "head_dim": cfg.head_dim,
-        "scale": cfg.head_dim ** -0.5,       # 1/sqrt(hd), src/attention.cu:690-692
-        "window": 0,                          # causal over all keys
-        "position": position,
-        "names": {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight",
-                  "v": "self_attn.v_proj.weight", "o": "self_attn.o_proj.weight"},
-    })
+    def mixer(i: int) -> PartSpec:
+        return PartSpec("attention", {
+            "num_heads": cfg.num_attention_heads,
+            "num_kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim,
+            "scale": cfg.head_dim ** -0.5,       # 1/sqrt(hd), src/attention.cu:690-692
+            "window": cfg.window_of(i),          # 0: causal over all keys, as the reference
+            "position": position,
+            "names": {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight",
+                      "v": "self_attn.v_proj.weight", "o": "self_attn.o_proj.weight"},
+        })
     ffn = PartSpec("gated_mlp", {
         "intermediate_size": cfg.intermediate_size,
         "activation": cfg.hidden_act,
@@ -211,12 +245,11 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
                   "down": "mlp.down_proj.weight"},
     })
     layers = [
-        LayerSpec(prefix=f"model.layers.{i}.", mixer=mixer, feed_forward=ffn,
-                  mixer_norm=PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps,
-                                                  "name": "input_layernorm.weight"}),
-                  feed_forward_norm=PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps,
-                                                         "name": "post_attention_layernorm.weight"}),
-                  arrangement="prenorm")
+        prenorm_layer(f"model.layers.{i}.", mixer(i), ffn,
+                      PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps,
+                                           "name": "input_layernorm.weight"}),
+                      PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps,
+                                           "name": "post_attention_layernorm.weight"}))
         for i in range(cfg.num_hidden_layers)
     ]
     return ModelSpec(

@@ -14,7 +14,7 @@ constants from weights is kept, but the loop itself is data.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -29,20 +29,44 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
-class LayerSpec:
-    """A block: a mixer and a feed-forward, each behind its own norm.
+class BranchSpec:
+    """One residual branch of a block: ``h += post_norm(part(norm(h)))``.
 
-    ``arrangement`` names how the parts are wired (``"prenorm"``: ``h += mixer(norm1(h))``
-    then ``h += ffn(norm2(h))``, the order of src/model.cu:887-1018).
-    ``prefix`` is the weight-name prefix of the layer (``model.layers.3.``).
+    ``role`` is the part's category (``"mixer"`` or ``"feed_forward"``); ``norm`` stands
+    before the part and ``post_norm`` after it, and either may be absent.
+    """
+
+    role: str
+    part: PartSpec
+    norm: Optional[PartSpec] = None
+    post_norm: Optional[PartSpec] = None
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """A block: an ordered list of residual branches and the arrangement that wires them.
+
+    The reference's block is two branches, attention then feed-forward, each behind a
+    norm of its own (src/model.cu:887-1018); :func:`prenorm_layer` builds exactly that.
+    A block may as well have one branch, three, or norms after its parts.
+    ``arrangement`` names the registered function that runs the branches
+    (``"residual"``: one after the other).  ``prefix`` is the weight-name prefix of the
+    layer (``model.layers.3.``).
     """
 
     prefix: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    arrangement: str = "prenorm"
+    branches: Tuple[BranchSpec, ...]
+    arrangement: str = "residual"
+
+    def of_role(self, role: str) -> List[BranchSpec]:
+        return [b for b in self.branches if b.role == role]
+
+
+def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                  feed_forward_norm: PartSpec) -> LayerSpec:
+    """``h += mixer(norm1(h))`` then ``h += feed_forward(norm2(h))``."""
+    return LayerSpec(prefix, (BranchSpec("mixer", mixer, norm=mixer_norm),
+                              BranchSpec("feed_forward", feed_forward, norm=feed_forward_norm)))
 
 
 @dataclass(frozen=True)
@@ -82,6 +106,10 @@ class ModelSpec:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, "
                                  f"but the model has {len(self.layers)} layers")
+            for b in self.layers[e.layer].branches:
+                if b.role not in ("mixer", "feed_forward"):
+                    raise ValueError(f"layer {e.layer}: a branch's role is 'mixer' or "
+                                     f"'feed_forward', got {b.role!r}")
             if e.cache is not None:
                 if not 0 <= e.cache < i:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache}, "
@@ -89,3 +117,8 @@ class ModelSpec:
                 if self.schedule[e.cache].cache is not None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache}, "
                                      "which itself borrows a cache")
+                mine = [b.part for b in self.layers[e.layer].of_role("mixer")]
+                theirs = [b.part for b in self.layers[self.schedule[e.cache].layer].of_role("mixer")]
+                if len(mine) != len(theirs):
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache}, "
+                                     "whose layer has another number of mixers")

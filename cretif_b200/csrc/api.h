@@ -26,7 +26,8 @@ int cretif_add_rmsnorm(float* h, const void* delta, int delta_dt, const float* w
 int cretif_silu_mul(const void* gu, void* act, int dt, int T, int I, int block, void* stream);
 
 // Rotate q and k of every token by its position's angles (pairing 0: (j, j+rot/2),
-// 1: (2j, 2j+1)); q in place, rotated k and v into the block cache.
+// 1: (2j, 2j+1)); q in place.  write_cache bit 0: rotated k and v into the block cache;
+// bit 1: k rotated in place too (encoding only; with rot_dim 0 and bit 0 it only stores).
 int cretif_rope_kv_append(void* qkv, int ld, int dt, const float* cos_t, const float* sin_t,
                           int pairing, int rot_dim, int nh, int nkv, int hd, const int* tok_pos,
                           const int* tok_seq, const int* seq_slot, const int* table,
@@ -142,21 +143,22 @@ int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, 
                            int nh, int nkv, int hd, float scale, int window, int bt, int B,
                            int max_new, unsigned int* fault, void* stream);
 
-// The whole decode step in one persistent launch (see decode_step.cu).  Layer records are
-// built on the host with cretif_step_layer_fill and copied to the device by the caller.
-int cretif_step_layer_bytes(void);
-int cretif_decode_step_supported(int B, int hd);
-int cretif_step_layer_fill(void* dst, const void* w_qkv, const void* w_o, const void* w_gu,
-                           const void* w_down, const float* norm1, const float* norm2, float eps1,
-                           float eps2, void* kc, void* vc, long long n_blocks, int nkv, int hd,
-                           const int* table, int table_stride, int write_cache);
-int cretif_decode_step(const int* ints, const float* floats, void* const* ptrs, int ctas,
-                       void* stream);
+// One CTA waits, with the library's bounded wait, on a barrier that nothing completes; after
+// `limit` polls (at most 2^20) it gives up, sets bit 2 of *fault and returns.  *polls (may be
+// null) receives `limit` when the kernel has run.  Nothing faults or hangs: it exists so that
+// the path from an expired wait to the host's error can be exercised.
+int cretif_wait_that_expires(unsigned int limit, unsigned int* fault, unsigned int* polls,
+                             void* stream);
 
-// One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.
+// How often variant v of a kernel (cretif::Variant in common.cuh) has been launched; -1 for an
+// unknown v.  For tests that must know which path ran.
+int cretif_variant_count(int v);
+
+// One token id per row of logits: greedy (temperature <= 0), temperature, or top-k.  The
+// kernel reads the seed from *seed_dev when that is not null, else takes `seed`.
 int cretif_sample(const float* logits, int ld, int rows, int V, float temperature, int top_k,
-                  unsigned long long seed, const long long* request, int* draw, int* out,
-                  void* stream);
+                  unsigned long long seed, const unsigned long long* seed_dev,
+                  const long long* request, int* draw, int* out, void* stream);
 float cretif_uniform01(unsigned long long seed, long long request, int draw);
 int cretif_max_top_k(void);
 

@@ -64,6 +64,7 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
     attr[1].val.clusterDim.z = 1;
     cfg.numAttrs = 2;
   }
+  count_variant(CLUSTER ? kVarDecodeCluster : kVarDecodeSplit);
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, attn_decode_mma_kernel<HD16, CLUSTER>, mk, mv, (const __nv_bfloat16*)q, ldq, table,
       table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,

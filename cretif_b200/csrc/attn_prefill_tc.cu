@@ -428,6 +428,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
+  count_variant(kVarPrefillAttn);
   if (hd <= 64) {
     static int configured = 0;
     if (L.total > configured) {

@@ -1,11 +1,8 @@
 """Building and loading the kernel library.
 
-The ``.cu`` files beside this module are compiled with ``nvcc`` for sm_100a into shared
-libraries that are loaded with ``ctypes``: ``kernels`` holds everything a model's steps use,
-``step`` the optional whole-step kernel (``decode_step.cu``, half a minute of compile time
-on its own, off by default), which is built only when somebody asks for it.  A library's
-file name carries a hash of its sources and flags, so an edited source is never served by a
-stale build.  Libraries are looked for, and built at first need, in ``_build/`` beside the
+The ``.cu`` files beside this module are compiled with ``nvcc`` for sm_100a into one shared
+library (``kernels``) that is loaded with ``ctypes``.  The library's file name carries a hash
+of its sources and flags, so an edited source is never served by a stale build.  Libraries are looked for, and built at first need, in ``_build/`` beside the
 sources; if that folder cannot be written (a read-only installation) a per-user folder under
 the system's temporary directory is used instead.  While compiling, a line is printed to
 stderr for every file so that a first call does not look hung.
@@ -28,7 +25,7 @@ _ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 _NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
                "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
-_OPTIONAL = {"step": ["decode_step.cu"]}       # group -> its sources; the rest is "kernels"
+_OPTIONAL: dict = {}       # group -> sources of a library of its own; the rest is "kernels"
 _libs: dict = {}
 _lib_paths: dict = {}
 

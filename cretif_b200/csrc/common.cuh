@@ -115,6 +115,25 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// Which variant of a kernel a launch took, counted on the host at launch time (a replayed
+// CUDA graph counts nothing).  Tests read the counts to know that the path they mean to check
+// is the one that ran; nothing in the library depends on them.
+enum Variant : int {
+  kVarFusedRegisters = 0,   // fused projection, weights through registers, one row group
+  kVarFusedRowGroups,       // ... more than 32 rows as groups along gridDim.y
+  kVarFusedCluster2,        // ... norm prologue shared by clusters of two CTAs
+  kVarFusedCluster4,        // ... of four
+  kVarStream,               // fused projection, weights through a shared-memory ring
+  kVarStreamRowGroups,      // ... more than 16 rows as groups of 16
+  kVarDecodeCluster,        // decode attention merged inside a cluster
+  kVarDecodeSplit,          // decode attention merged through global scratch
+  kVarPrefillAttn,          // tcgen05 prefill attention
+  kVarTc64, kVarTc128, kVarTc256,   // tcgen05 product by tile width
+  kVarTcSeveralTiles,       // ... whose persistent CTAs walk more than one tile
+  kVarCount
+};
+void count_variant(int v);
+
 // Whether kernels that support it are launched as programmatic dependents of the kernel
 // before them (decode_fused.cu owns the switch).
 int dependent_launch_enabled();

@@ -8,6 +8,11 @@ namespace cretif {
 static int g_dependent_launch = 1;
 int dependent_launch_enabled() { return g_dependent_launch; }
 
+static int g_variant_counts[kVarCount];
+void count_variant(int v) {
+  if (v >= 0 && v < kVarCount) ++g_variant_counts[v];
+}
+
 // Largest cluster that shares a norm prologue (1: none; at most kFuClusterMax).
 static int g_fused_cluster = kFuClusterMax;
 
@@ -46,6 +51,8 @@ static int launch_fused(const FusedParams& p, int tiles, cudaStream_t st, int gr
     if ((int)grid.x < cluster) cluster = 1;
     grid.x -= grid.x % cluster;
   }
+  count_variant(groups > 1 ? kVarFusedRowGroups : kVarFusedRegisters);
+  if (cluster > 1) count_variant(cluster == 4 ? kVarFusedCluster4 : kVarFusedCluster2);
   if (g_dependent_launch || cluster > 1) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -159,6 +166,7 @@ static int launch_stream(const FusedParams& whole, int tiles, cudaStream_t st) {
   } else {
     map_x = map_w;
   }
+  count_variant(groups > 1 ? kVarStreamRowGroups : kVarStream);
   cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_stream_kernel<NT, PRO, EPI>, whole, map_w, map_x,
                                      tiles, stages, g_stream_early);
   return e == cudaSuccess ? launch_status() : (int)e;
@@ -238,6 +246,10 @@ extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, fl
       (gu_block && (I % gu_block || gu_block % 8)))
     return kBadArgument;
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
+}
+
+extern "C" int cretif_variant_count(int v) {
+  return v >= 0 && v < kVarCount ? g_variant_counts[v] : -1;
 }
 
 extern "C" int cretif_set_stream_min_k(int k, long long min_bytes) {

@@ -407,6 +407,9 @@ __device__ __forceinline__ void norm_rows_to_cluster(const FusedParams& p, unsig
         }
       }
       __syncthreads();
+      // every CTA of the cluster signalled at its start (skinny_fused_tiles): once all have,
+      // their shared memory exists and may be written from here
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     if (!row) break;
     const uint32_t row_off = (uint32_t)m * (uint32_t)xs_stride;
@@ -472,7 +475,7 @@ __device__ __forceinline__ void fetch_weights(const FusedParams& p, int tile, in
 
 // The body of the fused product for the CTA's share of tiles: tiles first_tile,
 // first_tile + tile_stride, ...  `pdl`: signal/await the neighbouring launches
-// (programmatic dependent launch); the whole-step kernel passes false.
+// (programmatic dependent launch).
 template <int NT, int PRO, int EPI>
 __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_tiles,
                                                    unsigned char* fsmem, int first_tile,
@@ -490,6 +493,14 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   const int n_chunks = (p.K + 31) >> 5;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+  // A cluster shares the norm prologue by storing into its CTAs' shared memory, which may
+  // only be touched once every CTA of the cluster runs: each says so here, at no cost, and
+  // waits for the others just before its first remote store (norm_rows_to_cluster).
+  if (NT > 1 && PRO == kProNorm) {
+    uint32_t csize = 1;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+    if (csize > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  }
   // The first tile's weights do not depend on anything computed before this kernel: ask for
   // them first, so that their latency runs under the prologue.
   int tile = first_tile;

@@ -155,8 +155,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
 }
 
 // ---------------------------------------------------------------- rotary + cache write
-// One block per token.  qkv row = [q heads | k heads | v heads]; q is rotated in place,
-// k is rotated and written to the cache, v is copied to the cache.
+// One block per token.  qkv row = [q heads | k heads | v heads]; q is rotated in place.
+// write_cache bit 0: rotated k and v go to the cache; bit 1: k is rotated in place as well
+// (position encoding alone, for a caller that stores the keys itself).
 template <typename T>
 __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, int pairing, int rot_dim,
@@ -175,7 +176,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int ld, const float* 
 
   size_t cache_row = 0;
   bool cache_ok = false;
-  if (write_cache) {
+  if (write_cache & 1) {
     const int slot = seq_slot[tok_seq[t]];
     const int blk = table[(size_t)slot * table_stride + pos / bt];
     if (blk < 0) {
@@ -198,10 +199,16 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int ld, const float* 
     if (head < nh) {
       hp[i0] = from_float<T>(y0);
       hp[i1] = from_float<T>(y1);
-    } else if (cache_ok) {
-      T* kp = kc + (cache_row + (size_t)(head - nh) * bt) * hd;
-      kp[i0] = from_float<T>(y0);
-      kp[i1] = from_float<T>(y1);
+    } else {
+      if (cache_ok) {
+        T* kp = kc + (cache_row + (size_t)(head - nh) * bt) * hd;
+        kp[i0] = from_float<T>(y0);
+        kp[i1] = from_float<T>(y1);
+      }
+      if (write_cache & 2) {
+        hp[i0] = from_float<T>(y0);
+        hp[i1] = from_float<T>(y1);
+      }
     }
   }
   if (!cache_ok) return;

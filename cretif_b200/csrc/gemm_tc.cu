@@ -530,6 +530,8 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  count_variant(BN == 64 ? kVarTc64 : BN == 128 ? kVarTc128 : kVarTc256);
+  if (tiles > resident) count_variant(kVarTcSeveralTiles);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, map_a, map_w, ep, M, N, K,
                                      fault, stages, g_tc_stamps, n_n_tiles, (int)tiles);
   return e == cudaSuccess ? launch_status() : (int)e;

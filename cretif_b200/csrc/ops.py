@@ -52,18 +52,25 @@ def lib():
     return _lib
 
 
-def step_lib():
-    """The optional library with the whole-step kernel, built when it is first asked for."""
-    lib()
-    return load_library(group="step")
-
-
 _launches = 0
 
 
 def launch_count() -> int:
     """Kernels launched through this module so far (graph replays are not counted)."""
     return _launches
+
+
+_VARIANTS = ("fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4", "stream",
+             "stream_row_groups", "decode_cluster", "decode_split", "prefill_attn", "tc64",
+             "tc128", "tc256", "tc_several_tiles")
+
+
+def variant_counts() -> dict:
+    """How often each variant of the kernels has been launched so far (the order is that of
+    ``cretif::Variant``); tests take differences to know which path a step took.  Launches
+    replayed from a CUDA graph are not counted."""
+    L = lib()
+    return {name: int(L.cretif_variant_count(i)) for i, name in enumerate(_VARIANTS)}
 
 
 def _check(code: int, what: str, kernels: int = 1) -> None:
@@ -166,27 +173,38 @@ def silu_mul(gu, act, block: int = 0) -> None:
 
 
 def rope_kv_append(qkv, cos, sin, pairing: int, rot_dim: int, nh: int, nkv: int, hd: int,
-                   tok_pos, tok_seq, seq_slot, table, kc, vc, block_tokens: int,
-                   write_cache: bool, fault) -> None:
+                   tok_pos, tok_seq=None, seq_slot=None, table=None, kc=None, vc=None,
+                   block_tokens: int = 64, write_cache: bool = True, fault=None,
+                   rotate_k_in_place: bool = False) -> None:
+    """Position-encode q (in place) and k of the packed ``[T, (nh + 2 nkv) hd]`` rows by a
+    rotation table, and/or store k and v at each token's position in the block cache.
+    ``write_cache``: rotated k, and v, go to the cache; ``rotate_k_in_place``: k is rotated in
+    the buffer as well (encoding alone).  ``rot_dim`` 0 rotates nothing (storing alone)."""
     _need(qkv, "qkv", dim=2)
     T, ld = qkv.shape[0], _rows(qkv, "qkv")
-    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
-    if rot_dim and (cos.shape[1] != rot_dim // 2 or not cos.is_contiguous()
-                    or not sin.is_contiguous()):
-        raise KernelError("rope_kv_append: cos/sin must be contiguous [positions, rot_dim/2]")
-    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (seq_slot, "seq_slot")):
-        _need(t, n, torch.int32, 1)
-    _need(table, "table", torch.int32, 2)
+    if rot_dim:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if (cos.shape[1] != rot_dim // 2 or not cos.is_contiguous() or not sin.is_contiguous()):
+            raise KernelError("rope_kv_append: cos/sin must be contiguous [positions, rot_dim/2]")
+    else:
+        cos = sin = None                       # nothing is rotated: the tables are not read
+    _need(tok_pos, "tok_pos", torch.int32, 1)
     if write_cache:
+        for t, n in ((tok_seq, "tok_seq"), (seq_slot, "seq_slot")):
+            _need(t, n, torch.int32, 1)
+        _need(table, "table", torch.int32, 2)
         _need(kc, "k cache", qkv.dtype, 4); _need(vc, "v cache", qkv.dtype, 4)
         if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
                 or not vc.is_contiguous() or kc.shape != vc.shape):
             raise KernelError("rope_kv_append: cache must be contiguous "
                               f"[blocks, {nkv}, {block_tokens}, {hd}], got {tuple(kc.shape)}")
+    if fault is None:
+        fault = fault_word(qkv.device)
+    flags = (1 if write_cache else 0) | (2 if rotate_k_in_place else 0)
     _check(lib().cretif_rope_kv_append(
         _p(qkv), ld, _dt(qkv), _p(cos), _p(sin), pairing, rot_dim, nh, nkv, hd, _p(tok_pos),
-        _p(tok_seq), _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc), block_tokens,
-        int(write_cache), T, _p(fault), _stream()), "rope_kv_append")
+        _p(tok_seq), _p(seq_slot), _p(table), table.stride(0) if table is not None else 0,
+        _p(kc), _p(vc), block_tokens, flags, T, _p(fault), _stream()), "rope_kv_append")
 
 
 def advance_decode(tok_ids, tok_pos, seq_start, sampled, B: int) -> None:
@@ -228,7 +246,9 @@ def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: i
 
 # ------------------------------------------------------------------ sampling
 def sample(logits, out, temperature: float, top_k: int, seed: int, request=None,
-           draw=None) -> None:
+           draw=None, seed_dev=None) -> None:
+    """``seed_dev`` (one int64 on the device), when given, is read by the kernel instead of
+    ``seed``: a captured launch then serves any seed."""
     _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
     rows, V = logits.shape
     if out.numel() < rows:
@@ -237,13 +257,15 @@ def sample(logits, out, temperature: float, top_k: int, seed: int, request=None,
         _need(request, "request", torch.int64, 1)
     if draw is not None:
         _need(draw, "draw", torch.int32, 1)
+    if seed_dev is not None:
+        _need(seed_dev, "seed_dev", torch.int64, 1)
     if temperature > 0 and 0 < top_k < V and top_k > lib().cretif_max_top_k():
         raise KernelError(f"sample: top_k {top_k} exceeds the kernel's limit "
                           f"{lib().cretif_max_top_k()}")
     _check(lib().cretif_sample(_p(logits), _rows(logits, "logits"), rows, V,
                                ctypes.c_float(temperature), int(top_k),
-                               ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(request),
-                               _p(draw), _p(out), _stream()), "sample")
+                               ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(seed_dev),
+                               _p(request), _p(draw), _p(out), _stream()), "sample")
 
 
 def uniform01(seed: int, request: int, draw: int) -> float:
@@ -284,6 +306,17 @@ def fault_word(device) -> torch.Tensor:
     if key not in _FAULT:
         _FAULT[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _FAULT[key]
+
+
+def wait_that_expires(limit: int = 2000, fault=None) -> None:
+    """Launch one CTA whose bounded wait runs out after ``limit`` polls: it sets the
+    "wait expired" bit of the status word and returns.  Harmless; for exercising the path
+    from an expired wait to the host's error."""
+    if fault is None:
+        fault = fault_word(torch.device("cuda", torch.cuda.current_device()))
+    _need(fault, "fault", torch.int32)
+    _check(lib().cretif_wait_that_expires(int(limit), _p(fault), None, _stream()),
+           "wait_that_expires")
 
 
 def gemm_tc_supported(x, w, out) -> bool:

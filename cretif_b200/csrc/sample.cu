@@ -74,8 +74,10 @@ __device__ __forceinline__ V block_exclusive_scan(V v, V* warp_tot, V* total) {
 
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, int top_k,
-              unsigned long long seed, const long long* __restrict__ request,
-              int* __restrict__ draw, int* __restrict__ out) {
+              unsigned long long seed, const unsigned long long* __restrict__ seed_dev,
+              const long long* __restrict__ request, int* __restrict__ draw,
+              int* __restrict__ out) {
+  if (seed_dev) seed = *seed_dev;      // the seed of a captured launch lives in device memory
   __shared__ float scratch[33];
   __shared__ float fscan[33];
   __shared__ int iscan[33];
@@ -252,13 +254,15 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
 using namespace cretif;
 
 extern "C" int cretif_sample(const float* logits, int ld, int rows, int V, float temperature,
-                             int top_k, unsigned long long seed, const long long* request,
+                             int top_k, unsigned long long seed,
+                             const unsigned long long* seed_dev, const long long* request,
                              int* draw, int* out, void* stream) {
   if (rows <= 0) return kOk;
   if (V <= 0 || ld < V) return kBadArgument;
   if (temperature > 0.f && top_k > kMaxTopK && top_k < V) return kBadArgument;
   sample_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, ld, V, temperature,
-                                                                  top_k, seed, request, draw, out);
+                                                                  top_k, seed, seed_dev, request,
+                                                                  draw, out);
   return launch_status();
 }
 

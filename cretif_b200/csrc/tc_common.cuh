@@ -38,10 +38,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Wait for the phase with the given parity; false when it gave up (and raised *abort).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+// Wait for the phase with the given parity; false when it gave up after `limit` polls (and
+// raised *abort).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          unsigned limit = kSpinLimit) {
   const uint32_t addr = smem_u32(bar);
-  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+  for (unsigned spin = 0; spin < limit; ++spin) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -1,14 +1,23 @@
 """The engine: a loaded model, its cache, and the one step function.
 
-``Engine.step`` takes a batch of sequences that either all begin (whole prompts of
-unequal lengths, packed into one pass) or all continue by one token, runs exactly the
-tokens it is given against what earlier steps left in the cache, and returns the
-logits at the places that were asked for.  Nothing is padded: tokens of all
-sequences are packed one sequence after another, so padding cannot change a result.
+``Engine.step`` takes a batch of sequences, each with its next tokens — a whole
+prompt, a further chunk of one, or a single decoded token, in any mixture — runs
+exactly the tokens it is given against what earlier steps left in the cache, and
+returns the logits at the places that were asked for.  Nothing is padded: tokens of
+all sequences are packed one sequence after another, so padding cannot change a
+result.  A step in which every sequence brings one token takes the decode kernels;
+any other step takes the kernels for ragged prompts, which start each sequence at the
+position its cache has reached.
 
 The reference's step is ``TransformerModel::forward(token_ids)`` for one sequence
-with an implicit position (src/model.cu:831-1040); its checks (empty input, overflow
-of the context, :832-849) are made here on the host before anything is launched.
+with an implicit position: any number of tokens at any cached position, the causal
+mask offset by what is cached (src/model.cu:831-1040, src/attention.cu:60-77, 695);
+its checks (empty input, overflow of the context, src/model.cu:832-849) are made here
+on the host before anything is launched.
+
+There is one way through a step — :meth:`Engine.context` builds what the parts read,
+:meth:`Engine.run` brackets the launch with the cache's bookkeeping — and both
+``Engine.step`` and the generation loop's decode graph go that way.
 """
 from __future__ import annotations
 
@@ -35,7 +44,33 @@ _FAULTS = {1: "a token id outside the vocabulary reached the embedding kernel",
 
 
 class StepError(RuntimeError):
-    """A step that cannot be run as asked (bad tokens, unknown slot, mixed batch)."""
+    """A step that cannot be run as asked (bad tokens, unknown slot), or whose kernels
+    reported a fault."""
+
+
+class _PinnedRing:
+    """Page-locked staging buffers for the small host-to-device copies of a step, reused in
+    turn; a buffer is taken again only after the copy that last read it has finished."""
+
+    def __init__(self, n: int = 8):
+        self.bufs = [None] * n
+        self.events = [None] * n
+        self.at = 0
+
+    def copy_to(self, dst: torch.Tensor, src: np.ndarray) -> None:
+        i = self.at
+        self.at = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < src.size:
+            buf = self.bufs[i] = torch.empty(max(1024, 2 * src.size), dtype=torch.int32
+                                             ).pin_memory()
+        buf[:src.size].numpy()[:] = src
+        dst[:src.size].copy_(buf[:src.size], non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
 
 
 def parse_dtype(dtype) -> torch.dtype:
@@ -87,8 +122,6 @@ class Engine:
                                    self.device, block_tokens=block_tokens, max_slots=max_slots,
                                    max_len=longest)
         self.model.prepare(self.cache.max_len)
-        from .step_kernel import StepKernel
-        self.model.step_kernel = StepKernel(self.model, self.cache)
         self.fault = ops.fault_word(self.device)
         self.vocab_size = self.spec.vocab_size
         # Steps whose shape (tokens per sequence, wanted places) repeats are captured as CUDA
@@ -97,12 +130,14 @@ class Engine:
         # that is refreshed before each replay, so a captured step serves any sequences.
         self.step_graphs = step_graphs and self.model.graph_safe
         self.graph_max_tokens = 8192
+        self.graph_max_logit_bytes = 128 << 20       # a captured step pins its logits
         self.max_step_graphs = 16
         self._graphs = collections.OrderedDict()
         self._seen: Dict[tuple, int] = {}
         self._last_meta_len = 0
         self._graph_stream = torch.cuda.Stream(device=self.device)
         self._graph_pool = torch.cuda.graph_pool_handle()
+        self._staging = _PinnedRing()
 
     # -- slots -------------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -112,6 +147,35 @@ class Engine:
         self.cache.free_slot(slot)
 
     # -- the step ------------------------------------------------------------------
+    def context_bucket(self, context: int) -> int:
+        """The context length a decode step is planned for: the next power of two (from 512)
+        at or above the longest live context, capped by the longest sequence allowed.  The
+        split of the keys among CTAs depends on it, so steps of one bucket can share a
+        captured graph and a step is planned the same way whether it is captured or not."""
+        b = 512
+        while b < context:
+            b *= 2
+        return min(b, self.cache.max_len)
+
+    def context(self, *, T, B, tok_ids, tok_pos, tok_seq, seq_slot, seq_start, cu_seqlens,
+                is_decode, max_new, max_context, slots=(), starts=(), news=()) -> StepContext:
+        """The one place a StepContext is made (index tensors on the device, int32)."""
+        if is_decode:
+            max_context = self.context_bucket(max_context)
+        return StepContext(
+            T=T, B=B, tok_ids=tok_ids, tok_pos=tok_pos, tok_seq=tok_seq, seq_slot=seq_slot,
+            seq_start=seq_start, cu_seqlens=cu_seqlens, is_decode=is_decode, max_new=max_new,
+            max_context=max_context, fault=self.fault, dtype=self.dtype, device=self.device,
+            seq_slot_host=tuple(slots), seq_start_host=tuple(starts), seq_new_host=tuple(news))
+
+    def run(self, pairs, launch):
+        """The one way a step runs: the cache makes room for ``pairs`` (slot, new tokens),
+        ``launch()`` puts the step's kernels on the stream, the cache counts the tokens."""
+        self.cache.begin_step(pairs)
+        out = launch()
+        self.cache.end_step(pairs)
+        return out
+
     def make_context(self, entries: Sequence[Entry], want, meta: Optional[torch.Tensor] = None
                      ) -> Tuple[StepContext, torch.Tensor, int]:
         """Validate a step on the host and put its index arrays on the device (into ``meta``
@@ -124,10 +188,6 @@ class Engine:
         if (new == 0).any():
             raise StepError("every sequence of a step must bring at least one token")
         starts = np.array([self.cache.length(s) for s in slots], dtype=np.int64)
-        all_begin, all_one = bool((starts == 0).all()), bool((new == 1).all())
-        if not (all_begin or all_one):
-            raise StepError("the sequences of a step must either all start at their first "
-                            "token or all go on by one token")
         ids = np.concatenate(toks)
         if ids.min() < 0 or ids.max() >= self.vocab_size:
             bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
@@ -137,9 +197,9 @@ class Engine:
         np.cumsum(new, out=cu[1:])
         tok_seq = np.repeat(np.arange(B), new)
         tok_pos = np.arange(T) - cu[tok_seq] + starts[tok_seq]
-        if want == "last":
+        if isinstance(want, str) and want == "last":
             rows = cu[1:] - 1
-        elif want == "all":
+        elif isinstance(want, str) and want == "all":
             rows = np.arange(T)
         else:
             if len(want) != B:
@@ -155,11 +215,9 @@ class Engine:
         packed = np.concatenate([ids, tok_pos, tok_seq, np.asarray(slots), starts, cu, rows]
                                 ).astype(np.int32)
         self._last_meta_len = int(packed.size)
-        pinned = torch.from_numpy(packed).pin_memory()
         if meta is None:
-            meta = pinned.to(self.device, non_blocking=True)
-        else:                                   # the fixed buffer of a captured step
-            meta.copy_(pinned, non_blocking=True)
+            meta = torch.empty(packed.size, dtype=torch.int32, device=self.device)
+        self._staging.copy_to(meta, packed)
         o = 0
 
         def take(n):
@@ -167,12 +225,11 @@ class Engine:
             out = meta[o:o + n]
             o += n
             return out
-        ctx = StepContext(
+        ctx = self.context(
             T=T, B=B, tok_ids=take(T), tok_pos=take(T), tok_seq=take(T), seq_slot=take(B),
-            seq_start=take(B), cu_seqlens=take(B + 1), is_decode=all_one,
-            max_new=int(new.max()), max_context=int((starts + new).max()), fault=self.fault,
-            dtype=self.dtype, device=self.device, seq_slot_host=tuple(slots),
-            seq_start_host=tuple(int(s) for s in starts), seq_new_host=tuple(int(n) for n in new))
+            seq_start=take(B), cu_seqlens=take(B + 1), is_decode=bool((new == 1).all()),
+            max_new=int(new.max()), max_context=int((starts + new).max()), slots=slots,
+            starts=(int(s) for s in starts), news=(int(n) for n in new))
         want_rows = take(rows.size)
         return ctx, want_rows, int(rows.size)
 
@@ -186,19 +243,20 @@ class Engine:
         if captured is not None:
             # the same step shape has been captured: refresh its indices, replay its kernels
             ctx, want_rows, n_want = self.make_context(entries, want, meta=captured["meta"])
-            pairs = [(s, n) for s, n in zip(ctx.seq_slot_host, ctx.seq_new_host)]
-            self.cache.begin_step(pairs)
-            captured["graph"].replay()
-            logits = captured["logits"].clone()
+
+            def launch():
+                captured["graph"].replay()
+                return captured["logits"].clone()
             self._graphs.move_to_end(key)
         else:
             ctx, want_rows, n_want = self.make_context(entries, want)
-            pairs = [(s, n) for s, n in zip(ctx.seq_slot_host, ctx.seq_new_host)]
-            self.cache.begin_step(pairs)
-            logits = self.model.forward(ctx, self.cache, None if all_rows else want_rows)
-            if key is not None:
-                self._maybe_capture(key, entries, want, all_rows, ctx.T)
-        self.cache.end_step(pairs)
+
+            def launch():
+                return self.model.forward(ctx, self.cache, None if all_rows else want_rows)
+        pairs = list(zip(ctx.seq_slot_host, ctx.seq_new_host))
+        logits = self.run(pairs, launch)
+        if captured is None and key is not None:
+            self._maybe_capture(key, entries, want, all_rows, ctx, n_want)
         if check:
             self.check_fault()
         return logits
@@ -206,25 +264,38 @@ class Engine:
     # -- captured steps --------------------------------------------------------------
     def _shape_key(self, entries, want):
         """What a captured step depends on beyond the indices it reads from the device: how
-        many tokens each sequence brings and where logits are wanted."""
+        many tokens each sequence brings, where logits are wanted, and for a decode step the
+        context length it is planned for."""
         news = tuple(len(t) for _, t in entries)
         if sum(news) > self.graph_max_tokens:
             return None
         w = want if isinstance(want, str) else tuple(tuple(int(i) for i in x) for x in want)
-        return (news, w)
+        bucket = 0
+        if all(n == 1 for n in news):
+            longest = max((int(self.cache.lengths[int(s)]) for s, _ in entries), default=0) + 1
+            bucket = self.context_bucket(longest)
+        return (news, w, bucket)
 
-    def _maybe_capture(self, key, entries, want, all_rows, T) -> None:
-        """A step shape seen for the second time is captured as a CUDA graph (the step that
-        was just run left the cache in the state the capture's warm run expects: the capture
-        itself launches nothing)."""
+    def _maybe_capture(self, key, entries, want, all_rows, ran: StepContext, n_want) -> None:
+        """A step shape seen for the second time is captured as a CUDA graph.  The step that
+        was just run left the cache as the capture expects it (the capture launches nothing),
+        so the capture's context is the finished step's, rebuilt on a buffer of its own."""
+        if n_want * self.vocab_size * 4 > self.graph_max_logit_bytes:
+            return
         self._seen[key] = self._seen.get(key, 0) + 1
         if self._seen[key] < 2:
             return
         if len(self._seen) > 4096:
             self._seen.clear()
-        n_meta = self._last_meta_len
-        meta = torch.zeros(n_meta, dtype=torch.int32, device=self.device)
-        ctx, want_rows, _ = self.make_context(entries, want, meta=meta)
+        meta = torch.zeros(self._last_meta_len, dtype=torch.int32, device=self.device)
+        saved = {s: int(self.cache.lengths[s]) for s in ran.seq_slot_host}
+        for s, n in zip(ran.seq_slot_host, ran.seq_new_host):
+            self.cache.lengths[s] -= n              # as they were when the step began
+        try:
+            ctx, want_rows, _ = self.make_context(entries, want, meta=meta)
+        finally:
+            for s, n in saved.items():
+                self.cache.lengths[s] = n
         graph = torch.cuda.CUDAGraph()
         cur = torch.cuda.current_stream()
         self._graph_stream.wait_stream(cur)
@@ -241,9 +312,6 @@ class Engine:
         word = int(self.fault.item())
         if word:
             self.fault.zero_()
-            sk = getattr(self.model, "step_kernel", None)
-            if sk is not None and sk.ok:
-                sk.barrier.zero_()         # a step that gave up may have left it half counted
             what = [msg for bit, msg in _FAULTS.items() if word & bit]
             raise StepError("device fault: " + "; ".join(what or [f"status {word}"]))
 

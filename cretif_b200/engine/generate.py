@@ -15,12 +15,14 @@ sequence here ends with reason ``"length"`` when its cache is full.
 """
 from __future__ import annotations
 
+import collections
 from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Sequence
 
 import numpy as np
 import torch
 
+from ..csrc import ops
 from ..sampling import Sampler, SamplingParams
 
 
@@ -29,6 +31,9 @@ class GenerationResult:
     prompt_len: int
     tokens: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None        # "stop" or "length"
+
+
+MAX_BACKENDS = 4      # sets of decode graphs kept per engine (one per temperature / top_k)
 
 
 class GenerationLoop:
@@ -128,12 +133,14 @@ class GenerationLoop:
 class DecodeRunner:
     """One decode step of a fixed batch as a CUDA graph: embed the last tokens, run the
     layers, head, sample, then advance ids and positions on the device.  Between two
-    launches with the same batch nothing is copied to the device."""
+    launches with the same batch nothing is copied to the device.  The step's context comes
+    from ``Engine.context`` and its launch goes through ``Engine.run``, like every step; a
+    graph is kept per (batch size, context bucket)."""
 
     def __init__(self, engine, sampler: Sampler, use_graph: bool = True):
         use_graph = use_graph and engine.model.graph_safe
         self.engine, self.sampler, self.use_graph = engine, sampler, use_graph
-        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.bufs: Dict[int, dict] = {}
         self.stream = torch.cuda.Stream(device=engine.device)
         self.pool = torch.cuda.graph_pool_handle() if use_graph else None
@@ -148,7 +155,6 @@ class DecodeRunner:
                  "tok_seq": torch.arange(B, dtype=torch.int32, device=dev),
                  "cu": torch.arange(B + 1, dtype=torch.int32, device=dev),
                  "request": torch.zeros(B, dtype=torch.int64, device=dev),
-                 "host": torch.zeros(B, dtype=torch.int32).pin_memory(),
                  "logits": None}
             self.bufs[B] = b
         return self.bufs[B]
@@ -164,43 +170,42 @@ class DecodeRunner:
                            non_blocking=True)
         self.B = B
 
-    def _body(self, b: dict, B: int) -> None:
-        from ..parts.base import StepContext
+    def _body(self, b: dict, B: int, context: int) -> None:
         eng = self.engine
-        ctx = StepContext(T=B, B=B, tok_ids=b["tok_ids"], tok_pos=b["tok_pos"],
-                          tok_seq=b["tok_seq"], seq_slot=b["seq_slot"], seq_start=b["seq_start"],
-                          cu_seqlens=b["cu"], is_decode=True, max_new=1,
-                          max_context=eng.cache.max_len, fault=eng.fault, dtype=eng.dtype,
-                          device=eng.device)
+        ctx = eng.context(T=B, B=B, tok_ids=b["tok_ids"], tok_pos=b["tok_pos"],
+                          tok_seq=b["tok_seq"], seq_slot=b["seq_slot"],
+                          seq_start=b["seq_start"], cu_seqlens=b["cu"], is_decode=True,
+                          max_new=1, max_context=context)
         logits = eng.model.forward(ctx, eng.cache, None)
         b["logits"] = logits
         self.sampler(logits, b["sampled"], b["request"], b["draw"])
-        from ..csrc import ops
         ops.advance_decode(b["tok_ids"], b["tok_pos"], b["seq_start"], b["sampled"], B)
 
-    def run(self) -> torch.Tensor:
-        """Launch one step for the loaded batch; returns the device tensor of sampled ids."""
+    def run(self, context: int) -> torch.Tensor:
+        """Launch one step for the loaded batch, whose longest sequence will hold ``context``
+        tokens after it; returns the device tensor of sampled ids."""
         B = self.B
         b = self._buffers(B)
         if not self.use_graph:
-            self._body(b, B)
+            self._body(b, B, context)
             return b["sampled"]
-        if B not in self.graphs:
+        key = (B, self.engine.context_bucket(context))
+        if key not in self.graphs:
             # Warm up outside the capture (lazy initialisation, kernel loading), restoring
             # the state the warm-up advanced, then capture.
             saved = b["ints"].clone()
             cur = torch.cuda.current_stream()
             self.stream.wait_stream(cur)
             with torch.cuda.stream(self.stream):
-                self._body(b, B)
+                self._body(b, B, context)
                 b["ints"].copy_(saved)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, pool=self.pool, stream=self.stream):
-                    self._body(b, B)
+                    self._body(b, B, context)
             cur.wait_stream(self.stream)
             b["ints"].copy_(saved)
-            self.graphs[B] = g
-        self.graphs[B].replay()
+            self.graphs[key] = g
+        self.graphs[key].replay()
         return b["sampled"]
 
 
@@ -283,9 +288,8 @@ class EngineBackend:
                              np.asarray([self.n_sampled[i] for i in active]))
             self._loaded = key
         entries = [(int(s), 1) for s in slots]
-        cache.begin_step(entries)
-        sampled = self.runner.run()
-        cache.end_step(entries)
+        context = int(cache.lengths[slots].max()) + 1
+        sampled = self.engine.run(entries, lambda: self.runner.run(context))
         host = self._hosts[self._host_at][:len(active)]
         self._host_at = (self._host_at + 1) % len(self._hosts)
         host.copy_(sampled, non_blocking=True)
@@ -376,10 +380,16 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 100,
     """
     params = SamplingParams(float(temperature), int(top_k), int(seed))
     stops = engine.spec.stop_token_ids if stop_ids is None else list(stop_ids)
-    key = (params, use_graph)
-    backends = engine.__dict__.setdefault("_backends", {})
+    # A backend holds the decode graphs; what a graph bakes in is the temperature and top_k
+    # (launch constants), not the seed, which the sampling kernel reads from device memory.
+    key = (params.temperature, params.top_k, use_graph)
+    backends = engine.__dict__.setdefault("_backends", collections.OrderedDict())
     if key not in backends:
         backends[key] = EngineBackend(engine, params, use_graph)
+        while len(backends) > MAX_BACKENDS:
+            backends.popitem(last=False)
+    backends.move_to_end(key)
+    backends[key].sampler.set_seed(params.seed)
     loop = GenerationLoop(backends[key], stops, engine.cache.max_tokens, engine.cache.max_len,
                           engine.cache.block_tokens, max_batch)
     return loop.run(prompts, max_tokens)

@@ -14,18 +14,28 @@ from typing import Any, Callable, Dict, List, Optional, Set, Tuple
 
 import torch
 
-from ..config.spec import ModelSpec, PartSpec
+from ..config.spec import BranchSpec, ModelSpec, PartSpec
 from ..parts.base import LayerCache, Part, StepContext, build_part, lookup_part
 from ..weights.loader import WeightSpec
 
 
 @dataclass
+class Branch:
+    """One built residual branch of a layer: ``h += post_norm(part(norm(h)))``."""
+
+    role: str                      # "mixer" or "feed_forward"
+    part: Part
+    norm: Optional[Part] = None
+    post_norm: Optional[Part] = None
+
+    def parts(self) -> List[Part]:
+        return [p for p in (self.norm, self.part, self.post_norm) if p is not None]
+
+
+@dataclass
 class Layer:
     prefix: str
-    mixer_norm: Part
-    mixer: Part
-    feed_forward_norm: Part
-    feed_forward: Part
+    branches: List[Branch]
     run: Callable
 
 
@@ -33,14 +43,22 @@ def _with(spec: PartSpec, **extra) -> PartSpec:
     return PartSpec(spec.kind, {**spec.params, **extra})
 
 
+def _branch_specs(bs: BranchSpec):
+    """(category, PartSpec) of a branch's parts, in the order they are built and loaded."""
+    if bs.norm is not None:
+        yield "norm", bs.norm
+    yield bs.role, bs.part
+    if bs.post_norm is not None:
+        yield "norm", bs.post_norm
+
+
 def _part_specs(spec: ModelSpec):
     """Every (category, PartSpec, name prefix) of the model, in a fixed order."""
     yield "embedding", _with(spec.embedding, vocab_size=spec.vocab_size), ""
     for layer in spec.layers:
-        yield "norm", layer.mixer_norm, layer.prefix
-        yield "mixer", layer.mixer, layer.prefix
-        yield "norm", layer.feed_forward_norm, layer.prefix
-        yield "feed_forward", layer.feed_forward, layer.prefix
+        for bs in layer.branches:
+            for category, pspec in _branch_specs(bs):
+                yield category, pspec, layer.prefix
     yield "norm", spec.final_norm, ""
     yield "head", _with(spec.head, vocab_size=spec.vocab_size), ""
 
@@ -68,80 +86,93 @@ class Model:
             raise ValueError(f"the compute dtype must be float32 or bfloat16, got {dtype}")
         self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
         H = spec.hidden_size
-        self.embedding = build_part("embedding", _with(spec.embedding, vocab_size=spec.vocab_size),
-                                    H, dtype, device)
+        # every part is built in the order of _part_specs, which is also the order of loading
+        built = [build_part(category, pspec, H, dtype, device)
+                 for category, pspec, _ in _part_specs(spec)]
+        self._parts: List[Part] = built
+        it = iter(built)
+        self.embedding = next(it)
         self.layers: List[Layer] = []
         for ls in spec.layers:
-            self.layers.append(Layer(
-                prefix=ls.prefix,
-                mixer_norm=build_part("norm", ls.mixer_norm, H, dtype, device),
-                mixer=build_part("mixer", ls.mixer, H, dtype, device),
-                feed_forward_norm=build_part("norm", ls.feed_forward_norm, H, dtype, device),
-                feed_forward=build_part("feed_forward", ls.feed_forward, H, dtype, device),
-                run=lookup_part("arrangement", ls.arrangement)))
-        self.final_norm = build_part("norm", spec.final_norm, H, dtype, device)
-        self.head = build_part("head", _with(spec.head, vocab_size=spec.vocab_size), H, dtype,
-                               device)
+            branches = []
+            for bs in ls.branches:
+                norm = next(it) if bs.norm is not None else None
+                part = next(it)
+                post = next(it) if bs.post_norm is not None else None
+                branches.append(Branch(bs.role, part, norm, post))
+            self.layers.append(Layer(ls.prefix, branches,
+                                     lookup_part("arrangement", ls.arrangement)))
+        self.final_norm = next(it)
+        self.head = next(it)
+
+    def parts(self) -> List[Part]:
+        """Every part of the model: embedding, each layer's branches in order, final norm, head."""
+        return list(self._parts)
 
     @property
     def graph_safe(self) -> bool:
         """Whether every part allows its steps to be captured as CUDA graphs."""
-        parts = [self.embedding, self.final_norm, self.head]
-        for layer in self.layers:
-            parts += [layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward]
-        return all(getattr(p, "graph_safe", False) for p in parts)
+        return all(getattr(p, "graph_safe", False) for p in self._parts)
 
     # -- weights ---------------------------------------------------------------
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Hand each part its tensors (CPU, by full name) and let it place them."""
-        def give(part: Part, category: str, pspec: PartSpec, prefix: str):
+        for part, (category, pspec, prefix) in zip(self._parts, _part_specs(self.spec)):
             specs = lookup_part(category, pspec.kind).weight_specs(pspec.params,
                                                                    self.spec.hidden_size)
             part.load({key: tensors[prefix + name] for key, (name, _) in specs.items()})
-        s = self.spec
-        give(self.embedding, "embedding", _with(s.embedding, vocab_size=s.vocab_size), "")
-        for layer, ls in zip(self.layers, s.layers):
-            give(layer.mixer_norm, "norm", ls.mixer_norm, ls.prefix)
-            give(layer.mixer, "mixer", ls.mixer, ls.prefix)
-            give(layer.feed_forward_norm, "norm", ls.feed_forward_norm, ls.prefix)
-            give(layer.feed_forward, "feed_forward", ls.feed_forward, ls.prefix)
-        give(self.final_norm, "norm", s.final_norm, "")
-        give(self.head, "head", _with(s.head, vocab_size=s.vocab_size), "")
-        if s.head.params.get("tied"):
+        if self.spec.head.params.get("tied"):
             self.head.tie(self.embedding)
 
     def prepare(self, max_positions: int) -> None:
-        """Build what depends on the longest sequence (position tables)."""
-        for layer in self.layers:
-            if hasattr(layer.mixer, "prepare"):
-                layer.mixer.prepare(max_positions)
+        """Let every part build what depends on the longest sequence (position tables)."""
+        for part in self._parts:
+            if hasattr(part, "prepare"):
+                part.prepare(max_positions)
 
     # -- cache -------------------------------------------------------------------
-    def cache_requests(self) -> Dict[int, Any]:
-        """cache id (index of the owning schedule entry) → what its mixer keeps."""
+    def cache_requests(self) -> Dict[Tuple[int, int], Any]:
+        """cache id → what its part keeps between steps.  A cache id is (index of the owning
+        schedule entry, index of the branch in its layer); only entries that own their cache
+        (``ScheduleEntry.cache is None``) appear."""
         out = {}
         for i, entry in enumerate(self.spec.schedule):
             if entry.cache is None:
-                mixer = self.layers[entry.layer].mixer
-                out[i] = mixer.cache_request() if hasattr(mixer, "cache_request") else None
+                for k, br in enumerate(self.layers[entry.layer].branches):
+                    if hasattr(br.part, "cache_request"):
+                        out[(i, k)] = br.part.cache_request()
         return out
+
+    def layer_caches(self, i: int, cache) -> List[Optional[LayerCache]]:
+        """What each branch of schedule entry ``i`` is handed: its own cache, the cache of the
+        entry it borrows from (read-only), or None for a part that keeps nothing."""
+        entry = self.spec.schedule[i]
+        owner = i if entry.cache is None else entry.cache
+        views: List[Optional[LayerCache]] = []
+        for k, br in enumerate(self.layers[entry.layer].branches):
+            cid = (owner, k)
+            if entry.cache is not None and br.role == "mixer":
+                # the k-th mixer of this layer reads the k-th mixer's cache of the owner's layer
+                mine = [j for j, b in enumerate(self.layers[entry.layer].branches)
+                        if b.role == "mixer"]
+                theirs = [j for j, b in enumerate(
+                    self.layers[self.spec.schedule[owner].layer].branches) if b.role == "mixer"]
+                cid = (owner, theirs[mine.index(k)])
+            kv = cache.kv_view(cid) if cache.has_kv(cid) else None
+            state = cache.state_view(cid) if cache.has_state(cid) else None
+            views.append(None if kv is None and state is None
+                         else LayerCache(kv=kv, state=state, writes=entry.cache is None))
+        return views
 
     # -- one step ------------------------------------------------------------------
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Run the scheduled layers on the step's tokens; logits [rows, vocab] float32
         at ``want_rows`` (token indices), or at every token when it is None."""
-        sk = getattr(self, "step_kernel", None)
-        if sk is not None and sk.takes(ctx):
-            return sk.run(ctx, want_rows)            # the whole step in one launch
         h = self.embedding.forward(ctx.tok_ids, ctx)
         pending = None
         for i, entry in enumerate(self.spec.schedule):
-            cid = i if entry.cache is None else entry.cache
-            view = LayerCache(kv=cache.kv_view(cid) if cache.has_kv(cid) else None,
-                              state=cache.state_view(cid) if cache.has_state(cid) else None,
-                              writes=entry.cache is None)
             layer = self.layers[entry.layer]
-            pending = layer.run(layer, h, pending, ctx, view)
+            pending = layer.run(layer, h, pending, ctx, self.layer_caches(i, cache))
         if want_rows is not None and want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         if hasattr(self.head, "forward_from_residual"):
@@ -152,9 +183,4 @@ class Model:
         return self.head.forward(n, ctx)
 
     def weight_bytes(self) -> int:
-        total = self.embedding.weight_bytes() + self.final_norm.weight_bytes() \
-            + self.head.weight_bytes()
-        for layer in self.layers:
-            total += (layer.mixer_norm.weight_bytes() + layer.mixer.weight_bytes()
-                      + layer.feed_forward_norm.weight_bytes() + layer.feed_forward.weight_bytes())
-        return total
+        return sum(p.weight_bytes() for p in self._parts)

@@ -87,52 +87,62 @@ class Attention(Part):
         self.position.load({})
 
     def prepare(self, max_positions: int) -> None:
-        self.position.prepare(max_positions)
+        if hasattr(self.position, "prepare"):
+            self.position.prepare(max_positions)
 
     def cache_request(self):
         return KVRequest(self.nkv, self.hd, self.window)
 
     def forward(self, x, ctx, cache):
         from .linear import plain_forced, skinny_max_rows
-        from .position import Rotary
+        kv = cache.kv
+        rot = getattr(self.position, "rotary_table", None)
+        rot = rot() if rot is not None else None         # (cos, sin, pairing, rotary_dim)
         o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
         if (self.dtype == torch.bfloat16 and ctx.T > skinny_max_rows() and not plain_forced()
-                and not _force_plain and self.hd in (64, 128) and type(self.position) is Rotary
-                and self.position.rot_dim == self.hd and cache.kv is not None
-                and ops.gemm_tc_supported(x, self.w_qkv, o)):
+                and not _force_plain and self.hd in (64, 128) and rot is not None
+                and rot[3] == self.hd and ops.gemm_tc_supported(x, self.w_qkv, o)):
             # many tokens: rotary and the cache write ride in the product's epilogue
-            kv = cache.kv
-            cos, sin = self.position._table
             q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
-            ops.gemm_tc_qkv_rope(x, self.w_qkv, q, cos, sin, self.position.pairing, self.nh,
+            ops.gemm_tc_qkv_rope(x, self.w_qkv, q, rot[0], rot[1], rot[2], self.nh,
                                  self.nkv, self.hd, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                                  kv.table, kv.k, kv.v, kv.block_tokens, cache.writes)
             self.attend(q, o, ctx, kv)
         else:
             qkv = linear(x, self.w_qkv)                               # [T, q + 2 kv]
-            self.position.rotate_and_store(qkv, ctx, cache, self.nh, self.nkv, self.hd)
-            self.attend(qkv, o, ctx, cache.kv)
+            if rot is not None:          # a rotation by table: one kernel encodes and stores
+                ops.rope_kv_append(qkv, rot[0], rot[1], rot[2], rot[3], self.nh, self.nkv,
+                                   self.hd, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table,
+                                   kv.k, kv.v, kv.block_tokens, cache.writes, ctx.fault)
+            else:                        # any other encoding, then the store
+                self.position.encode(qkv, ctx, self.nh, self.nkv, self.hd)
+                if cache.writes:
+                    ops.rope_kv_append(qkv, None, None, 0, 0, self.nh, self.nkv, self.hd,
+                                       ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k,
+                                       kv.v, kv.block_tokens, True, ctx.fault)
+            self.attend(qkv, o, ctx, kv)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx, cache) -> bool:
         """Few tokens, bfloat16: norm + q|k|v + rotary + cache write in one kernel, attention,
         then the output projection added into ``h``.  False if the step does not qualify."""
-        from .norm import RMSNorm
-        from .position import Rotary
+        rms = getattr(norm, "rms_params", None)
+        rot = getattr(self.position, "rotary_table", None)
         if (_force_plain or not fused_steps_enabled() or self.dtype != torch.bfloat16
-                or ctx.T > FUSED_MAX_TOKENS or type(norm) is not RMSNorm
-                or type(self.position) is not Rotary or self.position.rot_dim != self.hd
+                or ctx.T > FUSED_MAX_TOKENS or rms is None or rot is None or cache is None
                 or cache.kv is None or cache.kv.block_tokens & (cache.kv.block_tokens - 1)
                 or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
                 or not ops.fused_supported(ctx.T, self.q_dim, self.w_o, norm=False)):
             return False
+        cos, sin, pairing, rot_dim = rot()
+        if rot_dim != self.hd:
+            return False
+        norm_w, eps = rms()
         kv = cache.kv
-        cos, sin = self.position._table
         q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=h.device)
-        ops.fused_qkv_rope(h, norm.weight, norm.eps, self.w_qkv, q, cos, sin,
-                           self.position.pairing, self.nh, self.nkv, self.hd, ctx.tok_pos,
-                           ctx.tok_seq, ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens,
-                           cache.writes, ctx.fault)
+        ops.fused_qkv_rope(h, norm_w, eps, self.w_qkv, q, cos, sin, pairing, self.nh, self.nkv,
+                           self.hd, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k, kv.v,
+                           kv.block_tokens, cache.writes, ctx.fault)
         o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=h.device)
         self.attend(q, o, ctx, kv)
         ops.fused_linear_add(o, self.w_o, h)

@@ -64,14 +64,15 @@ class LinearHead(Part):
         """Few wanted rows, bfloat16: final norm and head product in one kernel; None if the
         step does not qualify."""
         from .attention import FUSED_MAX_TOKENS, fused_steps_enabled
-        from .norm import RMSNorm
         R = h.shape[0] if rows is None else rows.numel()
+        rms = getattr(norm, "rms_params", None)
         if (pending is not None or not fused_steps_enabled() or self.dtype != torch.bfloat16
-                or R > FUSED_MAX_TOKENS or type(norm) is not RMSNorm
+                or R > FUSED_MAX_TOKENS or rms is None
                 or not ops.fused_supported(R, self.hidden_size, self.weight)):
             return None
         logits = torch.empty((R, self.weight.shape[0]), dtype=torch.float32, device=h.device)
-        ops.fused_norm_linear(h, norm.weight, norm.eps, self.weight, logits, rows=rows)
+        norm_w, eps = rms()
+        ops.fused_norm_linear(h, norm_w, eps, self.weight, logits, rows=rows)
         return logits
 
     def weight_bytes(self):

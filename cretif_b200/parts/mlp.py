@@ -65,15 +65,16 @@ class GatedMLP(Part):
         """Few tokens, bfloat16: norm + gate|up + SiLU·mul in one kernel, then the down
         projection added into ``h``.  False if the step does not qualify."""
         from .attention import FUSED_MAX_TOKENS, fused_steps_enabled
-        from .norm import RMSNorm
         T = h.shape[0]
+        rms = getattr(norm, "rms_params", None)
         if (not fused_steps_enabled() or self.dtype != torch.bfloat16 or T > FUSED_MAX_TOKENS
-                or type(norm) is not RMSNorm
+                or rms is None
                 or not ops.fused_supported(T, self.hidden_size, self.w_gate_up)
                 or not ops.fused_supported(T, self.inter, self.w_down, norm=False)):
             return False
         act = torch.empty((T, self.inter), dtype=self.dtype, device=h.device)
-        ops.fused_gate_up_silu(h, norm.weight, norm.eps, self.w_gate_up, act, self.gu_block)
+        norm_w, eps = rms()
+        ops.fused_gate_up_silu(h, norm_w, eps, self.w_gate_up, act, self.gu_block)
         ops.fused_linear_add(act, self.w_down, h)
         return True
 

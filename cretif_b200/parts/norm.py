@@ -28,6 +28,11 @@ class RMSNorm(Part):
         self.weight = self._vector32(tensors["weight"])
         self.eps = float(self.params["eps"])
 
+    def rms_params(self):
+        """(weight, eps): offered so that a kernel may apply this norm in its own prologue.  A
+        norm that offers it promises that its ``forward`` is exactly this RMSNorm."""
+        return self.weight, self.eps
+
     def forward(self, h, delta=None, rows=None, write_h=True):
         R = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((R, h.shape[1]), dtype=self.dtype, device=h.device)

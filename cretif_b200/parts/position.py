@@ -10,11 +10,15 @@ function).  Angles, cosines and sines are computed once on the host in 64-bit an
 kept as a 32-bit table ``[positions, rotary_dim/2]`` that every kernel reads, so a
 position's rotation is the same in every step shape.
 
-``none``: keys and values are stored as they are.
+``none``: queries and keys stay as they are.
 
-Interface: ``rotate_and_store(qkv, ctx, cache, nh, nkv, hd)`` rotates q in place in
-the packed ``[T, (nh + 2·nkv)·hd]`` buffer and writes rotated k, and v, into the
-block cache of ``cache.kv`` (unless the visit only borrows that cache).
+Interface of a position part: ``prepare(max_positions)`` builds what depends on the longest
+sequence; ``encode(qkv, ctx, nh, nkv, hd)`` position-encodes the queries and keys of the
+packed ``[T, (nh + 2·nkv)·hd]`` buffer in place.  Storing keys and values in the cache is the
+mixer's job, not the encoding's.  A part whose encoding is a rotation by a table may also
+offer ``rotary_table() -> (cos, sin, pairing, rotary_dim)``; a mixer can then hand the table
+to kernels that rotate inside a product's epilogue or together with the cache write.  A part
+that offers it promises that ``encode`` is exactly that rotation.
 """
 from __future__ import annotations
 
@@ -59,30 +63,24 @@ class Rotary(Part):
     def prepare(self, max_positions: int) -> None:
         self._table = rotary_table(self.theta, self.rot_dim, max_positions, self.device)
 
-    def rotate_and_store(self, qkv, ctx, cache, nh, nkv, hd):
+    def rotary_table(self):
         cos, sin = self._table
-        kv = cache.kv
+        return cos, sin, self.pairing, self.rot_dim
+
+    def encode(self, qkv, ctx, nh, nkv, hd):
+        cos, sin = self._table
         ops.rope_kv_append(qkv, cos, sin, self.pairing, self.rot_dim, nh, nkv, hd, ctx.tok_pos,
-                           ctx.tok_seq, ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens,
-                           cache.writes, ctx.fault)
+                           write_cache=False, fault=ctx.fault, rotate_k_in_place=True)
 
 
 @register_part("position", "none")
 class NoPosition(Part):
-    """Stores keys and values unrotated."""
+    """Leaves queries and keys as they are."""
 
     graph_safe = True
 
-    def load(self, tensors):
-        self._table = None
-
     def prepare(self, max_positions: int) -> None:
-        z = torch.zeros((1, 1), dtype=torch.float32, device=self.device)
-        self._table = (z, z)
+        pass
 
-    def rotate_and_store(self, qkv, ctx, cache, nh, nkv, hd):
-        cos, sin = self._table
-        kv = cache.kv
-        ops.rope_kv_append(qkv, cos, sin, 0, 0, nh, nkv, hd, ctx.tok_pos, ctx.tok_seq,
-                           ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens, cache.writes,
-                           ctx.fault)
+    def encode(self, qkv, ctx, nh, nkv, hd):
+        pass

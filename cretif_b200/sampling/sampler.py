@@ -48,11 +48,21 @@ def uniform01(seed: int, request: int, draw: int) -> float:
 
 
 class Sampler:
-    """Runs the sampling kernel: one token id per row of float32 logits."""
+    """Runs the sampling kernel: one token id per row of float32 logits.
+
+    The seed lives in device memory and the kernel reads it from there, so a captured
+    launch serves any seed: :meth:`set_seed` takes effect at the next launch or replay."""
 
     def __init__(self, params: SamplingParams, vocab_size: int):
         params.validate(vocab_size)
         self.params = params
+        self._seed = int(params.seed)
+        self._seed_dev: Optional[torch.Tensor] = None
+
+    def set_seed(self, seed: int) -> None:
+        self._seed = int(seed)
+        if self._seed_dev is not None:
+            self._seed_dev.fill_(_as_int64(self._seed))
 
     def __call__(self, logits: torch.Tensor, out: torch.Tensor,
                  request: Optional[torch.Tensor] = None,
@@ -60,5 +70,15 @@ class Sampler:
         """``request`` [rows] int64 and ``draw`` [rows] int32 (incremented by the kernel)
         key the random numbers; both may be None for greedy sampling."""
         p = self.params
-        ops.sample(logits, out, p.temperature, p.top_k, p.seed, request, draw)
+        if self._seed_dev is None or self._seed_dev.device != logits.device:
+            self._seed_dev = torch.full((1,), _as_int64(self._seed), dtype=torch.int64,
+                                        device=logits.device)
+        ops.sample(logits, out, p.temperature, p.top_k, self._seed, request, draw,
+                   seed_dev=self._seed_dev)
         return out
+
+
+def _as_int64(seed: int) -> int:
+    """The 64 bits of ``seed`` as a signed value (what an int64 tensor holds)."""
+    seed &= 0xFFFFFFFFFFFFFFFF
+    return seed - (1 << 64) if seed >= (1 << 63) else seed

@@ -102,14 +102,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     nkv = k.shape[1]
     g = nh // nkv
     out = torch.zeros(S, nh, hd, dtype=q.dtype)
+    p = start + torch.arange(S)[:, None]                  # each query's position
+    u = torch.arange(k.shape[0])[None, :]                 # each key's position
+    hidden = u > p                                        # the causal mask
+    if window > 0:
+        hidden = hidden | (u <= p - window)
     for h in range(nh):
         kvh = h // g
         scores = (q[:, h, :] @ k[:, kvh, :].T) * scale            # [S, start+S]
-        for t in range(S):
-            p = start + t
-            scores[t, p + 1:] = -math.inf
-            if window > 0:
-                scores[t, : max(0, p - window + 1)] = -math.inf
+        scores = scores.masked_fill(hidden, -math.inf)
         m = scores.max(dim=-1, keepdim=True).values
         e = torch.exp(scores - m)
         probs = e / e.sum(dim=-1, keepdim=True)
@@ -157,6 +158,26 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int],
         rope = "interleaved" if cfg.get("rope_interleaved") else "half"
     rot = rope_interleaved if rope == "interleaved" else rope_half
     S = len(ids)
+    pos = torch.arange(S, dtype=torch.float64)[:, None]
+
+    def rot_all(x):        # every token's heads rotated by its own position's angles
+        if S <= 64:
+            return torch.stack([rot(x[t], t, theta) for t in range(S)])
+        j = torch.arange(hd // 2, dtype=torch.float64)
+        a = (pos / torch.pow(torch.tensor(theta, dtype=torch.float64), 2.0 * j / hd)).to(dtype)
+        cos, sin = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]      # [S, 1, hd/2]
+        if rope == "interleaved":
+            x0, x1 = x[..., 0::2], x[..., 1::2]
+            return torch.stack([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1).flatten(-2)
+        x0, x1 = x[..., : hd // 2], x[..., hd // 2:]
+        return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
+
+    def window_of(i):      # keys a query of layer i sees (0: all), see config/llama.py
+        w = cfg.get("sliding_window")
+        kinds = cfg.get("layer_types")
+        if w is None or (kinds is not None and kinds[i] != "sliding_attention"):
+            return 0
+        return int(w)
     h = embed(W["model.embed_tokens.weight"], ids)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
@@ -164,9 +185,9 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int],
         q = st(n @ W[p + "self_attn.q_proj.weight"].T).reshape(S, nh, hd)  # src/attention.cu:567-576
         k = st(n @ W[p + "self_attn.k_proj.weight"].T).reshape(S, nkv, hd)
         v = st(n @ W[p + "self_attn.v_proj.weight"].T).reshape(S, nkv, hd)
-        q = st(torch.stack([rot(q[t], t, theta) for t in range(S)]))     # src/attention.cu:589-597
-        k = st(torch.stack([rot(k[t], t, theta) for t in range(S)]))
-        o = st(attention(q, k, v, 1.0 / math.sqrt(hd)))
+        q = st(rot_all(q))                                               # src/attention.cu:589-597
+        k = st(rot_all(k))
+        o = st(attention(q, k, v, 1.0 / math.sqrt(hd), window=window_of(i)))
         h = h + o.reshape(S, nh * hd) @ W[p + "self_attn.o_proj.weight"].T  # src/attention.cu:720-728
         n = st(rmsnorm(h, W[p + "post_attention_layernorm.weight"], eps))
         if storage is None:

@@ -61,6 +61,51 @@ def run_batch(engine, requests, prompt_lens):
                 engine.free_slot(s)
 
 
+def run_chunks(engine, toks, chunks):
+    """One request alone, fed as chunks of the given sizes (the rest as a last chunk)."""
+    slot = engine.alloc_slot()
+    try:
+        rows, at = [], 0
+        sizes = list(chunks)
+        while at < len(toks):
+            n = sizes.pop(0) if sizes else len(toks) - at
+            n = min(n, len(toks) - at)
+            rows.append(engine.step([(slot, toks[at:at + n])], "all").cpu().numpy())
+            at += n
+        return np.concatenate(rows, axis=0)
+    finally:
+        engine.free_slot(slot)
+
+
+def run_schedule(engine, requests, schedule):
+    """Any mixture: ``schedule`` is a list of steps, each a list of (request index, number of
+    tokens); a request starts at its first appearance, is fed in the chunks given and its
+    slot is given back when its tokens are used up.  Returns the logits of every place."""
+    slots = {}
+    fed = [0] * len(requests)
+    out = [np.zeros((len(t), engine.vocab_size), dtype=np.float32) for t in requests]
+    try:
+        for step in schedule:
+            entries = []
+            for r, n in step:
+                if r not in slots:
+                    slots[r] = engine.alloc_slot()
+                entries.append((slots[r], requests[r][fed[r]:fed[r] + n]))
+            logits = engine.step(entries, "all").cpu().numpy()
+            o = 0
+            for r, n in step:
+                out[r][fed[r]:fed[r] + n] = logits[o:o + n]
+                o += n
+                fed[r] += n
+                if fed[r] >= len(requests[r]):
+                    engine.free_slot(slots.pop(r))
+        assert all(f == len(t) for f, t in zip(fed, requests)), "the schedule leaves tokens unfed"
+        return out
+    finally:
+        for s in slots.values():
+            engine.free_slot(s)
+
+
 def rel_err(got, want):
     """max |difference| over max |plain logit|."""
     want = np.asarray(want, dtype=np.float64)

@@ -74,8 +74,11 @@ def test_missing_keys_and_unknown_architecture(tmp_path):
 def test_spec_is_data_and_validated():
     spec = build_llama_spec(llama_config_from_dict(tiny.TINY_A))
     assert len(spec.layers) == 2 and [e.layer for e in spec.schedule] == [0, 1]
-    assert spec.layers[0].mixer.kind == "attention"
-    assert spec.layers[0].mixer.params["position"]["pairing"] == "half"
+    mixer, ffn = spec.layers[0].branches
+    assert (mixer.role, mixer.part.kind, mixer.norm.kind) == ("mixer", "attention", "rmsnorm")
+    assert (ffn.role, ffn.part.kind, ffn.post_norm) == ("feed_forward", "gated_mlp", None)
+    assert mixer.part.params["position"]["pairing"] == "half"
+    assert mixer.part.params["window"] == 0
     assert spec.head.params["tied"] is True
     # a schedule may visit a layer twice or borrow an earlier visit's cache
     spec.schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache=1)]

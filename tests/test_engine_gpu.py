@@ -5,7 +5,8 @@ import torch
 
 import plain_llama
 import tiny
-from replay_cuts import rel_err, run_batch, run_tail_by_one, run_whole
+from replay_cuts import (rel_err, run_batch, run_chunks, run_schedule, run_tail_by_one,
+                         run_whole)
 
 pytestmark = pytest.mark.gpu
 
@@ -13,7 +14,8 @@ pytestmark = pytest.mark.gpu
 # activations and cached keys/values are rounded to 8 bits of mantissa (2^-9 relative
 # each) several times a layer; sums and the residual stream stay in 32-bit.
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
-LENGTHS = {"A": [5, 9, 13, 70, 100], "B": [1, 17, 40, 130, 200], "C": [3, 33, 64, 65, 300]}
+LENGTHS = {"A": [5, 9, 13, 70, 100], "B": [1, 17, 40, 130, 200], "C": [3, 33, 64, 65, 300],
+           "W": [7, 24, 25, 90, 210]}
 
 
 @pytest.fixture(scope="module")
@@ -129,24 +131,93 @@ def test_a_repeated_step_shape_is_replayed_as_a_graph(model_dirs, plain_logits, 
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-def test_the_whole_step_kernel_equals_the_kernels_of_the_parts(engines, plain_logits, name):
-    """Decode steps of few sequences can run as one persistent launch (switched on here); by
-    default they run through the parts' kernels.  Both are compared with the plain model and
-    with each other."""
-    from cretif_b200.engine import step_kernel
-    eng = engines(name, "bfloat16")
-    assert eng.model.step_kernel.ok, eng.model.step_kernel.reason
-    reqs = [tiny.tokens(name, n + 20, 60 + i) for i, n in enumerate(LENGTHS[name][:4])]
-    prompts = [len(r) - 20 for r in reqs]
-    without = run_batch(eng, reqs, prompts)
-    step_kernel.enable(True)
-    try:
-        with_kernel = run_batch(eng, reqs, prompts)
-    finally:
-        step_kernel.enable(False)
-    for r, a, b in zip(reqs, with_kernel, without):
-        want = plain_logits(name, r)
-        assert rel_err(a, want) <= TOL["bfloat16"] and rel_err(b, want) <= TOL["bfloat16"]
-        assert rel_err(a, b) <= TOL["bfloat16"]
+def test_a_prompt_fed_in_chunks(engines, plain_logits, name, dtype):
+    """A fourth cutting: several tokens at a cached position (the reference's forward takes
+    any number of tokens at any position, src/attention.cu:60-77; its test is
+    tests/test_attention.cu:307-336).  Alone, and inside a batch in which other sequences
+    start fresh or go on by one token in the same step."""
+    eng = engines(name, dtype)
+    n = LENGTHS[name][3] + 18
+    toks = tiny.tokens(name, n, 31)
+    want = plain_logits(name, toks)
+    assert rel_err(run_chunks(eng, toks, [40, 30, 1, 17]), want) <= TOL[dtype]
+    assert rel_err(run_chunks(eng, toks, [1, 64, 2]), want) <= TOL[dtype]
+    reqs = [toks, tiny.tokens(name, 50 + 17 + 3, 32), tiny.tokens(name, 9 + 4, 33),
+            tiny.tokens(name, 66, 34)]
+    rest = n - 40 - 30 - 1 - 17
+    schedule = [[(0, 40)],
+                [(0, 30), (1, 50)],                   # a chunk beside a fresh prompt
+                [(0, 1), (1, 17), (2, 9)],            # one token, a chunk, a fresh prompt
+                [(0, 17), (1, 1), (2, 1)],
+                [(0, rest), (1, 1), (2, 1), (3, 66)],
+                [(1, 1), (2, 1)],
+                [(2, 1)]]
+    for _ in range(2):                                # again: slots and blocks used again
+        outs = run_schedule(eng, reqs, schedule)
+        for r, got in zip(reqs, outs):
+            assert rel_err(got, plain_logits(name, r)) <= TOL[dtype], len(r)
     eng.cache.check()
+    assert eng.cache.stats()["slots_live"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_sliding_window_from_config_json(engines, plain_logits, model_dirs, dtype):
+    """`sliding_window` and `layer_types` in config.json: two of four layers see the last 24
+    keys only.  Their cache group gives blocks back behind the window, the other keeps all.
+    Small random weights give nearly uniform attention, so a key that is wrongly seen or
+    wrongly hidden moves the logits little; the sharpened variant below makes it show."""
+    eng = engines("W", dtype, max_tokens=1024)
+    groups = eng.cache.stats()["groups"]
+    assert sorted((g["window"], g["layers"]) for g in groups) == [(0, 2), (24, 2)]
+    for n in LENGTHS["W"]:
+        toks = tiny.tokens("W", n, 3)
+        want = plain_logits("W", toks)
+        assert rel_err(run_whole(eng, toks), want) <= TOL[dtype], n
+        assert rel_err(run_tail_by_one(eng, toks, tail=32), want) <= TOL[dtype], n
+    toks = tiny.tokens("W", 150, 4)
+    assert rel_err(run_chunks(eng, toks, [30, 70, 1, 20]), plain_logits("W", toks)) <= TOL[dtype]
+    reqs = [tiny.tokens("W", n + 10, 50 + n) for n in LENGTHS["W"][:4]]
+    for _ in range(2):
+        outs = run_batch(eng, reqs, LENGTHS["W"][:4])
+        for r, got in zip(reqs, outs):
+            assert rel_err(got, plain_logits("W", r)) <= TOL[dtype], len(r)
+    eng.cache.check()
+    # while a long sequence decodes, the window group holds two blocks, the other all four
+    slot = eng.alloc_slot()
+    eng.step([(slot, tiny.tokens("W", 200, 9))])
+    free = dict(zip([g["window"] for g in groups], eng.cache.stats()["blocks_free"]))
+    assert free[0] == eng.cache.n_blocks - 4 and free[24] == eng.cache.n_blocks - 1
+    eng.free_slot(slot)
+    eng.cache.check()
+
+
+def test_a_sliding_window_with_sharp_attention(model_dirs, tmp_path):
+    """Queries and keys scaled up so that every query reads a few particular keys: one key
+    too many or too few at the window's edge changes the logits by far more than rounding."""
+    import plain_llama as pl
+    from cretif_b200.engine import Engine
+    from cretif_b200.weights import write_model_folder
+    cfg, w = pl.read_model_folder(model_dirs["W"])
+    tensors = {k: v.to(torch.float32) for k, v in w.items()}
+    for i in range(cfg["num_hidden_layers"]):
+        for name in ("q_proj", "k_proj"):
+            tensors[f"model.layers.{i}.self_attn.{name}.weight"] *= 25.0
+    d = str(tmp_path / "sharp_w")
+    write_model_folder(d, cfg, tensors)
+    cfg, w = pl.read_model_folder(d)
+    toks = tiny.tokens("W", 140, 77)
+    want = pl.forward(cfg, w, toks).numpy()
+    wider = pl.forward(dict(cfg, sliding_window=25), w, toks).numpy()
+    assert rel_err(wider, want) > 1e-2                 # the edge matters with these weights
+    eng = Engine(d, dtype="float32", max_tokens=512)
+    assert rel_err(run_whole(eng, toks), want) <= 1e-4
+    assert rel_err(run_tail_by_one(eng, toks, tail=40), want) <= 1e-4
+    assert rel_err(run_chunks(eng, toks, [23, 24, 25, 1, 40]), want) <= 1e-4
+    eng16 = Engine(d, dtype="bfloat16", max_tokens=512)
+    want16 = pl.forward(cfg, w, toks, storage=torch.bfloat16).numpy()
+    for got in (run_whole(eng16, toks), run_tail_by_one(eng16, toks, tail=40),
+                run_chunks(eng16, toks, [23, 24, 25, 1, 40])):
+        assert rel_err(got, want16) <= 3e-2            # against the plain model rounded alike
+        assert rel_err(got, wider) > 3 * rel_err(got, want16)

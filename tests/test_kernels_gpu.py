@@ -592,6 +592,71 @@ def test_attn_decode_finds_a_far_key(ops, cluster):
         close(out[0, h * hd:(h + 1) * hd], cache.v[blk, h // 2, target % 64, :], 2e-2)
 
 
+@pytest.mark.parametrize("kernel", ["simt", "decode_split", "decode_cluster", "decode_cuda_cores",
+                                    "prefill"])
+@pytest.mark.parametrize("first_key", [128, 191])       # a block's first and last position
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_the_edge_of_a_window_with_dominant_keys(ops, kernel, first_key, splits):
+    """A query at position 299 with a window that begins at ``first_key``.  The key just
+    before the window is made to dominate everything (it must not be seen), the window's
+    first key to dominate the rest (it must be): the output is that key's value, and one key
+    too many or too few changes it completely.  Random keys alone give diffuse weights under
+    which one key at the edge hides inside the tolerance.  With 16 ranges most of them are
+    empty, and the leading cache blocks lie wholly outside the window."""
+    if kernel in ("simt", "prefill") and splits != 1:
+        pytest.skip("no ranges to split")
+    nh, nkv, hd, n = 4, 2, 64, 300
+    pos = n - 1
+    window = pos - first_key + 1
+    cache = ToyCache([n], nkv, hd, torch.bfloat16, seed=21)
+    fault = torch.zeros(1, dtype=torch.int32, device=DEV)
+    seq_slot = cache.seq_slot
+    if kernel == "prefill":           # the last 200 tokens of the sequence as one chunk
+        new = 200
+        qkv = rnd(new, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=22)
+        q_last = qkv[new - 1, :nh * hd]
+    else:
+        q = rnd(1, nh * hd, dtype=torch.bfloat16, seed=22)
+        q_last = q[0]
+    for key_pos, gain in ((first_key - 1, 40.0), (first_key, 30.0)):
+        blk = cache.table_host[cache.slots[0], key_pos // 64]
+        for kvh in range(nkv):
+            own = q_last[kvh * 2 * hd:kvh * 2 * hd + hd].float()     # the group's first head
+            cache.k[blk, kvh, key_pos % 64, :] = (own * gain).to(torch.bfloat16)
+    if kernel == "prefill":
+        out = torch.zeros(new, nh * hd, device=DEV, dtype=torch.bfloat16)
+        cu = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+        start = torch.tensor([n - new], dtype=torch.int32, device=DEV)
+        ops.attn_prefill(qkv, out, cache.k, cache.v, cache.table, cu, start, seq_slot, nh, nkv,
+                         hd, 1.0, window, 64, 1, new, fault)
+        got = out[new - 1]
+    else:
+        out = torch.empty(1, nh * hd, device=DEV, dtype=torch.bfloat16)
+        tpos = torch.tensor([pos], dtype=torch.int32, device=DEV)
+        seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+        if kernel == "simt":
+            ops.attn_simt(q, out, cache.k, cache.v, cache.table, tpos, seq, seq_slot, nh, nkv,
+                          hd, 1.0, window, 64)
+        else:
+            ops.decode_attention_simt_only(kernel == "decode_cuda_cores")
+            try:
+                ops.attn_decode(q, out, cache.k, cache.v, cache.table, tpos, seq, seq_slot, nh,
+                                nkv, hd, 1.0, window, 64, splits, fault,
+                                kernel == "decode_cluster" and splits <= ops.CLUSTER_MAX_RANGES)
+            finally:
+                ops.decode_attention_simt_only(False)
+        got = out[0]
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    blk = cache.table_host[cache.slots[0], first_key // 64]
+    hidden = cache.table_host[cache.slots[0], (first_key - 1) // 64]
+    for h in (0, 2):       # the heads whose own query was copied into the keys
+        want = cache.v[blk, h // 2, first_key % 64, :]
+        close(got[h * hd:(h + 1) * hd], want, 2e-2)
+        wrong = cache.v[hidden, h // 2, (first_key - 1) % 64, :]
+        assert (got[h * hd:(h + 1) * hd].float() - wrong.float()).abs().max() > 0.5
+
+
 # ------------------------------------------------------------------ rotary + cache write
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pairing", [0, 1])

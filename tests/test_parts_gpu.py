@@ -173,40 +173,13 @@ def test_embedding_and_tied_head(dtype):
     close(logits, pl.lm_head(n.double(), table.double()), 1e-5 if dtype == torch.float32 else 1e-5)
 
 
-def test_prenorm_arrangement_fuses_the_residual():
-    """h += pending; a = mixer(norm(h)); h += a; returns ffn(norm(h)) unadded."""
-    from cretif_b200.parts.base import lookup_part
-
-    class Norm:
-        def forward(self, h, delta=None, rows=None, write_h=True):
-            if delta is not None:
-                h += delta
-            return h * 2
-
-    class Mixer:
-        def forward(self, x, ctx, cache):
-            return x + 1
-
-    class FF:
-        def forward(self, x, ctx):
-            return x * 10
-
-    class Layer:
-        mixer_norm, mixer, feed_forward_norm, feed_forward = Norm(), Mixer(), Norm(), FF()
-    run = lookup_part("arrangement", "prenorm")
-    h = torch.ones(2, 3)
-    out = run(Layer, h, torch.full((2, 3), 0.5), None, None)
-    # h = 1.5; a = 2*1.5 + 1 = 4; h = 5.5; out = 10 * (2 * 5.5) = 110
-    assert torch.allclose(h, torch.full((2, 3), 5.5)) and torch.allclose(out, torch.full((2, 3), 110.0))
-
-
 # ---------------------------------------------------------------------------------------
 # A toy architecture defined here: its mixer keeps a running sum of its inputs per sequence
 # (fixed-size state, no keys or values) and returns the running mean.
 # ---------------------------------------------------------------------------------------
 def _register_toy():
     from cretif_b200.cache import StateRequest
-    from cretif_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
+    from cretif_b200.config import (ModelSpec, PartSpec, ScheduleEntry, prenorm_layer,
                                     register_architecture)
     from cretif_b200.parts.base import Part, register_part
     from cretif_b200.weights.loader import WeightSpec
@@ -245,12 +218,12 @@ def _register_toy():
     def build_spec(cfg):
         H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
         norm = lambda name: PartSpec("rmsnorm", {"eps": 1e-5, "name": name})
-        layers = [LayerSpec(prefix=f"blocks.{i}.",
-                            mixer=PartSpec("running_mean", {"name": "mix.gain"}),
-                            feed_forward=PartSpec("gated_mlp", {
-                                "intermediate_size": cfg["ffn"], "activation": "silu",
-                                "names": {"gate": "ff.g", "up": "ff.u", "down": "ff.d"}}),
-                            mixer_norm=norm("n1"), feed_forward_norm=norm("n2"))
+        layers = [prenorm_layer(f"blocks.{i}.",
+                                mixer=PartSpec("running_mean", {"name": "mix.gain"}),
+                                feed_forward=PartSpec("gated_mlp", {
+                                    "intermediate_size": cfg["ffn"], "activation": "silu",
+                                    "names": {"gate": "ff.g", "up": "ff.u", "down": "ff.d"}}),
+                                mixer_norm=norm("n1"), feed_forward_norm=norm("n2"))
                   for i in range(L)]
         return ModelSpec(architecture="ToyRunningMean", vocab_size=cfg["vocab_size"],
                          hidden_size=H, embedding=PartSpec("token_embedding", {"name": "emb"}),
@@ -292,9 +265,15 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     rng = np.random.default_rng(0)
     reqs = [rng.integers(0, 120, size=n).tolist() for n in (40, 7, 23)]
     wants = [_toy_plain(w, 2, r).numpy() for r in reqs]
+    from replay_cuts import run_chunks, run_schedule
     for r, want in zip(reqs, wants):
         assert rel_err(run_whole(eng, r), want) < 1e-4
         assert rel_err(run_tail_by_one(eng, r, tail=10), want) < 1e-4
+    # chunks at a cached position: the state carries the scan over
+    assert rel_err(run_chunks(eng, reqs[0], [15, 1, 20]), wants[0]) < 1e-4
+    outs = run_schedule(eng, reqs, [[(0, 20)], [(0, 13), (1, 7)], [(0, 7), (2, 23)]])
+    for got, want in zip(outs, wants):
+        assert rel_err(got, want) < 1e-4
     for _ in range(2):          # the second pass takes the slots (and their state) again
         outs = run_batch(eng, reqs, [30, 2, 23])
         for got, want in zip(outs, wants):
@@ -316,7 +295,7 @@ def _wave(pos, hd, amp, freq, dtype=torch.float64):
 
 
 def _register_routed_toy():
-    from cretif_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
+    from cretif_b200.config import (ModelSpec, PartSpec, ScheduleEntry, prenorm_layer,
                                     register_architecture)
     from cretif_b200.csrc import ops
     from cretif_b200.parts.base import Part, register_part
@@ -329,18 +308,10 @@ def _register_routed_toy():
         def load(self, tensors):
             self.amp, self.freq = float(self.params["amp"]), float(self.params["freq"])
 
-        def prepare(self, max_positions):
-            z = torch.zeros((1, 1), dtype=torch.float32, device=self.device)
-            self._none = (z, z)
-
-        def rotate_and_store(self, qkv, ctx, cache, nh, nkv, hd):
+        def encode(self, qkv, ctx, nh, nkv, hd):
             w = _wave(ctx.tok_pos.cpu(), hd, self.amp, self.freq).to(qkv.device)
             qk = qkv[:, :(nh + nkv) * hd].unflatten(1, (nh + nkv, hd))
-            qk.copy_((qk.double() * w[:, None, :]).to(qkv.dtype))
-            kv = cache.kv          # stored as they are now (rotary_dim 0 of the library's kernel)
-            ops.rope_kv_append(qkv, *self._none, 0, 0, nh, nkv, hd, ctx.tok_pos, ctx.tok_seq,
-                               ctx.seq_slot, kv.table, kv.k, kv.v, kv.block_tokens,
-                               cache.writes, ctx.fault)
+            qk.copy_((qk.double() * w[:, None, :]).to(qkv.dtype))    # the mixer stores them
 
     @register_part("feed_forward", "best_expert")
     class BestExpert(Part):
@@ -368,8 +339,8 @@ def _register_routed_toy():
     def build_spec(cfg):
         H, L, hd = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["head_dim"]
         norm = lambda name: PartSpec("rmsnorm", {"eps": 1e-6, "name": name})
-        layers = [LayerSpec(
-            prefix=f"l{i}.",
+        layers = [prenorm_layer(
+            f"l{i}.",
             mixer=PartSpec("attention", {
                 "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"], "head_dim": hd,
                 "scale": hd ** -0.5, "window": 0,
@@ -452,3 +423,86 @@ def test_a_toy_position_encoding_and_a_routed_feed_forward(tmp_path):
     flat = dict(cfg, amp=0.0)
     other, _ = _routed_toy_plain(flat, w, reqs[0])
     assert rel_err(other.numpy(), wants[0]) > 1e-2
+
+
+# ---------------------------------------------------------------------------------------
+# A third toy architecture, made of the library's own parts in another block layout: layers
+# of ONE branch each.  Even layers are attention behind a norm and nothing else (no
+# feed-forward); odd layers are a feed-forward that reads the residual stream as it is and
+# whose output is normed AFTER the part, before it is added.  Only a spec builder is
+# registered: the engine, the loader, the cache and the random-weights mode follow from it.
+# ---------------------------------------------------------------------------------------
+def _register_lean_toy():
+    from cretif_b200.config import (BranchSpec, LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
+                                    register_architecture)
+
+    def build_spec(cfg):
+        H, L, hd = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["head_dim"]
+        norm = lambda name: PartSpec("rmsnorm", {"eps": 1e-5, "name": name})
+        attn = PartSpec("attention", {
+            "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"], "head_dim": hd,
+            "scale": hd ** -0.5, "window": 0,
+            "position": {"kind": "rotary", "theta": 10000.0, "rotary_dim": hd, "pairing": "half"},
+            "names": {"q": "q", "k": "k", "v": "v", "o": "o"}})
+        ffn = PartSpec("gated_mlp", {"intermediate_size": cfg["ffn"], "activation": "silu",
+                                     "names": {"gate": "g", "up": "u", "down": "d"}})
+        layers = [LayerSpec(f"l{i}.", (BranchSpec("mixer", attn, norm=norm("pre")),))
+                  if i % 2 == 0 else
+                  LayerSpec(f"l{i}.", (BranchSpec("feed_forward", ffn, post_norm=norm("post")),))
+                  for i in range(L)]
+        return ModelSpec(architecture="ToyLean", vocab_size=cfg["vocab_size"], hidden_size=H,
+                         embedding=PartSpec("token_embedding", {"name": "emb"}),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(L)],
+                         final_norm=norm("final"),
+                         head=PartSpec("linear_head", {"tied": True, "name": "head",
+                                                       "tied_to": "emb"}),
+                         max_positions=cfg["max_positions"])
+    register_architecture("ToyLean", lambda raw: dict(raw), build_spec)
+
+
+def _lean_toy_plain(cfg, w, ids):
+    nh, nkv, hd = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    S = len(ids)
+    h = pl.embed(w["emb"], ids)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"l{i}."
+        if i % 2 == 0:
+            n = pl.rmsnorm(h, w[p + "pre"], 1e-5)
+            q = (n @ w[p + "q"].T).reshape(S, nh, hd)
+            k = (n @ w[p + "k"].T).reshape(S, nkv, hd)
+            v = (n @ w[p + "v"].T).reshape(S, nkv, hd)
+            q = torch.stack([pl.rope_half(q[t], t, 10000.0) for t in range(S)])
+            k = torch.stack([pl.rope_half(k[t], t, 10000.0) for t in range(S)])
+            h = h + pl.attention(q, k, v, hd ** -0.5).reshape(S, nh * hd) @ w[p + "o"].T
+        else:
+            y = pl.swiglu(h, w[p + "g"], w[p + "u"], w[p + "d"])
+            h = h + pl.rmsnorm(y, w[p + "post"], 1e-5)
+    return pl.lm_head(pl.rmsnorm(h, w["final"], 1e-5), w["emb"])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 2e-2)])
+def test_blocks_of_one_branch_and_a_norm_after_the_part(tmp_path, dtype, tol):
+    from replay_cuts import rel_err, run_batch, run_chunks, run_tail_by_one, run_whole
+    from cretif_b200.engine import Engine
+    from cretif_b200.weights.random_model import write_random_model
+    _register_lean_toy()
+    cfg = {"architectures": ["ToyLean"], "hidden_size": 64, "num_hidden_layers": 4, "heads": 4,
+           "kv_heads": 2, "head_dim": 16, "ffn": 96, "vocab_size": 150, "max_positions": 256}
+    d = str(tmp_path / "lean")
+    write_random_model(d, cfg, seed=8)
+    eng = Engine(d, dtype=dtype, max_tokens=1024)
+    assert [len(layer.branches) for layer in eng.model.layers] == [1, 1, 1, 1]
+    # two of the four layers keep keys and values; the others keep nothing
+    assert eng.cache.stats()["groups"][0]["layers"] == 2
+    _, w = pl.read_model_folder(d)
+    rng = np.random.default_rng(2)
+    reqs = [rng.integers(0, 150, size=n).tolist() for n in (70, 9, 33)]
+    wants = [_lean_toy_plain(cfg, w, r).numpy() for r in reqs]
+    for r, want in zip(reqs, wants):
+        assert rel_err(run_whole(eng, r), want) <= tol
+        assert rel_err(run_tail_by_one(eng, r, tail=12), want) <= tol
+    assert rel_err(run_chunks(eng, reqs[0], [30, 1, 25]), wants[0]) <= tol
+    for _ in range(2):
+        for got, want in zip(run_batch(eng, reqs, [50, 3, 33]), wants):
+            assert rel_err(got, want) <= tol
+    eng.cache.check()

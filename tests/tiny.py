@@ -23,8 +23,17 @@ TINY_C = {
     "intermediate_size": 200, "vocab_size": 333, "rope_theta": 500000.0, "rms_norm_eps": 3e-5,
     "tie_word_embeddings": False, "max_position_embeddings": 1024, "rope_interleaved": True,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 11, "B": 22, "C": 33}
+# 4 layers of which the first and third see only the last 24 keys (a cache group of their
+# own, whose blocks are given back behind the window), 5 heads on 1 key/value head.
+TINY_W = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 80, "num_hidden_layers": 4,
+    "num_attention_heads": 5, "num_key_value_heads": 1, "head_dim": 16,
+    "intermediate_size": 112, "vocab_size": 200, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 512, "sliding_window": 24,
+    "layer_types": ["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "W": TINY_W}
+SEEDS = {"A": 11, "B": 22, "C": 33, "W": 44}
 
 
 def tokens(name: str, length: int, seed: int):

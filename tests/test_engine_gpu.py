@@ -139,7 +139,7 @@ def test_a_prompt_fed_in_chunks(engines, plain_logits, name, dtype):
     tests/test_attention.cu:307-336).  Alone, and inside a batch in which other sequences
     start fresh or go on by one token in the same step."""
     eng = engines(name, dtype)
-    n = LENGTHS[name][3] + 18
+    n = LENGTHS[name][3] + 30
     toks = tiny.tokens(name, n, 31)
     want = plain_logits(name, toks)
     assert rel_err(run_chunks(eng, toks, [40, 30, 1, 17]), want) <= TOL[dtype]
@@ -188,29 +188,30 @@ def test_a_sliding_window_from_config_json(engines, plain_logits, model_dirs, dt
     slot = eng.alloc_slot()
     eng.step([(slot, tiny.tokens("W", 200, 9))])
     free = dict(zip([g["window"] for g in groups], eng.cache.stats()["blocks_free"]))
-    assert free[0] == eng.cache.n_blocks - 4 and free[24] == eng.cache.n_blocks - 1
+    assert free[0] == eng.cache.n_blocks - 4 and free[24] == eng.cache.n_blocks - 2
     eng.free_slot(slot)
     eng.cache.check()
 
 
 def test_a_sliding_window_with_sharp_attention(model_dirs, tmp_path):
-    """Queries and keys scaled up so that every query reads a few particular keys: one key
-    too many or too few at the window's edge changes the logits by far more than rounding."""
+    """Queries and keys of the two windowed layers scaled up (by 8: the scores by 64) so that
+    every query reads a few particular keys: one key too many at the window's edge then moves
+    the logits by 0.2 of the largest, fifty times what rounding to bfloat16 moves them."""
     import plain_llama as pl
     from cretif_b200.engine import Engine
     from cretif_b200.weights import write_model_folder
     cfg, w = pl.read_model_folder(model_dirs["W"])
     tensors = {k: v.to(torch.float32) for k, v in w.items()}
-    for i in range(cfg["num_hidden_layers"]):
+    for i in (0, 2):
         for name in ("q_proj", "k_proj"):
-            tensors[f"model.layers.{i}.self_attn.{name}.weight"] *= 25.0
+            tensors[f"model.layers.{i}.self_attn.{name}.weight"] *= 8.0
     d = str(tmp_path / "sharp_w")
     write_model_folder(d, cfg, tensors)
     cfg, w = pl.read_model_folder(d)
     toks = tiny.tokens("W", 140, 77)
     want = pl.forward(cfg, w, toks).numpy()
     wider = pl.forward(dict(cfg, sliding_window=25), w, toks).numpy()
-    assert rel_err(wider, want) > 1e-2                 # the edge matters with these weights
+    assert rel_err(wider, want) > 0.1                  # the edge matters with these weights
     eng = Engine(d, dtype="float32", max_tokens=512)
     assert rel_err(run_whole(eng, toks), want) <= 1e-4
     assert rel_err(run_tail_by_one(eng, toks, tail=40), want) <= 1e-4
@@ -219,5 +220,5 @@ def test_a_sliding_window_with_sharp_attention(model_dirs, tmp_path):
     want16 = pl.forward(cfg, w, toks, storage=torch.bfloat16).numpy()
     for got in (run_whole(eng16, toks), run_tail_by_one(eng16, toks, tail=40),
                 run_chunks(eng16, toks, [23, 24, 25, 1, 40])):
-        assert rel_err(got, want16) <= 3e-2            # against the plain model rounded alike
-        assert rel_err(got, wider) > 3 * rel_err(got, want16)
+        assert rel_err(got, want16) <= TOL["bfloat16"]  # against the plain model rounded alike
+        assert rel_err(got, wider) > 0.1

@@ -592,10 +592,9 @@ def test_attn_decode_finds_a_far_key(ops, cluster):
         close(out[0, h * hd:(h + 1) * hd], cache.v[blk, h // 2, target % 64, :], 2e-2)
 
 
-@pytest.mark.parametrize("kernel", ["simt", "decode_split", "decode_cluster", "decode_cuda_cores",
-                                    "prefill"])
+@pytest.mark.parametrize("kernel,splits", [("simt", 1), ("prefill", 1)] + [
+    (k, n) for k in ("decode_split", "decode_cluster", "decode_cuda_cores") for n in (1, 3, 16)])
 @pytest.mark.parametrize("first_key", [128, 191])       # a block's first and last position
-@pytest.mark.parametrize("splits", [1, 3, 16])
 def test_the_edge_of_a_window_with_dominant_keys(ops, kernel, first_key, splits):
     """A query at position 299 with a window that begins at ``first_key``.  The key just
     before the window is made to dominate everything (it must not be seen), the window's
@@ -603,8 +602,6 @@ def test_the_edge_of_a_window_with_dominant_keys(ops, kernel, first_key, splits)
     too many or too few changes it completely.  Random keys alone give diffuse weights under
     which one key at the edge hides inside the tolerance.  With 16 ranges most of them are
     empty, and the leading cache blocks lie wholly outside the window."""
-    if kernel in ("simt", "prefill") and splits != 1:
-        pytest.skip("no ranges to split")
     nh, nkv, hd, n = 4, 2, 64, 300
     pos = n - 1
     window = pos - first_key + 1

@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-    python bench.py --impl reference ...      # the reference arm (see below)
+    python bench.py --impl reference ...      # the reference arm (see reference_arm)
 
 The model has the layer sizes of SmolLM2-135M (30 layers, width 576, 9 heads on 3
 key/value heads of 64, feed-forward 1536, vocabulary 49152, tied head) with seeded
@@ -233,6 +233,80 @@ def probe(engine, args) -> int:
     return 0
 
 
+def reference_arm(args) -> int:
+    """The unmodified reference (CuInfer), built from its own sources by
+    ``baseline/reference_tools.py`` into ``baseline/_ref/cuinfer``, run through its stock command
+    line ``cuinfer <gguf> <prompt> <n>``.  It serves one sequence at a time, in float32, with
+    a context of at most 2,048 positions, so its arm is batch 1 with a 1,024-token prompt: the
+    closest it can do.  Two runs that differ only in the number of new tokens give the decode
+    rate (its own timer covers prefill + decoding; the difference leaves the decoding)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_tools as ref
+    why = ref.available()
+    if why is None and args.gpus != 1:
+        why = "the reference runs on one GPU only"
+    if why is None:
+        import torch
+        if not torch.cuda.is_available():
+            why = "no CUDA device here (the reference binary is built and needs a GPU)"
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    import numpy as np
+    from cretif_b200.weights.random_model import write_random_model
+    cfg = _preset(SIZES[args.size])
+    cfg["rope_interleaved"] = True
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    prompt_len, first = 1024, max(args.warmup, 3)
+    steps = max(args.steps, 128)
+    steps = min(steps, 2048 - prompt_len - first - 1)
+    tmp = tempfile.mkdtemp(prefix="cretif_ref_")
+    try:
+        write_random_model(tmp, cfg, seed=1234)
+        gguf = os.path.join(tmp, "model.gguf")
+        ref.write_gguf(tmp, gguf)
+        chars = ref.char_ids(cfg["vocab_size"])
+        rng = np.random.default_rng(0)
+        ids = [chars[i] for i in rng.integers(0, len(chars), size=prompt_len)]
+        prompt = ref.prompt_for(ids, cfg["vocab_size"])
+        with ClockSampler() as clocks:
+            short = ref.generate(gguf, prompt, first)
+            long_ = ref.generate(gguf, prompt, first + steps)
+    except Exception as e:          # a build that does not run here, a fault of the reference
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "the reference did not run: "
+                                         + " ".join(str(e).split())[:300]}))
+        return 0
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    new = long_["positions"] - short["positions"]
+    ms = long_["ms"] - short["ms"]
+    if new <= 0 or ms <= 0:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference stopped early (its end-of-sequence id was sampled)"}))
+        return 0
+    line = {
+        "metric": f"decode tokens/s (SmolLM2-{args.size.upper()} sizes, random weights, batch 1)",
+        "value": new / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": new,
+        "warmup": first, "ms_per_step": ms / new, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "reference",
+        "same_config": False,
+        "config": {"model": f"SmolLM2-{args.size.upper()} sizes (Llama)",
+                   "layers": cfg["num_hidden_layers"], "global_batch": 1,
+                   "prompt_len": prompt_len, "seq_len": prompt_len + first + steps,
+                   "weights": "random N(0,0.02), seed 1234, as F32 GGUF",
+                   "why_not_the_same": "the reference serves one sequence, in float32, up to "
+                                       "2,048 positions",
+                   "timing": "the reference's own timer; difference of two runs"},
+        "e2e": {"value": long_["positions"] / (long_["ms"] * 1e-3), "unit": "positions/s",
+                "includes": "prefill of 1,024 tokens and decoding, text in and text out"},
+        "clocks": clocks.result,
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -251,12 +325,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++/CUDA program with no Python package "
-                          "(pip finds no setup.py or pyproject.toml), its build fetches "
-                          "googletest from the network, and it runs GGUF model files that "
-                          "cannot be downloaded here"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (the engine is "
               "single-GPU by design)")

@@ -5,10 +5,13 @@ package: it reads config.json with ``json`` and the weights with the
 ``safetensors`` library, and computes in float64 (or float32) with elementary
 torch arithmetic on the CPU.
 
-It rests on the reference's formulas, cited function by function as
+It follows the reference's formulas, cited function by function as
 ``file:line`` within the reference project.  The reference's own model code is
-CUDA-only (it has no CPU forward pass that could be imported or compiled here),
-so there is no golden output of the reference itself behind this file.
+CUDA-only (it has no CPU forward pass that could be imported or compiled on a
+machine without a GPU), so it was run once on a GPU instead: the logits its
+unmodified program printed for seeded random models lie under ``tests/golden/``
+with the script that made them, and ``tests/test_reference_golden.py`` checks on
+the CPU that :func:`forward` reproduces them.
 """
 from __future__ import annotations
 

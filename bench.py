@@ -13,7 +13,12 @@ launching stream.  ``value`` is decoded tokens per second at the default batch o
 ``e2e`` is the same through ``Engine.generate`` with host token lists in and out;
 ``prefill`` is one step over a 2,048-token prompt; ``roofline`` is the bytes a decode
 step has to read (every weight once plus the live requests' cache) over its time,
-against the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+against the measured copy bandwidth.  ``points`` holds decode at batch 1 and 64 and, at
+the headline batch, at contexts of about 3,072 and 4,096 (``points_roofline_frac``: the same
+fraction for each); ``prefill_b8`` and ``prefill_b64`` are steps over 8 and 64 prompts of
+2,048 tokens; ``shares`` says where a decode step's time goes (each kind of kernel alone).
+``--size 360m --unequal`` decodes after prompts of unequal lengths 256..2,048;
+``--dtype float32`` measures the true 32-bit path.
 Every weight plus the cache exceed the L2 cache, so no flush is needed between steps.
 """
 from __future__ import annotations
@@ -106,19 +111,22 @@ def model_numbers(cfg, layers):
             "kv_bytes_per_token": layers * 2 * nkv * hd * 2, "per_layer": per_layer}
 
 
-def run_decode(engine, batch, steps, warmup, prompt_len, seed=0):
+def run_decode(engine, batch, steps, warmup, prompt_len, seed=0, unequal=False, shares=False):
     """Prefill `batch` prompts, then time `steps` graph-replayed decode steps.
-    Returns (ms_per_step, mean context during the timed steps, launches per step)."""
+    Returns (ms_per_step, mean context during the timed steps, launches per step[, shares])."""
     import numpy as np
     import torch
     from cretif_b200.csrc import ops
     from cretif_b200.engine.generate import EngineBackend
     from cretif_b200.sampling import SamplingParams
     rng = np.random.default_rng(seed)
-    prompts = [rng.integers(0, engine.vocab_size, size=prompt_len).tolist() for _ in range(batch)]
+    lengths = [prompt_len] * batch
+    if unequal and batch > 1:                 # 256 .. prompt_len, the longest one present
+        lengths = [prompt_len] + rng.integers(256, prompt_len + 1, size=batch - 1).tolist()
+    prompts = [rng.integers(0, engine.vocab_size, size=n).tolist() for n in lengths]
     be = EngineBackend(engine, SamplingParams(0.0, 0, 42), use_graph=True, run_ahead=False)
-    total = prompt_len + warmup + steps + 1
-    be.start_batch(list(range(batch)), prompts, [total] * batch)
+    extra = warmup + steps + 1
+    be.start_batch(list(range(batch)), prompts, [n + extra for n in lengths])
     try:
         be.prefill()
         active = list(range(batch))
@@ -130,40 +138,129 @@ def run_decode(engine, batch, steps, warmup, prompt_len, seed=0):
         cache, runner = engine.cache, be.runner
         slots = [(s, 1) for s in be.slots]
         torch.cuda.synchronize()
-        ctx0 = int(cache.lengths[be.slots[0]])
+        ctx0 = float(np.mean([cache.lengths[s] for s in be.slots]))
+        longest = int(max(cache.lengths[s] for s in be.slots))
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for _ in range(steps):
-            cache.begin_step(slots)
-            runner.run()
-            cache.end_step(slots)
+        for i in range(steps):
+            engine.run(slots, lambda: runner.run(longest + i + 1))
         end.record()
         torch.cuda.synchronize()
         ms = start.elapsed_time(end) / steps
         engine.check_fault()
-        return ms, ctx0 + (steps - 1) / 2.0 + 1, per_step
+        mean_ctx = ctx0 + (steps - 1) / 2.0 + 1
+        if shares:
+            return ms, mean_ctx, per_step, decode_shares(engine, runner, batch, longest + steps)
+        return ms, mean_ctx, per_step
     finally:
         be.end_batch()
 
 
-def run_prefill(engine, tokens, repeats, warmup):
-    """One step over a prompt of `tokens` ids through Engine.step, timed with CUDA events.
-    (A step shape that repeats is replayed as a CUDA graph from its third call on; the
-    host-to-device copy of the token ids is inside the timed region.)"""
+def decode_shares(engine, runner, batch, context):
+    """Where a decode step's time goes: each kind of kernel of the step alone — every layer's
+    launch of that kind, on the model's own weights and cache, captured as one CUDA graph
+    and replayed — in microseconds per step.  Alone, a kernel's weight fetch no longer
+    overlaps its predecessor's tail, so the parts add up to more than the step."""
+    import torch
+    from cretif_b200.csrc import ops
+    model = engine.model
+    b = runner.bufs[batch]
+    ctx = engine.context(T=batch, B=batch, tok_ids=b["tok_ids"], tok_pos=b["tok_pos"],
+                         tok_seq=b["tok_seq"], seq_slot=b["seq_slot"], seq_start=b["seq_start"],
+                         cu_seqlens=b["cu"], is_decode=True, max_new=1, max_context=context)
+    layers = []
+    for i, entry in enumerate(model.spec.schedule):
+        layer = model.layers[entry.layer]
+        caches = model.layer_caches(i, engine.cache)
+        mix = next(k for k, br in enumerate(layer.branches) if br.role == "mixer")
+        ffn = next(k for k, br in enumerate(layer.branches) if br.role == "feed_forward")
+        layers.append((layer.branches[mix], caches[mix], layer.branches[ffn]))
+    a0 = layers[0][0].part
+    dev = engine.device
+    h = torch.zeros((batch, model.spec.hidden_size), dtype=torch.float32, device=dev)
+    ops.embed_rows(model.embedding.table, b["tok_ids"], h, engine.fault)
+    q = torch.zeros((batch, a0.q_dim), dtype=engine.dtype, device=dev)
+    o = torch.zeros((batch, a0.q_dim), dtype=engine.dtype, device=dev)
+    act = torch.zeros((batch, layers[0][2].part.inter), dtype=engine.dtype, device=dev)
+    logits = torch.zeros((batch, engine.vocab_size), dtype=torch.float32, device=dev)
+    sampled = torch.zeros(batch, dtype=torch.int32, device=dev)
+
+    def qkv(mb, cache, fb):
+        a, (w, eps), kv = mb.part, mb.norm.rms_params(), cache.kv
+        cos, sin, pairing, _ = a.position.rotary_table()
+        ops.fused_qkv_rope(h, w, eps, a.w_qkv, q, cos, sin, pairing, a.nh, a.nkv, a.hd,
+                           ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k, kv.v,
+                           kv.block_tokens, True, ctx.fault)
+
+    def attention(mb, cache, fb):
+        mb.part.attend(q, o, ctx, cache.kv)
+
+    def o_proj(mb, cache, fb):
+        ops.fused_linear_add(o, mb.part.w_o, h)
+
+    def gate_up(mb, cache, fb):
+        f, (w, eps) = fb.part, fb.norm.rms_params()
+        ops.fused_gate_up_silu(h, w, eps, f.w_gate_up, act, f.gu_block)
+
+    def down(mb, cache, fb):
+        ops.fused_linear_add(act, fb.part.w_down, h)
+
+    def head_and_sample():
+        w, eps = model.final_norm.rms_params()
+        ops.fused_norm_linear(h, w, eps, model.head.weight, logits)
+        runner.sampler(logits, sampled, b["request"], b["draw"])
+
+    def timed(fn):
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+        torch.cuda.synchronize()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            g.replay()
+        a.record()
+        for _ in range(10):
+            g.replay()
+        z.record()
+        torch.cuda.synchronize()
+        h.zero_()                 # the residual additions of the replays may have overflowed
+        return a.elapsed_time(z) * 100.0          # microseconds per replay
+    out = {}
+    try:
+        for name, fn in (("qkv", qkv), ("attention", attention), ("o_proj", o_proj),
+                         ("gate_up", gate_up), ("down", down)):
+            out[name] = timed(lambda fn=fn: [fn(*t) for t in layers])
+        out["head_and_sample"] = timed(head_and_sample)
+    except Exception as e:        # a model whose parts are not the fused bfloat16 ones
+        return {"unavailable": " ".join(str(e).split())[:200]}
+    out["unit"] = "us per step, each kind of kernel alone"
+    return out
+
+
+def run_prefill(engine, tokens, repeats, warmup, batch=1):
+    """One step over `batch` prompts of `tokens` ids through Engine.step, timed with CUDA
+    events.  (A step shape that repeats is replayed as a CUDA graph from its third call on;
+    the host-to-device copy of the token ids is inside the timed region.)"""
     import numpy as np
     import torch
     rng = np.random.default_rng(7)
-    prompt = rng.integers(0, engine.vocab_size, size=tokens).tolist()
+    prompts = [rng.integers(0, engine.vocab_size, size=tokens).tolist() for _ in range(batch)]
     times = []
     for i in range(warmup + repeats):
-        slot = engine.alloc_slot()
+        slots = [engine.alloc_slot() for _ in range(batch)]
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        engine.step([(slot, prompt)], "last", check=False)
+        engine.step(list(zip(slots, prompts)), "last", check=False)
         b.record()
         torch.cuda.synchronize()
-        engine.free_slot(slot)
+        for s in slots:
+            engine.free_slot(s)
         if i >= warmup:
             times.append(a.elapsed_time(b))
     engine.check_fault()
@@ -198,39 +295,6 @@ def run_e2e(engine, batch, steps, prompt_len):
     if n > n1 and dt > dt1:
         out["decode_only"] = (n - n1) / (dt - dt1)       # tokens/s after the first token
     return out
-
-
-def probe(engine, args) -> int:
-    """A small eager workload for profilers: `--probe decode` runs --steps decode steps of
-    --batch sequences without a CUDA graph after a 2,048-token prefill; `--probe prefill`
-    runs --steps prefills of one 2,048-token prompt."""
-    import numpy as np
-    import torch
-    from cretif_b200.engine.generate import EngineBackend
-    from cretif_b200.sampling import SamplingParams
-    if args.probe == "prefill":
-        ms = run_prefill(engine, PROMPT_LEN, repeats=max(1, args.steps), warmup=1)
-        print(f"prefill of {PROMPT_LEN} tokens: {ms:.3f} ms")
-        return 0
-    rng = np.random.default_rng(0)
-    B = args.batch
-    prompts = [rng.integers(0, engine.vocab_size, size=PROMPT_LEN).tolist() for _ in range(B)]
-    be = EngineBackend(engine, SamplingParams(), use_graph=False)
-    be.start_batch(list(range(B)), prompts, [PROMPT_LEN + args.steps + 8] * B)
-    try:
-        be.prefill()
-        active = list(range(B))
-        be.decode(active)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            be.decode(active)
-        torch.cuda.synchronize()
-        print(f"eager decode, batch {B}: {(time.perf_counter() - t0) * 1e3 / args.steps:.3f} "
-              "ms/step (launch-bound without the graph)")
-    finally:
-        be.end_batch()
-    return 0
 
 
 def reference_arm(args) -> int:
@@ -316,12 +380,15 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true",
+                    help="only the headline decode, the 2,048-token prefill and e2e")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="measure one phase only and print a short line (a small workload, "
+                         "for instance under a profiler)")
     ap.add_argument("--size", default="135m", choices=sorted(SIZES),
                     help="layer sizes: SmolLM2-135M (the headline), 360M or 1.7B")
-    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
-                    help="run a few eager steps of one phase and print their time (for "
-                         "profilers); no JSON line")
+    ap.add_argument("--unequal", action="store_true",
+                    help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -334,7 +401,6 @@ def main() -> int:
         args.warmup = 3
 
     import torch
-    from cretif_b200.csrc import ops
     from cretif_b200.engine import Engine
     from cretif_b200.weights.random_model import write_random_model
 
@@ -346,43 +412,75 @@ def main() -> int:
     pk = peaks()
     nums = model_numbers(cfg, layers)
     wbytes = 2 if args.dtype == "bfloat16" else 4
+    points_on = not args.skip_points and args.only is None
 
     tmp = tempfile.mkdtemp(prefix="cretif_bench_")
     try:
         write_random_model(tmp, cfg, seed=1234)
-        max_batch = args.batch if args.skip_points else max(args.batch, 64)
+        max_batch = max(args.batch, 64) if points_on else args.batch
         engine = Engine(tmp, dtype=args.dtype, max_tokens=max_batch * CONTEXT + 64 * 64,
                         max_len=CONTEXT)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
 
-    if args.probe:
-        return probe(engine, args)
+    def step_bytes(batch, mean_ctx):
+        """What a decode step has to read: every weight once, the live requests' cache."""
+        return (nums["matmul_params"] * wbytes + nums["norm_params"] * 4
+                + batch * mean_ctx * nums["kv_bytes_per_token"] * (wbytes // 2))
 
-    with ClockSampler() as clocks:
-        ms, mean_ctx, per_step = run_decode(engine, args.batch, steps, args.warmup, PROMPT_LEN)
-    value = args.batch / (ms * 1e-3)
-    step_bytes = (nums["matmul_params"] * wbytes + nums["norm_params"] * 4
-                  + args.batch * mean_ctx * nums["kv_bytes_per_token"] * (wbytes // 2))
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    def hbm_frac(batch, mean_ctx, ms):
+        return step_bytes(batch, mean_ctx) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
 
-    pre_ms = run_prefill(engine, PROMPT_LEN, repeats=5, warmup=3)
     T = PROMPT_LEN
     nh, hd = cfg["num_attention_heads"], cfg["head_dim"]
-    flops = 2 * T * (nums["matmul_params"] - cfg["vocab_size"] * cfg["hidden_size"]) \
-        + 2 * cfg["vocab_size"] * cfg["hidden_size"] \
-        + layers * nh * 2 * hd * T * (T + 1)          # causal QK^T and PV
-    prefill = {"value": T / (pre_ms * 1e-3), "tokens": T, "ms": pre_ms,
-               "frac": flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "flops": flops}
 
-    points = {}
-    if not args.skip_points:
+    def prefill_record(batch, repeats=5, warmup=3):
+        ms = run_prefill(engine, T, repeats=repeats, warmup=warmup, batch=batch)
+        flops = batch * (2 * T * (nums["matmul_params"] - cfg["vocab_size"] * cfg["hidden_size"])
+                         + 2 * cfg["vocab_size"] * cfg["hidden_size"]      # the head: last rows
+                         + layers * nh * 2 * hd * T * (T + 1))             # causal QK^T and PV
+        return {"value": batch * T / (ms * 1e-3), "tokens": batch * T, "ms": ms,
+                "frac": flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "flops": flops}
+
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "batch": args.batch,
+                          **prefill_record(args.batch, repeats=max(1, min(args.steps, 5)),
+                                           warmup=max(1, min(args.warmup, 3)))}))
+        return 0
+
+    with ClockSampler() as clocks:
+        ms, mean_ctx, per_step, shares = run_decode(engine, args.batch, steps, args.warmup,
+                                                    PROMPT_LEN, unequal=args.unequal,
+                                                    shares=True)
+    value = args.batch / (ms * 1e-3)
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": args.batch, "value": value,
+                          "ms_per_step": ms, "frac": hbm_frac(args.batch, mean_ctx, ms),
+                          "shares": shares}))
+        return 0
+
+    prefill = prefill_record(1)
+    points, fracs, more = {}, {}, {}
+    if points_on:
+        few = min(256, steps)
         for b, name in ((1, "decode_b1"), (64, "decode_b64")):
-            pms, _, _ = run_decode(engine, b, min(256, steps), args.warmup, PROMPT_LEN, seed=b)
+            pms, pctx, _ = run_decode(engine, b, few, args.warmup, PROMPT_LEN, seed=b,
+                                      unequal=args.unequal)
             points[name] = b / (pms * 1e-3)
+            fracs[name] = hbm_frac(b, pctx, pms)
+        # decoding at longer contexts (the batch of the headline), and whole batches of prompts
+        for ctx_at in (3072, 4096):
+            n = min(64, steps)
+            pms, pctx, _ = run_decode(engine, args.batch, n, args.warmup,
+                                      ctx_at - args.warmup - n - 1, seed=ctx_at)
+            points[f"decode_b{args.batch}_ctx{ctx_at}"] = args.batch / (pms * 1e-3)
+            fracs[f"decode_b{args.batch}_ctx{ctx_at}"] = hbm_frac(args.batch, pctx, pms)
+        for b in (8, 64):
+            more[f"prefill_b{b}"] = prefill_record(b, repeats=3, warmup=2)
 
     e2e = run_e2e(engine, args.batch, min(steps, 512), PROMPT_LEN)
 
+    achieved = step_bytes(args.batch, mean_ctx) / (ms * 1e-3) / 1e9
     line = {
         "metric": f"decode tokens/s (SmolLM2-{args.size.upper()} sizes, random weights, batch "
                   f"{args.batch}, context 2048->4096)",
@@ -394,16 +492,21 @@ def main() -> int:
                    "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
                    "heads": nh, "kv_heads": cfg["num_key_value_heads"], "head_dim": hd,
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch, "prompt_len": PROMPT_LEN,
-                   "seq_len": CONTEXT, "mean_context_timed": mean_ctx, "parallelism": "none",
-                   "weights": "random N(0,0.02), seed 1234", "cache_block_tokens": 64,
+                   "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch,
+                   "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "mean_context_timed": mean_ctx,
+                   "prompts": "unequal 256..2048" if args.unequal else "equal",
+                   "parallelism": "none", "weights": "random N(0,0.02), seed 1234",
+                   "cache_block_tokens": 64,
                    "l2": "weights+cache read per step exceed L2, no flush",
                    "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "bytes": step_bytes,
-                     "of": pk["source"]},
+                     "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "bytes": step_bytes(args.batch, mean_ctx), "of": pk["source"]},
         "points": points,
+        "points_roofline_frac": fracs,
+        "shares": shares,
+        **more,
         "e2e": e2e,
         "gpu_launches": per_step * steps,
         "launches_per_step": per_step,

@@ -49,10 +49,14 @@ int cretif_gemm_skinny(const void* X, const void* W, void* C, int c_dt, int M, i
 int cretif_gemm_skinny_max_rows(void);
 
 // C[M,N] (= or +=) A[M,K] · W[N,K]^T on the tcgen05 tensor cores (TMA + TMEM), bfloat16
-// operands, C bfloat16 or float32 (+= only float32).  bn = 64/128/256 picks the tile width,
+// operands, C bfloat16 or float32 (+= only float32).  bn = 64/128/192/256 picks the tile width,
 // 0 lets the launcher choose.  A wait that expires sets bit 2 of *fault.
 int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda,
                    int ldw, int ldc, int accumulate, int bn, unsigned int* fault, void* stream);
+
+// (For tests that run both.)  Epilogue warps of the tensor-core product: 4 or 8; 0, the default,
+// chooses per launch.  Returns the old setting.
+int cretif_set_tc_epilogue_warps(int n);
 
 // The same product with fused epilogues (see gemm_tc.cu): SiLU·mul for the stacked gate|up
 // matrix whose rows are interleaved in blocks of 64 (I % 64 == 0), and rotary + cache write for
@@ -95,10 +99,6 @@ int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const voi
                            float* part_o, float* part_ml, int* counters, unsigned int* fault,
                            void* stream);
 
-// Tuning aid: depth of that kernel's ring of K/V stages (2..6; 0, the default, chooses per
-// launch).  Returns the old setting.
-int cretif_attn_decode_stages(int n);
-
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
@@ -115,23 +115,18 @@ int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, co
                               int ldw, void* act, int I, int gu_block, int M, int K,
                               unsigned int* fault, void* stream);
 int cretif_fused_smem_ok(int M, int K, int norm_prologue);
+// The three switches below exist so that tests can run both variants of a kernel on one
+// shape; an ordinary run never touches them.
 // Programmatic dependent launch of the fused kernels on (default) or off; returns the old value.
 int cretif_set_dependent_launch(int on);
 // Matrices with at least k columns, or of at least min_bytes bytes (negative: unchanged), take
 // the shared-memory streaming variant (decode_stream.cuh); returns the old column threshold.
 int cretif_set_stream_min_k(int k, long long min_bytes);
 long long cretif_stream_min_bytes(void);
-// ... for calls of at most this many tokens (default 64; beyond 16 as groups of 16 rows).
-// Returns the old limit.
-int cretif_set_stream_max_rows(int rows);
 // The register variant with more than eight rows and a norm prologue shares the rows'
 // normalisation among the CTAs of a thread-block cluster of up to n (1: every CTA norms
 // every row itself; at most 4, the default).  Returns the old value; n < 1 leaves it.
 int cretif_set_fused_cluster(int n);
-// Depth of that variant's ring of stages (2..8); 0, the default, chooses per launch.  early
-// (>= 0; negative leaves it) is the number of stages whose weights are asked for before the
-// kernel waits for the one before it.  Returns the old depth.
-int cretif_set_stream_stages(int n, int early);
 
 // Causal attention for whole prompts on tcgen05 (bfloat16, head_dim a multiple of 16 up to
 // 128, 64-token cache blocks).  qkv rows hold the query heads first; sequence b brings the

@@ -9,8 +9,8 @@ namespace cretif {
 
 // Tuning aid: a device buffer of 10 x 16 timestamps the next launches fill (see the kernel).
 static unsigned long long* g_dm_stamps = nullptr;
-// Tuning aid: depth of the K/V ring (3..6); 0 chooses per launch.
-static int g_dm_stages = 0;
+// Depth of the K/V ring (3..6); 0 chooses per launch.
+static const int g_dm_stages = 0;
 
 template <int HD16>
 static size_t dm_smem_bytes(bool cluster, int n_stages) {
@@ -76,15 +76,11 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
 
 using namespace cretif;
 
+#ifdef CRETIF_STAMPS
 extern "C" void cretif_attn_decode_stamps(unsigned long long* device_buffer) {
   g_dm_stamps = device_buffer;
 }
-
-extern "C" int cretif_attn_decode_stages(int n) {
-  const int was = g_dm_stages;
-  g_dm_stages = n <= 0 ? 0 : (n < 2 ? 2 : (n > kDmMaxStages ? kDmMaxStages : n));
-  return was;
-}
+#endif
 
 extern "C" int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const void* kc,
                                       const void* vc, long long n_blocks, const int* table,

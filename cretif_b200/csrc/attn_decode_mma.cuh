@@ -105,7 +105,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
   constexpr int hd = HD16 * 16;
   // Tuning aid: with a buffer given, lane 0 of every warp of the first CTA notes the time at
   // which it passes each phase ([warp][16]); the CTA that merges notes its own at [8][..].
-  const bool stamping = stamps && split == 0 && kvh == 0 && b == 0;
+  const bool stamping = kStamps && stamps && split == 0 && kvh == 0 && b == 0;
   auto stamp = [&](int row, int i) {
     if ((threadIdx.x & 31) == 0) {
       unsigned long long t;
@@ -424,7 +424,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
   __syncthreads();
   DM_STAMP(9);
   if (!*is_last) return;
-  const bool stamping_last = stamps && kvh == 0 && b == 0;
+  const bool stamping_last = kStamps && stamps && kvh == 0 && b == 0;
   if (stamping_last && threadIdx.x == 0) stamp(8, 0);
   float* wts = mrg;                       // [g][n_splits]
   float* inv_den = mrg + 8 * kDmTile;     // [g]
@@ -510,7 +510,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        unsigned int* __restrict__ fault, unsigned long long* stamps,
                        int n_stages) {
   extern __shared__ unsigned char smem_raw[];
-  if (stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
+  if (kStamps && stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     stamps[9 * 16] = t;

@@ -94,7 +94,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   // Tuning aid: with a buffer given, the first CTA (the heaviest tile) notes the times at
   // which its MMA thread and one softmax thread pass the phases of steps 0 .. 7:
   // [step][16] nanoseconds.
-  const bool stamping = stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+  const bool stamping = kStamps && stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && (threadIdx.x & 31) == 0;
   auto stamp = [&](int j, int i) {
     if (stamping && j < 8) {
       unsigned long long t;
@@ -391,9 +391,11 @@ using namespace cretif;
 
 // Tuning aid: a device buffer of 8 x 16 timestamps that the next launches fill (see the kernel).
 static unsigned long long* g_pf_stamps = nullptr;
+#ifdef CRETIF_STAMPS
 extern "C" void cretif_attn_prefill_stamps(unsigned long long* device_buffer) {
   g_pf_stamps = device_buffer;
 }
+#endif
 
 extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo,
                                       const void* kc, const void* vc, long long n_blocks,

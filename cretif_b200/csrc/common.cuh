@@ -37,6 +37,13 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
   return __float2bfloat16_rn(x);
 }
 
+// silu(g) = g / (1 + e^-g) for the bfloat16 kernels: exponential and quotient on the
+// special-function unit (relative error about 2^-21, far below the 2^-9 of the bfloat16 the
+// result is rounded to).  The float32 path divides and calls expf.
+__device__ __forceinline__ float silu_bf16_path(float g) {
+  return __fdividef(g, 1.0f + __expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -115,6 +122,15 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+// Phase timestamps inside the kernels (%globaltimer written to a buffer) are a tuning aid.
+// They are compiled only with -DCRETIF_STAMPS; in the ordinary build the constant below is
+// false and the compiler drops every trace of them.
+#ifdef CRETIF_STAMPS
+constexpr bool kStamps = true;
+#else
+constexpr bool kStamps = false;
+#endif
+
 // Which variant of a kernel a launch took, counted on the host at launch time (a replayed
 // CUDA graph counts nothing).  Tests read the counts to know that the path they mean to check
 // is the one that ran; nothing in the library depends on them.
@@ -130,6 +146,7 @@ enum Variant : int {
   kVarPrefillAttn,          // tcgen05 prefill attention
   kVarTc64, kVarTc128, kVarTc256,   // tcgen05 product by tile width
   kVarTcSeveralTiles,       // ... whose persistent CTAs walk more than one tile
+  kVarTc192,                // ... 192 columns wide
   kVarCount
 };
 void count_variant(int v);

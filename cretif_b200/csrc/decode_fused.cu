@@ -100,11 +100,11 @@ static int dispatch_registers(const FusedParams& p, int tiles, cudaStream_t st) 
 static int g_stream_min_k = 768;
 static long long g_stream_min_bytes = 16LL << 20;
 // ... and up to this many tokens (beyond 16 as groups of 16 rows that each stream the matrix)
-static int g_stream_max_rows = 64;
+static const int g_stream_max_rows = 64;
 // Depth of the streaming ring; 0: chosen per launch.
-static int g_stream_stages = 0;
+static const int g_stream_stages = 0;
 // Stages of weights asked for before the kernel waits for the kernel before it.
-static int g_stream_early = 1;
+static const int g_stream_early = 1;
 
 template <int NT, int PRO, int EPI>
 static int launch_stream(const FusedParams& whole, int tiles, cudaStream_t st) {
@@ -264,19 +264,6 @@ extern "C" long long cretif_stream_min_bytes(void) { return g_stream_min_bytes; 
 extern "C" int cretif_set_fused_cluster(int n) {
   const int was = g_fused_cluster;
   if (n >= 1) g_fused_cluster = n > kFuClusterMax ? kFuClusterMax : n;
-  return was;
-}
-
-extern "C" int cretif_set_stream_max_rows(int rows) {
-  const int was = g_stream_max_rows;
-  if (rows > 0) g_stream_max_rows = rows;
-  return was;
-}
-
-extern "C" int cretif_set_stream_stages(int n, int early) {
-  const int was = g_stream_stages;
-  g_stream_stages = n < 0 ? 0 : (n > kStMaxStages ? kStMaxStages : n);
-  if (early >= 0) g_stream_early = early;
   return was;
 }
 

@@ -216,7 +216,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
         // the unfused path stores gate and up as bfloat16 before the activation
         const float g = __bfloat162float(__float2bfloat16_rn(s0));
         const float u = __bfloat162float(__float2bfloat16_rn(s1));
-        p.act[(size_t)m * p.I + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+        p.act[(size_t)m * p.I + col] = __float2bfloat16_rn(silu_bf16_path(g) * u);
       } else {
         const int tiles_per_head = p.hd >> 4;
         const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;

@@ -137,6 +137,63 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
   }
 }
 
+// Many rows: a warp per row, eight rows per block, no block-wide barrier.  A lane keeps its
+// REGS float4 of the row between the sum of squares and the scaling, so a row makes one trip
+// from memory.  Lanes, order of the sums and the arithmetic are those of the fused decode
+// prologue (decode_fused.cuh), so a row gets the same numbers from either.
+template <int REGS, typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                        const float* __restrict__ weight, TO* __restrict__ out,
+                        const int* __restrict__ rows, int R, int H, float eps, int write_h) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  const int n4 = H >> 2;
+  float4 w[REGS];                       // the weight does not wait for the kernel before
+#pragma unroll
+  for (int u = 0; u < REGS; ++u) {
+    const int i = u * 32 + lane;
+    w[u] = i < n4 ? load4f(weight + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (r >= R) return;
+  const int src = rows ? rows[r] : r;
+  float* hrow = h + (size_t)src * H;
+  const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+  float4 v[REGS];
+#pragma unroll
+  for (int u = 0; u < REGS; ++u) {
+    const int i = u * 32 + lane;
+    v[u] = i < n4 ? load4f(hrow + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (drow) {
+#pragma unroll
+    for (int u = 0; u < REGS; ++u) {
+      const int i = u * 32 + lane;
+      if (i < n4) {
+        const float4 d = load4f(drow + 4 * i);
+        v[u].x += d.x; v[u].y += d.y; v[u].z += d.z; v[u].w += d.w;
+        if (write_h) store4f(hrow + 4 * i, v[u]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < REGS; ++u)
+    ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  TO* orow = out + (size_t)r * H;
+#pragma unroll
+  for (int u = 0; u < REGS; ++u) {
+    const int i = u * 32 + lane;
+    if (i < n4)
+      store4f(orow + 4 * i, make_float4(v[u].x * w[u].x * inv, v[u].y * w[u].y * inv,
+                                        v[u].z * w[u].z * inv, v[u].w * w[u].w * inv));
+  }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // `block` = 0: gu row = [gate (I) | up (I)]; block = b > 0: gate and up alternate in groups of b
 // columns (b gate columns, then the b up columns that belong to them).
@@ -151,7 +208,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
   const int ucol = block ? gcol + block : I + i;
   const float g = to_float(gu[t * 2 * (size_t)I + gcol]);
   const float u = to_float(gu[t * 2 * (size_t)I + ucol]);
-  act[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  // float32: the reference's x / (1 + expf(-x)) (src/kernels/elementwise.cu:93-99);
+  // bfloat16: the same on the special-function unit, as in the fused epilogues
+  const float s = sizeof(T) == 4 ? g / (1.0f + expf(-g)) : silu_bf16_path(g);
+  act[idx] = from_float<T>(s * u);
 }
 
 // ---------------------------------------------------------------- rotary + cache write
@@ -262,6 +322,32 @@ static int add_rmsnorm_out(float* h, const TD* delta, const float* w, void* out,
                            cudaStream_t st) {
   const bool aligned = H % 4 == 0 && (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)w |
                                        (uintptr_t)out) & 15) == 0;
+  if (aligned && R >= 64 && H / 4 <= 32 * 16) {
+    // many rows (a prompt): a warp per row
+    const int n4 = H / 4;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((R + 7) / 8);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
+#define CRETIF_ROWS(REGS, TO)                                                                  \
+  e = cudaLaunchKernelEx(&cfg, add_rmsnorm_rows_kernel<REGS, TD, TO>, h, delta, w, (TO*)out,   \
+                         rows, R, H, eps, write_h)
+    if (out_dt == kF32) {
+      if (n4 <= 32 * 8) CRETIF_ROWS(8, float); else CRETIF_ROWS(16, float);
+    } else if (out_dt == kBF16) {
+      if (n4 <= 32 * 8) CRETIF_ROWS(8, __nv_bfloat16); else CRETIF_ROWS(16, __nv_bfloat16);
+    } else {
+      return kBadDType;
+    }
+#undef CRETIF_ROWS
+    return e == cudaSuccess ? launch_status() : (int)e;
+  }
   if (aligned) {
     const int n4 = H / 4;
     const int vthreads = n4 >= 512 ? 256 : (n4 >= 128 ? 128 : (n4 >= 64 ? 64 : 32));

@@ -7,8 +7,10 @@
 // work) through a ring of stages guarded by full/empty mbarriers, which runs on from tile to
 // tile.  One thread of warp 1 issues tcgen05.mma (M=128, N=BN, K=16, bf16 in, f32
 // accumulate) on shared-memory descriptors into one of two 128 x BN accumulators in tensor
-// memory and commits each stage back to the producer.  Warps 2-5 read an accumulator with
-// tcgen05.ld (each thread one row) while the next tile's product fills the other, and store
+// memory and commits each stage back to the producer.  Warps 2-9 read an accumulator with
+// tcgen05.ld (two threads share a row, half of the columns each: with four warps a tile's
+// epilogue — a read-modify-write of the residual stream, a rotation or 128 x 128 SiLUs — took
+// longer than its product) while the next tile's product fills the other, and store
 // it as bfloat16 or float32, add it into a float32 matrix (the residual stream), or run one
 // of the fused epilogues below.  Both operands are K-major exactly as activations
 // [tokens, in] and weights [out, in] lie in memory, so nothing is transposed.  The kernel is
@@ -28,7 +30,10 @@
 namespace cretif {
 
 constexpr int kTcBM = 128, kTcBK = 64;
-constexpr int kTcThreads = 192;
+// Producer warp, MMA warp, and four or eight epilogue warps (one or two per quadrant of
+// tensor-memory lanes), chosen per launch by the block size.
+constexpr int kTcMaxThreads = (2 + 8) * 32;
+inline int tc_threads(int epilogue_warps) { return (2 + epilogue_warps) * 32; }
 
 // The depth of the ring is chosen per launch.  With more tiles than SMs, narrow tiles take
 // three stages so that two (BN = 128) or three (BN = 64) CTAs share an SM and hide each
@@ -44,8 +49,11 @@ struct TcSmem {
   static constexpr int total(int stages) {     // barriers behind the stages, + align slack
     return stages * kStage + (2 * kTcMaxStages + 4) * 8 + 16 + 1024;
   }
+  // Tensor memory is handed out in powers of two columns; the two accumulators lie at
+  // columns 0 and BN of the allocation.
+  static constexpr int kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
   static int stages_for(long long ctas, int num_kb, int sm_count) {
-    int stages = BN >= 256 ? 4 : 3;
+    int stages = BN >= 256 ? 4 : (BN >= 192 ? 5 : 3);
     if (ctas <= sm_count) {
       stages = num_kb < kTcMaxStages ? (num_kb < 3 ? 3 : num_kb) : kTcMaxStages;
       while (stages > 3 && total(stages) > 200 * 1024) --stages;
@@ -80,13 +88,13 @@ __device__ __forceinline__ float round_bf16(float x) {
 }
 
 template <int BN, int EPI, typename TC>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcMaxThreads, BN <= 128 ? 2 : 1)   // narrow tiles: two CTAs an SM
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
                int kTcStages, unsigned long long* stamps, int n_n_tiles, int n_tiles) {
   // Tuning aid: with a buffer given, lane 0 of each warp of the first CTA notes the time at
   // which it passes the phases of its first tile: [warp][8] nanoseconds.
-  const bool stamping = stamps && blockIdx.x == 0 && (threadIdx.x & 31) == 0;
+  const bool stamping = kStamps && stamps && blockIdx.x == 0 && (threadIdx.x & 31) == 0;
   auto stamp = [&](int i) {
     if (stamping) {
       unsigned long long t;
@@ -126,14 +134,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], 128); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], (int)blockDim.x - 64); }
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_a);
     tc::tma_prefetch_descriptor(&map_w);
   }
   if (warp == 1) {                       // one warp allocates both accumulators' columns
-    tc::tmem_alloc(tmem_slot, 2 * BN);
+    tc::tmem_alloc(tmem_slot, L::kTmemCols);
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
@@ -207,9 +215,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ---- epilogue: thread = one row of the tile, TMEM lanes 32*(warp%4) ..; it works on one
+    // ---- epilogue: a thread takes one row of the tile (TMEM lanes 32*(warp%4) ..) and one
+    // half of its columns (warps 2-5 the first, 6-9 the second); the eight warps work on one
     // accumulator while the next tile's product fills the other
-    const int quad = warp & 3;
+    const int quad = warp & 3, chalf = (warp - 2) >> 2;
+    const int halves = ((int)blockDim.x - 64) >> 7;            // 1: a thread takes a whole row
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(2);
     Tile t = first;
@@ -241,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
       if (ok && EPI == kTcStore) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = chalf * (BN / halves); c0 < (chalf + 1) * (BN / halves); c0 += 32) {
           uint32_t r[32];
           tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
           tc::tmem_load_wait();
@@ -279,7 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int pair = 0; pair < BN / 128; ++pair) {
           const int col0 = (n0 >> 1) + pair * 64;
 #pragma unroll 1
-          for (int c0 = 0; c0 < 64; c0 += 32) {
+          for (int c0 = chalf * (64 / halves); c0 < (chalf + 1) * (64 / halves); c0 += 32) {
             uint32_t g[32], u[32];
             tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + c0), g);
             tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + 64 + c0), u);
@@ -294,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   // gate and up pass through bfloat16 as they do when stored separately
                   const float gg = round_bf16(__uint_as_float(g[j + e]));
                   const float uu = round_bf16(__uint_as_float(u[j + e]));
-                  v[e] = gg / (1.0f + expf(-gg)) * uu;
+                  v[e] = silu_bf16_path(gg) * uu;
                 }
                 if (col0 + c0 + j + 8 <= ep.I) store8(out + j, v);
               }
@@ -305,7 +315,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (ok && EPI == kTcRope) {
         const float* cs = ep.cos_t + (size_t)pos * half;
         const float* sn = ep.sin_t + (size_t)pos * half;
-        for (int hh = 0; hh * hd < BN; ++hh) {
+        // the heads of a tile go to the two warps of a row in turn (a tile of one head is
+        // the first warp's)
+        for (int hh = chalf; hh * hd < BN; hh += halves) {
           const int head = head0 + hh;                   // (the same for the whole warp)
           if (head >= ep.nh + 2 * ep.nkv) break;
           const uint32_t acc_h = lane_acc + (uint32_t)(hh * hd);
@@ -396,7 +408,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tc::tmem_dealloc(tmem_acc, 2 * BN);
+    tc::tmem_dealloc(tmem_acc, L::kTmemCols);
   }
   stamp(5);
 }
@@ -487,6 +499,8 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
 
 // Tuning aid: a device buffer of 6 x 8 timestamps that the next launches fill (see the kernel).
 static unsigned long long* g_tc_stamps = nullptr;
+// Epilogue warps: 0 chooses per launch, 4 or 8 force (for tests that run both).
+static int g_tc_epilogue_warps = 0;
 
 template <int BN, int EPI, typename TC>
 static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N, int K, int lda,
@@ -515,14 +529,36 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   }
   // Persistent CTAs: as many as fit the chip at once (by shared memory and by the 512 columns
   // of tensor memory, of which a CTA holds two accumulators), each walking its share of tiles.
-  int per_sm = (227 * 1024) / smem;
-  if (per_sm > 512 / (2 * BN)) per_sm = 512 / (2 * BN);
-  if (per_sm < 1) per_sm = 1;
+  // Eight epilogue warps where CTAs walk several tiles: a tile's epilogue (a read-modify-write
+  // of the residual stream, a rotation, 128 x 128 SiLUs) then has to keep pace with the next
+  // tile's product, which four warps do not (2048 x 8 tokens at SmolLM2-135M sizes: o-proj
+  // 48 -> 41 us, down-proj 61 -> 53 us).  A launch of a tile or two per CTA is latency from
+  // end to end and gains nothing from the larger block, and with a long K (8192: 432 -> 479
+  // us) the product hides any epilogue and the larger block only costs.
+  static int occ_key[2] = {-1, -1}, occ_val[2] = {1, 1};      // (per instantiation)
+  auto residents = [&](int warps) {
+    const int at = warps == 8;
+    if (occ_key[at] != smem) {
+      int n = 1;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tc_kernel<BN, EPI, TC>,
+                                                        tc_threads(warps), (size_t)smem) !=
+              cudaSuccess || n < 1)
+        n = 1;
+      if (n > 512 / TcSmem<BN>::kTmemCols) n = 512 / TcSmem<BN>::kTmemCols;
+      occ_val[at] = n < 1 ? 1 : n;
+      occ_key[at] = smem;
+    }
+    return occ_val[at];
+  };
+  int epi_warps = g_tc_epilogue_warps;
+  if (epi_warps != 4 && epi_warps != 8)
+    epi_warps = tiles > 2LL * residents(4) * sm_count && K <= 4096 ? 8 : 4;
+  const int per_sm = residents(epi_warps);
   const long long resident = (long long)per_sm * sm_count;
   const dim3 grid((unsigned)(tiles < resident ? tiles : resident));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(tc_threads(epi_warps));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -530,7 +566,7 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  count_variant(BN == 64 ? kVarTc64 : BN == 128 ? kVarTc128 : kVarTc256);
+  count_variant(BN == 64 ? kVarTc64 : BN == 128 ? kVarTc128 : BN == 192 ? kVarTc192 : kVarTc256);
   if (tiles > resident) count_variant(kVarTcSeveralTiles);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, map_a, map_w, ep, M, N, K,
                                      fault, stages, g_tc_stamps, n_n_tiles, (int)tiles);
@@ -546,9 +582,17 @@ static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, 
 
 using namespace cretif;
 
+extern "C" int cretif_set_tc_epilogue_warps(int n) {
+  const int was = g_tc_epilogue_warps;
+  g_tc_epilogue_warps = (n == 4 || n == 8) ? n : 0;
+  return was;
+}
+
+#ifdef CRETIF_STAMPS
 extern "C" void cretif_gemm_tc_stamps(unsigned long long* device_buffer) {
   g_tc_stamps = device_buffer;
 }
+#endif
 
 extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K,
                               int lda, int ldw, int ldc, int accumulate, int bn,
@@ -562,6 +606,10 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
   if (bn == 0) {
     const long long mt = (M + kTcBM - 1) / kTcBM;
     bn = (mt * ((N + 255) / 256) >= 148) ? 256 : (mt * ((N + 127) / 128) >= 148 ? 128 : 64);
+    // A width that is a multiple of 192 but not of 256 (576 = 3 x 192, 960 = 5 x 192) wastes
+    // a quarter of the widest tile's columns; 192-wide tiles waste none and still pull a
+    // sixth less through L2 per flop than 128-wide ones.
+    if (N % 192 == 0 && N % 256 != 0 && mt * (N / 192) >= 148) bn = 192;
   }
   TcEpi ep = {};
   ep.C = C; ep.ldc = ldc; ep.accumulate = accumulate;
@@ -574,6 +622,7 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
   switch (bn) {
     case 64: return CRETIF_TC(64);
     case 128: return CRETIF_TC(128);
+    case 192: return CRETIF_TC(192);
     case 256: return CRETIF_TC(256);
     default: return kBadArgument;
   }
@@ -619,8 +668,12 @@ extern "C" int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q,
   cudaStream_t st = (cudaStream_t)stream;
   // A tile is a whole number of heads.  Small products want many narrow tiles; large ones
   // (two waves of 128-wide tiles and more) do more arithmetic per byte with wide ones.
-  const long long wide_tiles = (long long)((N + 127) / 128) * ((M + kTcBM - 1) / kTcBM);
+  const long long m_tiles = (M + kTcBM - 1) / kTcBM;
+  const long long wide_tiles = (long long)((N + 127) / 128) * m_tiles;
   if (hd == 64 && wide_tiles < 2 * 148)
     return launch_tc<64, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
+  // three heads of 64 per tile where that divides the matrix and 128 does not
+  if (hd == 64 && N % 192 == 0 && N % 128 != 0 && m_tiles * (N / 192) >= 2 * 148)
+    return launch_tc<192, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
   return launch_tc<128, kTcRope, __nv_bfloat16>(A, Wqkv, ep, M, N, K, lda, ldw, fault, st);
 }

@@ -35,19 +35,6 @@ def lib():
         L = load_library()
         L.cretif_uniform01.restype = ctypes.c_float
         L.cretif_uniform01.argtypes = [ctypes.c_ulonglong, ctypes.c_longlong, ctypes.c_int]
-        tune = os.environ.get("CRETIF_STREAM_MIN_K")       # tuning knob, see set_stream_min_k
-        if tune:
-            L.cretif_set_stream_min_k(int(tune), ctypes.c_longlong(
-                int(os.environ.get("CRETIF_STREAM_MIN_BYTES", "-1"))))
-        tune = os.environ.get("CRETIF_STREAM_MAX_ROWS")
-        if tune:
-            L.cretif_set_stream_max_rows(int(tune))
-        tune = os.environ.get("CRETIF_FUSED_CLUSTER")
-        if tune:
-            L.cretif_set_fused_cluster(int(tune))
-        tune = os.environ.get("CRETIF_STREAM_STAGES")
-        if tune:
-            L.cretif_set_stream_stages(int(tune), int(os.environ.get("CRETIF_STREAM_EARLY", "-1")))
         _lib = L
     return _lib
 
@@ -62,7 +49,7 @@ def launch_count() -> int:
 
 _VARIANTS = ("fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4", "stream",
              "stream_row_groups", "decode_cluster", "decode_split", "prefill_attn", "tc64",
-             "tc128", "tc256", "tc_several_tiles")
+             "tc128", "tc256", "tc_several_tiles", "tc192")
 
 
 def variant_counts() -> dict:
@@ -332,6 +319,12 @@ def gemm_tc_supported(x, w, out) -> bool:
     return out.dtype == torch.float32 and out.stride(0) % 4 == 0
 
 
+def set_tc_epilogue_warps(n: int) -> int:
+    """(For tests that run both.)  Epilogue warps of the tensor-core product: 4 or 8; 0 lets
+    each launch choose.  Returns the old setting."""
+    return int(lib().cretif_set_tc_epilogue_warps(int(n)))
+
+
 def gemm_tc(x, w, out, accumulate: bool = False, bn: int = 0) -> None:
     """out[M,N] (+)= x[M,K] · w[N,K]ᵀ with TMA, tcgen05.mma and a TMEM accumulator."""
     _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
@@ -462,7 +455,7 @@ FUSED_MAX_ROWS = 128     # the kernels' limit; the parts choose how far they use
 # the matrix is small (measured at 64 tokens: 0.7 of the tensor-core path's time at
 # SmolLM2-135M sizes, where no matrix but the head exceeds 4 MB, 0.83 at 360M sizes (up to
 # 10 MB), 1.2 at 1.7B sizes (25 to 67 MB)).
-FUSED_GROUPS_MAX_BYTES = int(os.environ.get("CRETIF_FUSED_GROUPS_MAX_BYTES", str(16 << 20)))
+FUSED_GROUPS_MAX_BYTES = 16 << 20
 
 
 def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:
@@ -477,7 +470,7 @@ def fused_supported(M: int, K: int, w, norm: bool = True) -> bool:
 
 
 def set_stream_min_k(k: int, min_bytes: int = -1) -> int:
-    """The fused product streams weights through shared memory for matrices of at least k
+    """(For tests that must run both variants of the fused product on one shape.)  The fused product streams weights through shared memory for matrices of at least k
     columns or (if not negative) at least min_bytes bytes; returns the old column count."""
     return int(lib().cretif_set_stream_min_k(int(k), ctypes.c_longlong(int(min_bytes))))
 
@@ -487,13 +480,6 @@ def stream_min_bytes() -> int:
     fn = lib().cretif_stream_min_bytes
     fn.restype = ctypes.c_longlong
     return int(fn())
-
-
-def set_stream_stages(n: int, early: int = -1) -> int:
-    """Depth of the streaming variant's ring (2..8; 0: chosen per launch) and, if not
-    negative, how many stages of weights it asks for before waiting for the kernel before
-    it; returns the old depth."""
-    return int(lib().cretif_set_stream_stages(int(n), int(early)))
 
 
 def set_fused_cluster(n: int) -> int:

@@ -10,8 +10,6 @@ cache's blocks directly, for whole prompts and for single tokens alike.
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..cache import KVRequest
@@ -26,7 +24,7 @@ _fused_steps = True
 # Steps of at most this many tokens take the fused projection kernels; beyond 32 tokens they
 # run as row groups of one launch (measured on a B200: a 64-token step at SmolLM2-135M sizes
 # takes half the time of the tensor-core products, whose 128-row tiles run on a few CTAs).
-FUSED_MAX_TOKENS = int(os.environ.get("CRETIF_FUSED_MAX_TOKENS", "64"))
+FUSED_MAX_TOKENS = 64
 
 
 def fused_steps_enabled() -> bool:

@@ -89,11 +89,24 @@ def test_gemm_skinny_refuses_unaligned(ops):
         ops.gemv_bf16(x, w, torch.empty(2, 8, device=DEV))
 
 
+@pytest.fixture(params=[4, 8], ids=["4-epilogue-warps", "8-epilogue-warps"])
+def tc_epilogue(request, ops):
+    """The tensor-core product drains an accumulator with four warps (a thread per row) or
+    with eight (two threads per row, half of the columns each); a launch chooses by its size.
+    Tests of that kernel run both ways."""
+    old = ops.set_tc_epilogue_warps(request.param)
+    yield request.param
+    ops.set_tc_epilogue_warps(old)
+
+
 @pytest.mark.parametrize("M,N,K,bn", [(128, 128, 64, 128), (128, 64, 128, 64), (256, 256, 256, 256),
                                       (2048, 960, 576, 0), (300, 200, 72, 0), (129, 65, 136, 64),
                                       (70, 1000, 1544, 128), (1000, 3072, 576, 256),
-                                      (513, 576, 1536, 0)])
-def test_gemm_tc(ops, M, N, K, bn):
+                                      (513, 576, 1536, 0), (300, 576, 72, 192),
+                                      (1000, 960, 576, 192), (130, 200, 136, 192),
+                                      # enough rows that a width of 3 x 192 picks 192 itself
+                                      (19000, 576, 136, 0)])
+def test_gemm_tc(ops, tc_epilogue, M, N, K, bn):
     """The tcgen05 kernel against float64, tails in every dimension."""
     x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
     want = x.double() @ w.double().T
@@ -297,7 +310,7 @@ def _interleave(gate, up, b=64):
 
 @pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 1536, 576), (70, 192, 104), (2048, 256, 96),
                                    (2200, 4288, 72)])     # wide tiles of two gate|up pairs
-def test_gemm_tc_silu(ops, M, I, K):
+def test_gemm_tc_silu(ops, tc_epilogue, M, I, K):
     x = rnd(M, K, dtype=torch.bfloat16)
     gate = rnd(I, K, dtype=torch.bfloat16, seed=1, scale=0.3)
     up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
@@ -321,14 +334,20 @@ def test_gemm_tc_silu(ops, M, I, K):
 
 
 @pytest.mark.parametrize("pairing", [0, 1])
-@pytest.mark.parametrize("nh,nkv,hd,K", [(9, 3, 64, 576), (2, 1, 128, 96), (3, 3, 64, 72),
-                                         # so many heads that a tile takes two of them (and
-                                         # the last tile only one)
-                                         (101, 25, 64, 72)])
-def test_gemm_tc_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd, K):
-    theta, P = 10000.0, 512
+@pytest.mark.parametrize("nh,nkv,hd,K,long", [
+    (9, 3, 64, 576, False), (2, 1, 128, 96, False), (3, 3, 64, 72, False),
+    # so many heads that a tile takes two of them (and the last tile only one)
+    (101, 25, 64, 72, False),
+    # so many tokens that a tile takes three heads (15 heads = 5 tiles of 192 columns)
+    (9, 3, 64, 72, True)])
+def test_gemm_tc_qkv_rope_equals_the_separate_kernels(ops, tc_epilogue, pairing, nh, nkv, hd, K,
+                                                      long):
+    theta, P = 10000.0, 4096 if long else 512
     lens = [200, 70, 333]
     news = [200, 70, 150]                     # the third sequence continues at 183
+    if long:
+        lens, news = [4000, 70, 3900], [4000, 70, 3800]
+    before_192 = ops.variant_counts()["tc192"]
     j = torch.arange(hd // 2, dtype=torch.float64)
     ang = torch.arange(P, dtype=torch.float64)[:, None] / theta ** (2 * j / hd)[None, :]
     cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
@@ -353,6 +372,7 @@ def test_gemm_tc_qkv_rope_equals_the_separate_kernels(ops, pairing, nh, nkv, hd,
                          cb.table, cb.k, cb.v, 64, True)
     torch.cuda.synchronize()
     assert fault.item() == 0
+    assert (ops.variant_counts()["tc192"] > before_192) == long
     close(q, qkv[:, :nh * hd], 1e-2)
     close(cb.k, ca.k, 1e-2)
     close(cb.v, ca.v, 1e-2)

@@ -70,6 +70,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// The largest of three (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t lbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((tc::smem_u32(tile) & 0x3FFFFu) >> 4);
@@ -276,9 +283,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           uint32_t r[32];
           tc::tmem_load_32(lane_addr + kColO + (uint32_t)(jj & 1) * 128 + obase + c0, r);
           tc::tmem_load_wait();
+          const float2 a2 = make_float2(a, a);
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c0 + e < HDMAX / 2) o[c0 + e] = fmaf(o[c0 + e], a, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; e += 2)
+            if (c0 + e < HDMAX / 2) {
+              const float2 v = __ffma2_rn(make_float2(o[c0 + e], o[c0 + e + 1]), a2,
+                                          make_float2(__uint_as_float(r[e]),
+                                                      __uint_as_float(r[e + 1])));
+              o[c0 + e] = v.x;
+              o[c0 + e + 1] = v.y;
+            }
         }
       }
       tc::tc_fence_before();
@@ -313,9 +327,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]);
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // (three-input maxima and two-wide float operations halve the instructions of the
+      // loops below: what bounds a step is how many instructions its eight warps can issue)
+      float mx4[4] = {t[0], t[1], t[2], t[3]};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], t[c]);
+      for (int c = 4; c < 60; c += 8) {
+        mx4[0] = max3(mx4[0], t[c], t[c + 1]);
+        mx4[1] = max3(mx4[1], t[c + 2], t[c + 3]);
+        mx4[2] = max3(mx4[2], t[c + 4], t[c + 5]);
+        mx4[3] = max3(mx4[3], t[c + 6], t[c + 7]);
+      }
+      mx4[0] = max3(mx4[0], t[60], t[61]);
+      mx4[1] = max3(mx4[1], t[62], t[63]);
       // the scale is positive, so the largest raw score is the largest scaled one
       const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       float* xb = xch + (j & 1) * 256;        // double-buffered: one barrier per step
@@ -327,16 +350,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // p = 2^(s * scale - m); a masked score (-inf) gives 0, and a row with nothing to see
       // yet (m_new = -inf) uses 0 as its reference so that no inf - inf appears
       const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 sum4[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       uint32_t packed[32];
+      const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg_m, neg_m);
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = fast_exp2(fmaf(t[c], scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(t[c + 1], scale_log2, neg_m));
-        sum4[(c >> 1) & 3] += p0 + p1;
-        packed[c >> 1] = pack2(p0, p1);
+        const float2 x = __ffma2_rn(make_float2(t[c], t[c + 1]), scale2, neg2);
+        const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        sum4[(c >> 1) & 3] = __fadd2_rn(sum4[(c >> 1) & 3], pp);
+        packed[c >> 1] = pack2(pp.x, pp.y);
       }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      const float2 s01 = __fadd2_rn(sum4[0], sum4[1]), s23 = __fadd2_rn(sum4[2], sum4[3]);
+      const float2 s = __fadd2_rn(s01, s23);
+      l = l * alpha + (s.x + s.y);
       m = m_new;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {        // 16-byte chunks, swizzled by the row

@@ -88,7 +88,7 @@ __device__ __forceinline__ float round_bf16(float x) {
 }
 
 template <int BN, int EPI, typename TC>
-__global__ void __launch_bounds__(kTcMaxThreads, BN <= 128 ? 2 : 1)   // narrow tiles: two CTAs an SM
+__global__ void __launch_bounds__(kTcMaxThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
                int kTcStages, unsigned long long* stamps, int n_n_tiles, int n_tiles) {

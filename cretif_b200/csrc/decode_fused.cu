@@ -89,7 +89,11 @@ static int dispatch_registers(const FusedParams& p, int tiles, cudaStream_t st) 
   if (p.M <= 8) return launch_fused<1, PRO, EPI>(p, tiles, st);
   if (p.M <= 16) return launch_fused<2, PRO, EPI>(p, tiles, st);
   if (p.M <= kFuMaxGroupRows) return launch_fused<4, PRO, EPI>(p, tiles, st);
-  // more tokens: even groups of up to 32 rows, a multiple of 8 each
+  // More tokens: even groups of up to 32 rows, a multiple of 8 each.  (One group of 64 rows
+  // — eight token tiles per warp and k-chunk, the weights read once — was measured at
+  // SmolLM2-135M sizes and lost: q|k|v 5.6 -> 8.1 us, gate|up 8.0 -> 9.7 us at 64 tokens; a
+  // CTA's share of the arithmetic, not the second read of the weights from L2, is what a
+  // group costs.)
   const int groups = (p.M + kFuMaxGroupRows - 1) / kFuMaxGroupRows;
   const int group_rows = (((p.M + groups - 1) / groups) + 7) & ~7;
   return launch_fused<4, PRO, EPI>(p, tiles, st, groups, group_rows);

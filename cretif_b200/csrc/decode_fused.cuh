@@ -142,18 +142,24 @@ __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
 // What a tile's epilogue reads from memory besides the accumulator — the token's position,
 // its cache block and rotation, or the value it adds to — does not depend on the product.
 // It is asked for before the product runs, so that the epilogue does not wait for it.
+// (A tile has 16 weight rows and up to 8 NT tokens: the plain epilogue makes ceil(NT / 2)
+// passes of the block's 256 threads over its 128 NT outputs, the pair epilogues ceil(NT / 4)
+// over its 64 NT pairs.)
+template <int NT>
 struct EpiAhead {
-  float old[2];        // plain, accumulate: the values to add to (two passes of 256 threads)
-  int pos, blk;        // rope
-  float cs, sn;
+  static constexpr int kPlainPasses = NT >= 2 ? NT / 2 : 1;
+  static constexpr int kPairPasses = NT >= 4 ? NT / 4 : 1;
+  float old[kPlainPasses];        // plain, accumulate: the values to add to
+  int pos[kPairPasses], blk[kPairPasses];        // rope
+  float cs[kPairPasses], sn[kPairPasses];
 };
 
-template <int EPI>
-__device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, EpiAhead& a) {
+template <int NT, int EPI>
+__device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, EpiAhead<NT>& a) {
   if (EPI == kEpiPlain) {
     if (p.c_dt == kF32 && p.accumulate) {
 #pragma unroll
-      for (int it = 0; it < 2; ++it) {
+      for (int it = 0; it < EpiAhead<NT>::kPlainPasses; ++it) {
         const int i = threadIdx.x + it * kFuWarps * 32;
         const int m = i / kFuRows, n = tile * kFuRows + (i - m * kFuRows);
         a.old[it] = (m < p.M && n < p.N)
@@ -162,19 +168,23 @@ __device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, Epi
       }
     }
   } else if (EPI == kEpiRope) {
-    const int i = threadIdx.x;
-    a.pos = 0; a.blk = -1; a.cs = 1.f; a.sn = 0.f;
-    if (i < 8 * p.M) {
-      const int m = i >> 3, pr = i & 7;
-      const int tiles_per_head = p.hd >> 4;
-      const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
-      a.pos = p.tok_pos[m];
-      if (head >= p.nh && p.write_cache)
-        a.blk = p.table[(size_t)p.seq_slot[p.tok_seq[m]] * p.table_stride + (a.pos >> p.bt_shift)];
-      if (head < p.nh + p.nkv) {
-        const int j = t * 8 + pr;
-        a.cs = p.cos_t[(size_t)a.pos * (p.hd >> 1) + j];
-        a.sn = p.sin_t[(size_t)a.pos * (p.hd >> 1) + j];
+#pragma unroll
+    for (int it = 0; it < EpiAhead<NT>::kPairPasses; ++it) {
+      const int i = threadIdx.x + it * kFuWarps * 32;
+      a.pos[it] = 0; a.blk[it] = -1; a.cs[it] = 1.f; a.sn[it] = 0.f;
+      if (i < 8 * p.M) {
+        const int m = i >> 3, pr = i & 7;
+        const int tiles_per_head = p.hd >> 4;
+        const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
+        a.pos[it] = p.tok_pos[m];
+        if (head >= p.nh && p.write_cache)
+          a.blk[it] = p.table[(size_t)p.seq_slot[p.tok_seq[m]] * p.table_stride +
+                              (a.pos[it] >> p.bt_shift)];
+        if (head < p.nh + p.nkv) {
+          const int j = t * 8 + pr;
+          a.cs[it] = p.cos_t[(size_t)a.pos[it] * (p.hd >> 1) + j];
+          a.sn[it] = p.sin_t[(size_t)a.pos[it] * (p.hd >> 1) + j];
+        }
       }
     }
   }
@@ -183,10 +193,10 @@ __device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, Epi
 template <int NT, int EPI>
 __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
                                             float (*red)[kFuRows][8 * NT + 1],
-                                            const EpiAhead& ahead) {
+                                            const EpiAhead<NT>& ahead) {
   if (EPI == kEpiPlain) {
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {         // 16 rows x up to 32 tokens = two passes at most
+    for (int it = 0; it < EpiAhead<NT>::kPlainPasses; ++it) {
       const int i = threadIdx.x + it * kFuWarps * 32;
       if (i >= kFuRows * p.M) break;
       const int m = i / kFuRows, rr = i - m * kFuRows;
@@ -205,7 +215,10 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
     }
   } else {
     // one thread per (token, pair): rows pr and pr + 8 of the tile
-    for (int i = threadIdx.x; i < 8 * p.M; i += kFuWarps * 32) {
+#pragma unroll
+    for (int it = 0; it < EpiAhead<NT>::kPairPasses; ++it) {
+      const int i = threadIdx.x + it * kFuWarps * 32;
+      if (i >= 8 * p.M) break;
       const int m = i >> 3, pr = i & 7;
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -220,11 +233,11 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
       } else {
         const int tiles_per_head = p.hd >> 4;
         const int head = fast_div(p.tph_div, tile), t = tile - head * tiles_per_head;
-        const int pos = ahead.pos;
+        const int pos = ahead.pos[it];
         size_t cache_row = 0;
         bool cache_ok = false;
         if (head >= p.nh && p.write_cache) {
-          const int blk = ahead.blk;
+          const int blk = ahead.blk[it];
           if (blk < 0) atomicOr(p.fault, kFaultBlockTable);
           else {
             cache_ok = true;
@@ -244,7 +257,7 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
         // the unfused path stores q and k as bfloat16 before rotating them
         const float x0 = __bfloat162float(__float2bfloat16_rn(s0));
         const float x1 = __bfloat162float(__float2bfloat16_rn(s1));
-        const float cs = ahead.cs, sn = ahead.sn;
+        const float cs = ahead.cs[it], sn = ahead.sn[it];
         const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
         const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
         if (head < p.nh) {
@@ -514,10 +527,10 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   // Positions, the block table and the rotation table are not the work of the kernel before
   // this one either: the first tile's epilogue operands are on their way before the wait
   // (a chain of four dependent loads that the short product would not hide).
-  EpiAhead ahead;
+  EpiAhead<NT> ahead;
   bool have_ahead = false;
   if (EPI == kEpiRope) {
-    epi_prefetch<EPI>(p, tile, ahead);
+    epi_prefetch<NT, EPI>(p, tile, ahead);
     have_ahead = true;
   }
   if (pdl) {
@@ -538,7 +551,7 @@ __device__ __forceinline__ void skinny_fused_tiles(const FusedParams& p, int n_t
   }
 
   for (; tile < n_tiles; tile += tile_stride) {
-    if (!have_ahead) epi_prefetch<EPI>(p, tile, ahead);
+    if (!have_ahead) epi_prefetch<NT, EPI>(p, tile, ahead);
     have_ahead = false;
     float acc[NT][4];
 #pragma unroll

@@ -165,10 +165,10 @@ skinny_stream_kernel(const FusedParams whole, const __grid_constant__ CUtensorMa
     const int r = lane >> 2, c = lane & 3;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     // the first tile's rotary operands (positions, block table, angles) do not wait either
-    EpiAhead ahead;
+    EpiAhead<NT> ahead;
     bool have_ahead = false;
     if (EPI == kEpiRope && (int)blockIdx.x < n_tiles) {
-      epi_prefetch<EPI>(p, blockIdx.x, ahead);
+      epi_prefetch<NT, EPI>(p, blockIdx.x, ahead);
       have_ahead = true;
     }
     if (PRO == kProNorm) {
@@ -241,7 +241,7 @@ skinny_stream_kernel(const FusedParams whole, const __grid_constant__ CUtensorMa
     }
     int s = 0, turn = 0;                         // the ring's stage and how often it has turned
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      if (!have_ahead) epi_prefetch<EPI>(p, tile, ahead);
+      if (!have_ahead) epi_prefetch<NT, EPI>(p, tile, ahead);
       have_ahead = false;
       // where this lane's two weight rows (tile rows r and r + 8) lie within a stage
       int off_a = r * kStRowB, off_b = kStBoxes * kStGroup + r * kStRowB;

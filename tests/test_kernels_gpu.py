@@ -160,7 +160,8 @@ def _norm_bf16(h, w, eps, rows=None):
                                    (17, 96, 72), (32, 130, 576), (8, 200, 2048), (3, 64, 1544),
                                    (16, 48, 8192), (13, 77, 3000),
                                    # more than 32 rows: groups of rows in one launch
-                                   (40, 130, 576), (64, 96, 104), (100, 50, 200)])
+                                   (33, 130, 576), (40, 130, 576), (57, 100, 960), (64, 96, 104),
+                                   (100, 50, 200), (128, 96, 136)])
 def test_fused_norm_linear_and_add(ops, fused_variant, M, N, K):
     eps = 1e-5
     h, nw = rnd(M + 3, K), rnd(K, seed=1) * 0.1 + 1
@@ -185,7 +186,7 @@ def test_fused_norm_linear_and_add(ops, fused_variant, M, N, K):
 
 @pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 1536, 576), (7, 173, 104), (20, 256, 96),
                                    (8, 512, 2048), (12, 72, 1032), (50, 256, 96),
-                                   (64, 1536, 576)])
+                                   (64, 1536, 576), (33, 1536, 576), (90, 200, 104)])
 def test_fused_gate_up_silu_equals_the_separate_kernels(ops, fused_variant, M, I, K):
     eps = 1e-6
     h, nw = rnd(M, K), rnd(K, seed=1) * 0.1 + 1
@@ -206,7 +207,7 @@ def test_fused_gate_up_silu_equals_the_separate_kernels(ops, fused_variant, M, I
 
 
 @pytest.mark.parametrize("pairing", [0, 1])
-@pytest.mark.parametrize("many", [False, True], ids=["6tokens", "45tokens"])
+@pytest.mark.parametrize("many", [0, 45, 110], ids=["6tokens", "45tokens", "110tokens"])
 @pytest.mark.parametrize("nh,nkv,hd,K", [(4, 2, 16, 64), (9, 3, 64, 576), (3, 1, 32, 96),
                                          (5, 5, 48, 104), (4, 4, 64, 2048)])
 def test_fused_qkv_rope_equals_the_separate_kernels(ops, fused_variant, pairing, many, nh, nkv,
@@ -216,9 +217,12 @@ def test_fused_qkv_rope_equals_the_separate_kernels(ops, fused_variant, pairing,
     j = torch.arange(hd // 2, dtype=torch.float64)
     ang = torch.arange(P, dtype=torch.float64)[:, None] / theta ** (2 * j / hd)[None, :]
     cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
-    if many:          # more than 32 tokens: groups of rows in one launch
+    if many == 45:    # 33 to 64 tokens: two groups of rows in one launch
         qpos = list(range(10, 25)) + list(range(50, 65)) + list(range(115, 130))
         qseq = [0] * 15 + [1] * 15 + [2] * 15
+    elif many:        # more than 64 tokens: four groups
+        qpos = list(range(5, 25)) + list(range(30, 70)) + list(range(80, 130))
+        qseq = [0] * 20 + [1] * 40 + [2] * 50
     else:
         qpos = [4, 3, 64, 69, 129, 0]
         qseq = [0, 0, 1, 1, 2, 2]

@@ -387,6 +387,8 @@ def main() -> int:
                          "for instance under a profiler)")
     ap.add_argument("--size", default="135m", choices=sorted(SIZES),
                     help="layer sizes: SmolLM2-135M (the headline), 360M or 1.7B")
+    ap.add_argument("--no-shares", action="store_true",
+                    help="skip the per-kernel shares of the decode step")
     ap.add_argument("--unequal", action="store_true",
                     help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
     args = ap.parse_args()
@@ -449,9 +451,10 @@ def main() -> int:
         return 0
 
     with ClockSampler() as clocks:
-        ms, mean_ctx, per_step, shares = run_decode(engine, args.batch, steps, args.warmup,
-                                                    PROMPT_LEN, unequal=args.unequal,
-                                                    shares=True)
+        out = run_decode(engine, args.batch, steps, args.warmup, PROMPT_LEN,
+                         unequal=args.unequal, shares=not args.no_shares)
+    ms, mean_ctx, per_step = out[:3]
+    shares = out[3] if len(out) > 3 else None
     value = args.batch / (ms * 1e-3)
     if args.only == "decode":
         print(json.dumps({"only": "decode", "batch": args.batch, "value": value,
@@ -459,6 +462,8 @@ def main() -> int:
                           "shares": shares}))
         return 0
 
+    rest = ClockSampler()
+    rest.__enter__()           # the clocks under everything below, which runs much hotter
     prefill = prefill_record(1)
     points, fracs, more = {}, {}, {}
     if points_on:
@@ -479,6 +484,7 @@ def main() -> int:
             more[f"prefill_b{b}"] = prefill_record(b, repeats=3, warmup=2)
 
     e2e = run_e2e(engine, args.batch, min(steps, 512), PROMPT_LEN)
+    rest.__exit__(None, None, None)
 
     achieved = step_bytes(args.batch, mean_ctx) / (ms * 1e-3) / 1e9
     line = {
@@ -511,6 +517,7 @@ def main() -> int:
         "gpu_launches": per_step * steps,
         "launches_per_step": per_step,
         "clocks": clocks.result,
+        "clocks_other_points": rest.result,
     }
     print(json.dumps(line))
     return 0

@@ -31,9 +31,8 @@ namespace cretif {
 
 constexpr int kTcBM = 128, kTcBK = 64;
 // Producer warp, MMA warp, and four or eight epilogue warps (one or two per quadrant of
-// tensor-memory lanes), chosen per launch by the block size.
-constexpr int kTcMaxThreads = (2 + 8) * 32;
-inline int tc_threads(int epilogue_warps) { return (2 + epilogue_warps) * 32; }
+// tensor-memory lanes): a template parameter, chosen per launch.
+constexpr int tc_threads(int epilogue_warps) { return (2 + epilogue_warps) * 32; }
 
 // The depth of the ring is chosen per launch.  With more tiles than SMs, narrow tiles take
 // three stages so that two (BN = 128) or three (BN = 64) CTAs share an SM and hide each
@@ -87,8 +86,8 @@ __device__ __forceinline__ float round_bf16(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
 
-template <int BN, int EPI, typename TC>
-__global__ void __launch_bounds__(kTcMaxThreads)
+template <int BN, int EPI, typename TC, int EW>
+__global__ void __launch_bounds__(tc_threads(EW))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
                int kTcStages, unsigned long long* stamps, int n_n_tiles, int n_tiles) {
@@ -134,7 +133,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], (int)blockDim.x - 64); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&acc_full[b], 1); tc::mbar_init(&acc_empty[b], EW * 32); }
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_a);
@@ -219,7 +218,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // half of its columns (warps 2-5 the first, 6-9 the second); the eight warps work on one
     // accumulator while the next tile's product fills the other
     const int quad = warp & 3, chalf = (warp - 2) >> 2;
-    const int halves = ((int)blockDim.x - 64) >> 7;            // 1: a thread takes a whole row
+    constexpr int halves = EW / 4;                             // 1: a thread takes a whole row
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(2);
     Tile t = first;
@@ -502,6 +501,35 @@ static unsigned long long* g_tc_stamps = nullptr;
 // Epilogue warps: 0 chooses per launch, 4 or 8 force (for tests that run both).
 static int g_tc_epilogue_warps = 0;
 
+// Registers of a thread of the kernel, for the residency estimate (once per instantiation).
+template <int BN, int EPI, typename TC, int EW>
+static int tc_regs_per_thread() {
+  static int regs = 0;
+  if (!regs) {
+    cudaFuncAttributes fa;
+    regs = cudaFuncGetAttributes(&fa, gemm_tc_kernel<BN, EPI, TC, EW>) == cudaSuccess &&
+                   fa.numRegs > 0 ? fa.numRegs : 128;
+  }
+  return regs;
+}
+
+template <int BN, int EPI, typename TC, int EW>
+static cudaError_t launch_tc_kernel(const cudaLaunchConfig_t& cfg, int smem,
+                                    const CUtensorMap& map_a, const CUtensorMap& map_w,
+                                    const TcEpi& ep, int M, int N, int K, unsigned int* fault,
+                                    int stages, unsigned long long* stamps, int n_n_tiles,
+                                    int tiles) {
+  static int configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC, EW>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC, EW>, map_a, map_w, ep, M, N, K, fault,
+                            stages, stamps, n_n_tiles, tiles);
+}
+
 template <int BN, int EPI, typename TC>
 static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N, int K, int lda,
                      int ldw, unsigned int* fault, cudaStream_t st) {
@@ -520,13 +548,6 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   if (tiles > 0x7fffffffLL) return kBadArgument;
   const int stages = TcSmem<BN>::stages_for(tiles, (K + kTcBK - 1) / kTcBK, sm_count);
   const int smem = TcSmem<BN>::total(stages);
-  static int configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
   // Persistent CTAs: as many as fit the chip at once (by shared memory and by the 512 columns
   // of tensor memory, of which a CTA holds two accumulators), each walking its share of tiles.
   // Eight epilogue warps where CTAs walk several tiles: a tile's epilogue (a read-modify-write
@@ -535,20 +556,17 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   // 48 -> 41 us, down-proj 61 -> 53 us).  A launch of a tile or two per CTA is latency from
   // end to end and gains nothing from the larger block, and with a long K (8192: 432 -> 479
   // us) the product hides any epilogue and the larger block only costs.
-  static int occ_key[2] = {-1, -1}, occ_val[2] = {1, 1};      // (per instantiation)
+  // CTAs that fit an SM at once: by shared memory, by the 512 columns of tensor memory and by
+  // the register file (registers are handed out per warp in units of 256).
   auto residents = [&](int warps) {
-    const int at = warps == 8;
-    if (occ_key[at] != smem) {
-      int n = 1;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tc_kernel<BN, EPI, TC>,
-                                                        tc_threads(warps), (size_t)smem) !=
-              cudaSuccess || n < 1)
-        n = 1;
-      if (n > 512 / TcSmem<BN>::kTmemCols) n = 512 / TcSmem<BN>::kTmemCols;
-      occ_val[at] = n < 1 ? 1 : n;
-      occ_key[at] = smem;
-    }
-    return occ_val[at];
+    const int regs_per_thread = warps == 8 ? tc_regs_per_thread<BN, EPI, TC, 8>()
+                                           : tc_regs_per_thread<BN, EPI, TC, 4>();
+    int n = (227 * 1024) / smem;
+    if (n > 512 / TcSmem<BN>::kTmemCols) n = 512 / TcSmem<BN>::kTmemCols;
+    const int regs_per_warp = (regs_per_thread * 32 + 255) / 256 * 256;
+    const int by_regs = 65536 / ((2 + warps) * regs_per_warp);
+    if (n > by_regs) n = by_regs;
+    return n < 1 ? 1 : n;
   };
   int epi_warps = g_tc_epilogue_warps;
   if (epi_warps != 4 && epi_warps != 8)
@@ -568,8 +586,11 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   cfg.numAttrs = 1;
   count_variant(BN == 64 ? kVarTc64 : BN == 128 ? kVarTc128 : BN == 192 ? kVarTc192 : kVarTc256);
   if (tiles > resident) count_variant(kVarTcSeveralTiles);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, map_a, map_w, ep, M, N, K,
-                                     fault, stages, g_tc_stamps, n_n_tiles, (int)tiles);
+  const cudaError_t e =
+      epi_warps == 8 ? launch_tc_kernel<BN, EPI, TC, 8>(cfg, smem, map_a, map_w, ep, M, N, K, fault,
+                                                        stages, g_tc_stamps, n_n_tiles, (int)tiles)
+                     : launch_tc_kernel<BN, EPI, TC, 4>(cfg, smem, map_a, map_w, ep, M, N, K, fault,
+                                                        stages, g_tc_stamps, n_n_tiles, (int)tiles);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 

@@ -145,6 +145,11 @@ int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, 
 int cretif_wait_that_expires(unsigned int limit, unsigned int* fault, unsigned int* polls,
                              void* stream);
 
+// (For tests that run both.)  Two query tiles per CTA in cretif_attn_prefill_tc: -1 where the
+// launcher sees fit (default), 0 never, 1 wherever the kernel takes the shape.  Returns the old
+// setting.
+int cretif_set_prefill_pairing(int mode);
+
 // How often variant v of a kernel (cretif::Variant in common.cuh) has been launched; -1 for an
 // unknown v.  For tests that must know which path ran.
 int cretif_variant_count(int v);

@@ -411,12 +411,355 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Two query tiles per CTA.
+//
+// In the kernel above the two softmax warps of an SM sub-partition share the same rows and
+// meet at a barrier every step, so all eight warps pass through the step's phases together
+// and the special-function unit (two warps x 64 ex2 x 8 cycles of a 1,280 ns step) idles for
+// more than half of it.  Here a CTA owns TWO tiles of 128 queries that read the same key/value
+// head — two query heads of a group, or consecutive query tiles — and a softmax thread owns a
+// whole row of one of them (128 scores a step, the 64 output columns): no partner, no
+// barrier, and the tiles' warps (2-5 and 6-9, one of each on every sub-partition) run out of
+// phase with each other, one exponentiating while the other waits for its products.  The
+// keys and values of a step are loaded once for both tiles.
+//   tensor memory: S_a, S_b (128 columns each), O_blk of each tile twice (4 x 64);
+//   shared memory: Q_a, Q_b, P_a, P_b, three stages of K/V (128 keys).
+// A thread reads its scores twice (the maximum first, then the exponentials), which keeps
+// 32 of them in registers at a time.  Head sizes up to 64, no sliding window; the launcher
+// falls back to the kernel above otherwise, and for grids too small to fill the chip with
+// half as many CTAs.
+constexpr int kPpStages = 3;
+
+struct PpSmem {
+  int q, p, k, v, bars, total;
+  __host__ __device__ PpSmem() {
+    q = 0;                                   // [2][128 rows][128 B]
+    p = q + 2 * kPfBQ * 128;                 // [2 tiles][2 k-blocks][128 rows][128 B]
+    k = p + 2 * (kPfBK / 64) * kPfBQ * 128;
+    v = k + kPpStages * kPfBK * 128;
+    bars = v + kPpStages * kPfBK * 128;
+    total = bars + (2 * kPpStages + 12) * 8 + 32 + 1024;
+  }
+};
+
+__global__ void __launch_bounds__(kPfThreads, 1)
+attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
+                         const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                         int ldo, const int* __restrict__ table, int table_stride,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
+                         const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
+                         unsigned int* __restrict__ fault) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const PpSmem L;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* kv_empty = kv_full + kPpStages;
+  uint64_t* q_full = kv_empty + kPpStages;
+  uint64_t* s_full = q_full + 1;            // [tile]
+  uint64_t* p_full = s_full + 2;            // [tile]
+  uint64_t* o_full = p_full + 2;            // [tile][buffer]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 4);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.x, b = blockIdx.y;
+  const int group = nh / nkv;
+  const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
+  const int n_qt = (n_new + kPfBQ - 1) / kPfBQ;
+  const int n_items = n_qt * group;          // (query tile, head of the group), tile-major
+  // heavy pairs (late query tiles) of all sequences and key/value heads first
+  const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
+  if (2 * pair >= n_items) return;
+  const int start = seq_start[b];
+  const int* tab = table + (size_t)seq_slot[b] * table_stride;
+  // the CTA's one or two items
+  int it_q0[2], it_head[2], it_rows[2], it_steps[2];
+  const int n_mine = 2 * pair + 1 < n_items ? 2 : 1;
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int idx = 2 * pair + (x < n_mine ? x : 0);
+    const int t = idx / group;
+    it_q0[x] = t * kPfBQ;
+    it_head[x] = kvh * group + (idx - t * group);
+    it_rows[x] = min(kPfBQ, n_new - it_q0[x]);
+    const int pos_last = start + it_q0[x] + it_rows[x] - 1;
+    it_steps[x] = x < n_mine ? pos_last / kPfBlk / 2 + 1 : 0;    // steps of two cache blocks
+  }
+  const int n_steps = max(it_steps[0], it_steps[1]);
+  const int blk_hi = 2 * n_steps - 1;        // (blocks past a sequence's end are clamped below)
+  const int blk_last = (start + n_new - 1) / kPfBlk;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;          // S: + 128 tile; O: + 128 tile + 64 buffer
+  constexpr int kPBytes = (kPfBK / 64) * kPfBQ * 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPpStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
+    tc::mbar_init(q_full, 1);
+    for (int x = 0; x < 2; ++x) {
+      tc::mbar_init(&s_full[x], 1);
+      tc::mbar_init(&p_full[x], 128);
+      tc::mbar_init(&o_full[2 * x], 1);
+      tc::mbar_init(&o_full[2 * x + 1], 1);
+    }
+    *abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_descriptor(&map_q);
+    tc::tma_prefetch_descriptor(&map_k);
+    tc::tma_prefetch_descriptor(&map_v);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::mbar_expect_tx(q_full, (uint32_t)(n_mine * kPfBQ * 128));
+      for (int x = 0; x < n_mine; ++x)
+        tc::tma_load_2d(smem + L.q + x * kPfBQ * 128, &map_q, it_head[x] * hd, tok0 + it_q0[x],
+                        q_full);
+      for (int j = 0, s = 0, turn = 0; j < n_steps; ++j, s = s + 1 == kPpStages ? 0 : s + 1,
+               turn += s == 0) {
+        if (turn > 0 && !tc::mbar_wait(&kv_empty[s], (uint32_t)((turn - 1) & 1), abort)) break;
+        tc::mbar_expect_tx(&kv_full[s], (uint32_t)(2 * kPfBK * 128));
+        for (int half = 0; half < 2; ++half) {
+          // a block past the sequence's last loads that one again: its keys are masked
+          const int blk = tab[min(min(2 * j + half, blk_hi), blk_last)];
+          if (blk < 0) atomicOr(fault, kFaultBlockTable);
+          const int row = (max(blk, 0) * nkv + kvh) * kPfBlk;
+          const int off = s * kPfBK * 128 + half * kPfBlk * 128;
+          tc::tma_load_2d(smem + L.k + off, &map_k, 0, row, &kv_full[s]);
+          tc::tma_load_2d(smem + L.v + off, &map_v, 0, row, &kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK);
+      const uint32_t idesc_pv = tc::instr_desc_bf16(kPfBQ, hd) | (1u << 16);   // B is MN-major
+      const int k_steps = hd >> 4;
+      int ready = -1;                       // highest step whose keys and values have landed
+      bool ok = tc::mbar_wait(q_full, 0u, abort);
+      auto landed = [&](int j) {            // wait (once) for the stage of step j
+        while (ok && ready < j) {
+          ++ready;
+          ok = tc::mbar_wait(&kv_full[ready % kPpStages], (uint32_t)((ready / kPpStages) & 1), abort);
+        }
+        tc::tc_fence_after();
+        return ok;
+      };
+      auto scores = [&](int x, int j) {     // S_x = Q_x K_j^T
+        const int s = j % kPpStages;
+        for (int kk = 0; kk < k_steps; ++kk) {
+          const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + x * kPfBQ * 128) + 2 * kk;
+          const uint64_t kd = tc::smem_desc_k_sw128(smem + L.k + s * kPfBK * 128) + 2 * kk;
+          tc::umma_bf16(tmem + kColS + (uint32_t)x * kPfBK, qd, kd, idesc_qk, kk != 0);
+        }
+        tc::umma_commit(&s_full[x]);
+      };
+      // Both tiles' scores of a step are issued as early as their S tiles are free, so that the
+      // two tiles' threads work side by side.  (Taking strict turns — one tile exponentiating
+      // while the other folds and waits — was measured: 142 against 98 us at 8 x 2,048 tokens.
+      // A tile's step is a chain of latencies, not of special-function throughput, and two
+      // chains side by side hide more of each other than two in a row.)
+      auto product = [&](int x, int j) {     // O_blk_x = P_x V_j, once P_x of step j is there
+        ok = tc::mbar_wait(&p_full[x], (uint32_t)(j & 1), abort);
+        if (!ok) return;
+        tc::tc_fence_after();
+        const int s = j % kPpStages;
+        const uint64_t vd = smem_desc_mn_sw128(smem + L.v + s * kPfBK * 128,
+                                               (uint32_t)(kPfBK * 128));
+#pragma unroll
+        for (int kk = 0; kk < kPfBK / 16; ++kk) {
+          const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p + x * kPBytes +
+                                                    (kk >> 2) * kPfBQ * 128) + 2 * (kk & 3);
+          tc::umma_bf16(tmem + kColO + (uint32_t)(x * 128 + (j & 1) * 64), pd,
+                        vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
+        }
+        tc::umma_commit(&o_full[2 * x + (j & 1)]);
+      };
+      if (ok && n_steps > 0 && landed(0))
+        for (int x = 0; x < n_mine; ++x) scores(x, 0);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        for (int x = 0; x < n_mine && ok; ++x) {
+          if (j >= it_steps[x]) continue;
+          product(x, j);                     // (S_x has been read for the last time by then)
+          if (ok && j + 1 < it_steps[x] && landed(j + 1)) scores(x, j + 1);
+        }
+        if (ok) tc::umma_commit(&kv_empty[j % kPpStages]);   // all products on this stage issued
+      }
+    }
+  } else {
+    // ---- softmax: warps 2-5 tile 0, warps 6-9 tile 1; a thread owns one row
+    const int x = (warp - 2) >> 2, quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int steps = it_steps[x];
+    const int q_pos = start + it_q0[x] + row;
+    const int pos_first = start + it_q0[x];
+    const bool row_valid = x < n_mine && row < it_rows[x];
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + kColS + (uint32_t)x * kPfBK;
+    float o[64];
+#pragma unroll
+    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    unsigned char* prow = smem + L.p + x * kPBytes + row * 128;
+    bool ok = true;
+    auto fold = [&](int jj, float a) {       // o = o * a + (P V of step jj)
+      ok = tc::mbar_wait(&o_full[2 * x + (jj & 1)], (uint32_t)((jj >> 1) & 1), abort) && ok;
+      tc::tc_fence_after();
+      const float2 a2 = make_float2(a, a);
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        if (c0 < hd) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_addr + kColO + (uint32_t)(x * 128 + (jj & 1) * 64 + c0), r);
+          tc::tmem_load_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 v = __ffma2_rn(make_float2(o[c0 + e], o[c0 + e + 1]), a2,
+                                        make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])));
+            o[c0 + e] = v.x;
+            o[c0 + e + 1] = v.y;
+          }
+        }
+      }
+      tc::tc_fence_before();
+    };
+    float alpha_before = 0.f;
+    for (int j = 0; j < steps; ++j) {
+      ok = tc::mbar_wait(&s_full[x], (uint32_t)(j & 1), abort) && ok;
+      tc::tc_fence_after();
+      const int key0 = 2 * j * kPfBlk;
+      const bool masked = key0 + kPfBK - 1 > pos_first;     // the step reaches the diagonal
+      // One pass over the scores: p = 2^(s * scale - ref) with `ref` the reference the row
+      // already has, the step's maximum found on the way.  As long as no score exceeds the
+      // reference by more than 2^8 the reference stays (p <= 256 is harmless in bfloat16 and
+      // in the 32-bit sums, and the output needs no rescaling: alpha = 1).  Otherwise, and in
+      // the first step, the warp finds the maximum first and goes over the scores again.
+      float alpha = 1.0f, m_new = m;
+      float2 sum2[2];
+      float mx4[4];
+      auto pass = [&](bool want_p, float ref) {
+        const float neg_m = (ref == -INFINITY) ? 0.f : -ref;
+        const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg_m, neg_m);
+        sum2[0] = sum2[1] = make_float2(0.f, 0.f);
+        mx4[0] = mx4[1] = mx4[2] = mx4[3] = -INFINITY;
+        // 32 scores at a time
+        auto chunk = [&](int c0, uint32_t (&r)[32]) {
+          if (masked) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (key0 + c0 + c > q_pos) r[c] = 0xff800000u;          // -inf
+          }
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            mx4[0] = max3(mx4[0], __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+            mx4[1] = max3(mx4[1], __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+            mx4[2] = max3(mx4[2], __uint_as_float(r[c + 4]), __uint_as_float(r[c + 5]));
+            mx4[3] = max3(mx4[3], __uint_as_float(r[c + 6]), __uint_as_float(r[c + 7]));
+          }
+          if (want_p) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float2 e = __ffma2_rn(
+                  make_float2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2, neg2);
+              const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+              sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], pp);
+              packed[c >> 1] = pack2(pp.x, pp.y);
+            }
+            // 32 keys = four 16-byte chunks of the row's 128-byte line of k-block c0 / 64
+            unsigned char* line = prow + (c0 >> 6) * kPfBQ * 128;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const uint4 v4 = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2],
+                                          packed[4 * ch + 3]);
+              const int at = ((c0 & 32) >> 3) + ch;
+              *reinterpret_cast<uint4*>(line + ((at ^ (row & 7)) << 4)) = v4;
+            }
+          }
+        };
+        // (asking for the next 32 scores before these are worked on was measured and lost,
+        // 105 against 98 us at 8 x 2,048 tokens: it costs registers that spill)
+#pragma unroll
+        for (int c0 = 0; c0 < kPfBK; c0 += 32) {
+          uint32_t r[32];
+          tc::tmem_load_32(s_addr + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          chunk(c0, r);
+        }
+        // the scale is positive, so the largest raw score is the largest scaled one
+        return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      };
+      bool again = j == 0;
+      if (!again) {
+        const float top = pass(true, m);
+        again = __any_sync(0xffffffffu, top > m + 8.0f);
+        if (again) m_new = fmaxf(m, top);
+      } else {
+        m_new = fmaxf(m, pass(false, m));
+      }
+      if (again) {
+        alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+        pass(true, m_new);
+      }
+      const float2 s2 = __fadd2_rn(sum2[0], sum2[1]);
+      l = l * alpha + (s2.x + s2.y);
+      m = m_new;
+      tc::fence_proxy_async();                // generic-proxy writes -> visible to the MMA
+      tc::tc_fence_before();                  // and this step's reads of S are done
+      tc::mbar_arrive(&p_full[x]);
+      if (j > 0) fold(j - 1, alpha_before);
+      alpha_before = alpha;
+    }
+    if (steps > 0) fold(steps - 1, alpha_before);
+    if (ok && row_valid) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* orow = out + (size_t)(tok0 + it_q0[x] + row) * ldo + (size_t)it_head[x] * hd;
+#pragma unroll
+      for (int d = 0; d < 64; d += 8) {
+        if (d < hd) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = o[d + e] * inv;
+          store8(orow + d, v);
+        }
+      }
+    }
+  }
+  if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
 }  // namespace cretif
 
 using namespace cretif;
 
 // Tuning aid: a device buffer of 8 x 16 timestamps that the next launches fill (see the kernel).
 static unsigned long long* g_pf_stamps = nullptr;
+// Two query tiles per CTA: -1 where the launcher sees fit, 0 never, 1 wherever the kernel
+// takes the shape (for tests that run both).
+static int g_pf_pairing = -1;
+extern "C" int cretif_set_prefill_pairing(int mode) {
+  const int was = g_pf_pairing;
+  g_pf_pairing = mode < 0 ? -1 : (mode > 0 ? 1 : 0);
+  return was;
+}
 #ifdef CRETIF_STAMPS
 extern "C" void cretif_attn_prefill_stamps(unsigned long long* device_buffer) {
   g_pf_stamps = device_buffer;
@@ -456,6 +799,38 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
+  // Two query tiles per CTA where that still fills the chip: head sizes up to 64, no window.
+  const int group = nh / nkv;
+  const long long n_qt = (max_new + kPfBQ - 1) / kPfBQ;
+  const long long pairs = (n_qt * group + 1) / 2;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // (2,048-token prompts, 9 heads on 3: 31 against 44 us for two prompts = 144 CTAs of pairs,
+  // 48 against 43 us for three = 216, 117 against 98 us for eight)
+  const bool paired = g_pf_pairing != 0 && hd <= 64 && window == 0 && pairs <= 65535 &&
+                      (g_pf_pairing > 0 || 5 * pairs * nkv * B >= 7LL * sm_count);
+  if (paired) {
+    const PpSmem P;
+    static int configured_pair = 0;
+    if (P.total > configured_pair) {
+      e = cudaFuncSetAttribute(attn_prefill_pair_kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, P.total);
+      if (e != cudaSuccess) return (int)e;
+      configured_pair = P.total;
+    }
+    cfg.gridDim = dim3(nkv, B, (unsigned)pairs);
+    cfg.dynamicSmemBytes = P.total;
+    count_variant(kVarPrefillAttnPair);
+    e = cudaLaunchKernelEx(&cfg, attn_prefill_pair_kernel, map_q, map_k, map_v,
+                           (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
+                           seq_slot, nh, nkv, hd, scale_log2, fault);
+    return e == cudaSuccess ? launch_status() : (int)e;
+  }
   count_variant(kVarPrefillAttn);
   if (hd <= 64) {
     static int configured = 0;

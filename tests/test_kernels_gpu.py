@@ -568,10 +568,26 @@ PREFILL_CASES = [  # nh, nkv, hd, lens (cached + new), new tokens per sequence
 ]
 
 
-@pytest.mark.parametrize("nh,nkv,hd,lens,news", PREFILL_CASES)
+@pytest.fixture(params=[0, 1], ids=["one-tile-per-cta", "two-tiles-per-cta"])
+def prefill_pairing(request, ops):
+    """The tensor-core prefill attention gives a CTA one tile of 128 queries, or two tiles that
+    share a key/value head (head sizes up to 64, no window); a launch chooses by its size.
+    Tests of that kernel run both ways."""
+    old = ops.set_prefill_pairing(request.param)
+    yield request.param
+    ops.set_prefill_pairing(old)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,lens,news", PREFILL_CASES + [
+    # several query tiles and heads per group, so that pairs hold two heads of one tile, two
+    # tiles of one head, and a last pair of one item; the second sequence continues at 100
+    (9, 3, 64, [700, 500, 129], [700, 400, 129]),
+    (4, 1, 48, [390], [390]),
+    (2, 2, 16, [1000, 64], [1000, 64])])
 @pytest.mark.parametrize("window", [0, 100])
-def test_attn_prefill_tc(ops, nh, nkv, hd, lens, news, window):
+def test_attn_prefill_tc(ops, prefill_pairing, nh, nkv, hd, lens, news, window):
     scale = 1.0 / math.sqrt(hd)
+    before = ops.variant_counts()["prefill_attn_pair"]
     cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=6)
     B = len(lens)
     assert ops.attn_prefill_supported(hd, 64)
@@ -588,6 +604,8 @@ def test_attn_prefill_tc(ops, nh, nkv, hd, lens, news, window):
                      64, B, max(news), fault)
     torch.cuda.synchronize()
     assert fault.item() == 0
+    took_pairs = ops.variant_counts()["prefill_attn_pair"] > before
+    assert took_pairs == (prefill_pairing == 1 and window == 0 and hd <= 64)
     for b, n in enumerate(lens):
         k, v = cache.keys(b, n)
         q = qkv[cu[b]:cu[b + 1], :nh * hd].double().cpu().reshape(news[b], nh, hd)

@@ -147,48 +147,59 @@ def test_a_reused_slot_shows_nothing_of_its_last_owner(engines, plain_models, dt
     assert rel_err(after, alone) <= TOL[dtype]
 
 
+# name -> (gain of layer 0's query and key projections, tokens of the long request)
+SHARP = {"A": (32.0, 120), "B": (24.0, 250), "C": (24.0, 300)}
+
+
 @pytest.fixture(scope="module")
-def sharp_model(tmp_path_factory, model_dirs):
-    """Configuration B with layer 0's query and key projections scaled up so that attention
-    is sharp: each query then reads a few particular keys, far ones included, and a wrong
-    key, position or cache slot changes the logits visibly."""
+def sharp_models(tmp_path_factory, model_dirs):
+    """Every tiny configuration with layer 0's query and key projections scaled up so that
+    attention is sharp: each query then reads a few particular keys, far ones included, and a
+    wrong key, position or cache slot changes the logits visibly (head sizes 16, 32 and 48,
+    both pairings of the rotary channels)."""
     from safetensors import safe_open
     from cretif_b200.weights import write_model_folder
-    d = str(tmp_path_factory.mktemp("model_B_sharp"))
-    tensors = {}
-    with safe_open(os.path.join(model_dirs["B"], "model.safetensors"), framework="pt") as f:
-        for k in f.keys():
-            tensors[k] = f.get_tensor(k)
-    for name in ("q_proj", "k_proj"):
-        key = f"model.layers.0.self_attn.{name}.weight"
-        tensors[key] = (tensors[key].float() * 24.0).to(torch.bfloat16)
-    with open(os.path.join(model_dirs["B"], "config.json")) as f:
-        cfg = json.load(f)
-    write_model_folder(d, cfg, tensors)
-    return d, pl.read_model_folder(d)
+    made = {}
+    for name, (gain, _) in SHARP.items():
+        d = str(tmp_path_factory.mktemp(f"model_{name}_sharp"))
+        tensors = {}
+        with safe_open(os.path.join(model_dirs[name], "model.safetensors"), framework="pt") as f:
+            for k in f.keys():
+                tensors[k] = f.get_tensor(k)
+        for proj in ("q_proj", "k_proj"):
+            key = f"model.layers.0.self_attn.{proj}.weight"
+            tensors[key] = (tensors[key].float() * gain).to(torch.bfloat16)
+        with open(os.path.join(model_dirs[name], "config.json")) as f:
+            cfg = json.load(f)
+        write_model_folder(d, cfg, tensors)
+        made[name] = (d, pl.read_model_folder(d))
+    return made
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_sharp_attention_over_hundreds_of_keys(sharp_model, dtype):
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_sharp_attention_over_hundreds_of_keys(sharp_models, name, dtype):
     from cretif_b200.engine import Engine
-    d, (cfg, w) = sharp_model
+    d, (cfg, w) = sharp_models[name]
+    n = SHARP[name][1]
     eng = Engine(d, dtype=dtype, max_tokens=1024)
     # With scores this large, rounding q and k to bfloat16 alone moves the softmax by more
     # than the usual bound, in any engine; so the bfloat16 run is compared with the plain
     # model rounded at the same stores.  float32 is compared with the exact plain model.
     storage = torch.bfloat16 if dtype == "bfloat16" else None
     plain = lambda t: pl.forward(cfg, w, t, storage=storage).numpy()
-    toks = tiny.tokens("B", 250, 70)
+    toks = tiny.tokens(name, n, 70)
     want = plain(toks)
     exact = pl.forward(cfg, w, toks).numpy()
     if storage is not None:      # the sharpening bites: plain rounding alone breaks the bound
         assert rel_err(want, exact) > TOL[dtype]
     assert rel_err(run_whole(eng, toks), want) <= TOL[dtype]
     assert rel_err(run_tail_by_one(eng, toks, tail=32), want) <= TOL[dtype]
-    reqs = [toks, tiny.tokens("B", 100, 71), tiny.tokens("B", 180, 72)]
-    outs = run_batch(eng, reqs, [218, 70, 1])
+    reqs = [toks, tiny.tokens(name, 2 * n // 5, 71), tiny.tokens(name, 3 * n // 4, 72)]
+    outs = run_batch(eng, reqs, [n - 32, 2 * n // 7, 1])
     for r, got in zip(reqs, outs):
         assert rel_err(got, plain(r)) <= TOL[dtype]
+    eng.cache.check()
 
 
 def test_sampling_through_the_entry_point(engines):

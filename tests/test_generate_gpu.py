@@ -303,3 +303,52 @@ def test_command_line(model_dirs, plain_models, tmp_path):
     assert abs(doc["top_logits"][0]["logit_value"] - float(logits.max())) < 1e-4
     bad = run("hello there")
     assert bad.returncode != 0 and "token ids" in (bad.stderr + bad.stdout)
+
+
+def test_decoding_across_a_context_bucket(engines, plain_models):
+    """A decode step is planned for a context bucket (512, 1024, ...), which is part of a
+    captured graph's key.  Generation and single-token steps that cross 512 keep giving the
+    plain model's tokens and logits on both sides of the boundary, captured or not."""
+    eng = engines("C", "float32")
+    cfg, w = plain_models["C"]
+    assert [eng.context_bucket(n) for n in (1, 512, 513, 1024, 5000)] == [512, 512, 1024, 1024, 1024]
+    prompts = [tiny.tokens("C", 505, 5), tiny.tokens("C", 498, 6), tiny.tokens("C", 20, 7)]
+    got = eng.generate(prompts, max_tokens=14, stop_ids=[])
+    for p, r in zip(prompts, got):
+        assert r.tokens == pl.greedy(cfg, w, p, 14)
+    runner = eng._backends[(0.0, 0, True)].runner
+    assert {key[1] for key in runner.graphs} >= {512, 1024}      # a graph per bucket
+    # the step function: the same shape of step before and after the boundary, twice each so
+    # that both are captured and replayed
+    toks = tiny.tokens("C", 520, 8)
+    want = pl.forward(cfg, w, toks).numpy()
+    slot = eng.alloc_slot()
+    try:
+        rows = [eng.step([(slot, toks[:506])], "all").cpu().numpy()]
+        for i in range(506, 520):
+            rows.append(eng.step([(slot, [toks[i]])], "all").cpu().numpy())
+    finally:
+        eng.free_slot(slot)
+    assert rel_err(np.concatenate(rows), want) <= TOL["float32"]
+    assert {k[2] for k in eng._graphs if k[0] == (1,)} >= {512, 1024}
+
+
+def test_seeds_share_one_set_of_decode_graphs(engines):
+    """The sampling kernel reads its seed from device memory, so an engine keeps one backend
+    (and its graphs) per temperature and top-k, whatever seeds its callers use, and at most
+    four of them."""
+    from cretif_b200.engine.generate import MAX_BACKENDS
+    eng = engines("A", "float32")
+    prompts = [tiny.tokens("A", n, 90 + n) for n in (4, 11)]
+    outs = {}
+    for seed in (1, 2, 3, 1):
+        res = eng.generate(prompts, max_tokens=8, temperature=1.3, top_k=50, seed=seed, stop_ids=[])
+        toks = [r.tokens for r in res]
+        if seed in outs:
+            assert toks == outs[seed]                  # the same seed, the same draws
+        outs[seed] = toks
+    assert len({str(v) for v in outs.values()}) == 3   # other seeds, other draws
+    assert sum(1 for k in eng._backends if k[:2] == (1.3, 50)) == 1
+    for t in (0.5, 0.6, 0.7, 0.8, 0.9, 1.0):
+        eng.generate(prompts, max_tokens=2, temperature=t, stop_ids=[])
+    assert len(eng._backends) <= MAX_BACKENDS

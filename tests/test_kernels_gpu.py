@@ -613,6 +613,40 @@ def test_attn_prefill_tc(ops, prefill_pairing, nh, nkv, hd, lens, news, window):
         close(out[cu[b]:cu[b + 1]].reshape(news[b], nh, hd), want, 1e-2)
 
 
+def test_attn_prefill_rows_whose_reference_jumps(ops, prefill_pairing):
+    """Late in a long prompt a key appears that dominates everything the later queries have
+    seen so far (its score exceeds their running reference by far more than 2^8): the kernel
+    that keeps its output in tensor memory has to rescale it there, in the middle of the
+    sequence.  Queries before that key must not see it.  Against float64."""
+    nh, nkv, hd, n = 4, 2, 64, 1000
+    late = 700
+    cache = ToyCache([n], nkv, hd, torch.bfloat16, seed=31)
+    qkv = rnd(n, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=32)
+    # queries 800..999 of head 0 and 2 all look like one vector; the key at `late` is 30 x it
+    probe = rnd(1, hd, dtype=torch.bfloat16, seed=33)[0]
+    for h in (0, 2):
+        qkv[800:, h * hd:(h + 1) * hd] = probe
+    blk = cache.table_host[cache.slots[0], late // 64]
+    for kvh in range(nkv):
+        cache.k[blk, kvh, late % 64, :] = (probe.float() * 30).to(torch.bfloat16)
+    out = torch.zeros(n, nh * hd, device=DEV, dtype=torch.bfloat16)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    start = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    ops.attn_prefill(qkv, out, cache.k, cache.v, cache.table, cu, start, cache.seq_slot, nh, nkv,
+                     hd, 1.0, 0, 64, 1, n, fault)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+    k, v = cache.keys(0, n)
+    q = qkv[:, :nh * hd].double().cpu().reshape(n, nh, hd)
+    want = plain_attention(q, k, v, 1.0, list(range(n)))
+    close(out.reshape(n, nh, hd), want, 1e-2)
+    # the late queries of head 0 return that key's value, the early ones do not
+    close(out[900, :hd], cache.v[blk, 0, late % 64, :], 2e-2)
+    assert (out[600, :hd].float() - cache.v[blk, 0, late % 64, :].float()).abs().max() > 0.5
+
+
 @pytest.mark.parametrize("cluster", [False, True])
 def test_attn_decode_finds_a_far_key(ops, cluster):
     """One key among thousands is made to dominate; the output must be its value."""

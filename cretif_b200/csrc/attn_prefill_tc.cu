@@ -419,31 +419,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 // and the special-function unit (two warps x 64 ex2 x 8 cycles of a 1,280 ns step) idles for
 // more than half of it.  Here a CTA owns TWO tiles of 128 queries that read the same key/value
 // head — two query heads of a group, or consecutive query tiles — and a softmax thread owns a
-// whole row of one of them (128 scores a step, the 64 output columns): no partner, no
-// barrier, and the tiles' warps (2-5 and 6-9, one of each on every sub-partition) run out of
-// phase with each other, one exponentiating while the other waits for its products.  The
-// keys and values of a step are loaded once for both tiles.
-//   tensor memory: S_a, S_b (128 columns each), O_blk of each tile twice (4 x 64);
-//   shared memory: Q_a, Q_b, P_a, P_b, three stages of K/V (128 keys).
-// A thread reads its scores twice (the maximum first, then the exponentials), which keeps
-// 32 of them in registers at a time.  Head sizes up to 64, no sliding window; the launcher
-// falls back to the kernel above otherwise, and for grids too small to fill the chip with
-// half as many CTAs.
+// whole row of one of them (128 scores a step): no partner, no barrier, and the tiles' warps
+// (2-5 and 6-9, one of each on every sub-partition) work side by side.  The keys and values
+// of a step are loaded once for both tiles.
+//   tensor memory, per tile: S (128 columns), P (64: two bfloat16 a column), O (64);
+//   shared memory: Q_a, Q_b and the stages of K/V (128 keys).
+// P never touches shared memory: the row's thread writes it into tensor memory, from where
+// the product P V reads it as its A operand, and the product adds into O itself.  That works
+// because a row's reference for the exponentials is lazy — it stays as it is until a score
+// exceeds it by 2^8 — so O needs no rescaling in almost every step; when the reference does
+// move, the row's thread reads O, scales it and writes it back before it hands over its P.
+// A tile's chain is then: scores -> exponentials -> next scores; the product runs beside it.
+// Head sizes up to 64, no sliding window; the launcher falls back to the kernel above
+// otherwise, and for grids too small to fill the chip with half as many CTAs.
 constexpr int kPpStages = 3;
+constexpr int kPpThreads = 352;   // producer, issuer of tile 0, 2 x 4 softmax warps, issuer of tile 1
+constexpr int kPpIssuer1 = 10;
 
 struct PpSmem {
-  int q, p, k, v, bars, total;
+  int q, k, v, bars, total;
   __host__ __device__ PpSmem() {
     q = 0;                                   // [2][128 rows][128 B]
-    p = q + 2 * kPfBQ * 128;                 // [2 tiles][2 k-blocks][128 rows][128 B]
-    k = p + 2 * (kPfBK / 64) * kPfBQ * 128;
+    k = q + 2 * kPfBQ * 128;
     v = k + kPpStages * kPfBK * 128;
     bars = v + kPpStages * kPfBK * 128;
-    total = bars + (2 * kPpStages + 12) * 8 + 32 + 1024;
+    total = bars + 17 * 8 + 16 + 1024;       // 17 barriers, two words, alignment
   }
 };
 
-__global__ void __launch_bounds__(kPfThreads, 1)
+__global__ void __launch_bounds__(kPpThreads, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -458,10 +462,10 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L.bars);
   uint64_t* kv_empty = kv_full + kPpStages;
   uint64_t* q_full = kv_empty + kPpStages;
-  uint64_t* s_full = q_full + 1;            // [tile]
-  uint64_t* p_full = s_full + 2;            // [tile]
-  uint64_t* o_full = p_full + 2;            // [tile][buffer]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 4);
+  uint64_t* s_full = q_full + 1;            // [tile][half of a step's keys]
+  uint64_t* p_full = s_full + 4;            // [tile][half]
+  uint64_t* pv_done = p_full + 4;           // [tile]: its last product has finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -477,7 +481,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   const int* tab = table + (size_t)seq_slot[b] * table_stride;
   // the CTA's one or two items
   int it_q0[2], it_head[2], it_rows[2], it_steps[2];
-  const int n_mine = 2 * pair + 1 < n_items ? 2 : 1;
+  const int n_mine = min(2, n_items - 2 * pair);
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
     const int idx = 2 * pair + (x < n_mine ? x : 0);
@@ -492,18 +496,17 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   const int blk_hi = 2 * n_steps - 1;        // (blocks past a sequence's end are clamped below)
   const int blk_last = (start + n_new - 1) / kPfBlk;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColO = 256;          // S: + 128 tile; O: + 128 tile + 64 buffer
-  constexpr int kPBytes = (kPfBK / 64) * kPfBQ * 128;
+  constexpr uint32_t kColTile = 256, kColS = 0, kColP = 128, kColO = 192;   // per tile
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPpStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < kPpStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 2); }
     tc::mbar_init(q_full, 1);
-    for (int x = 0; x < 2; ++x) {
+    for (int x = 0; x < 4; ++x) {
       tc::mbar_init(&s_full[x], 1);
       tc::mbar_init(&p_full[x], 128);
-      tc::mbar_init(&o_full[2 * x], 1);
-      tc::mbar_init(&o_full[2 * x + 1], 1);
     }
+    tc::mbar_init(&pv_done[0], 1);
+    tc::mbar_init(&pv_done[1], 1);
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_q);
@@ -542,11 +545,24 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kPpIssuer1) {
+    // ---- the products of one tile each.  (An issuing thread pays some 45 cycles a product and
+    // 150-200 for every commit and barrier wait, whatever the products' sizes; one thread for
+    // both tiles was busy all the time.)
     if (lane == 0) {
-      const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK);
+      const int x = warp == 1 ? 0 : 1;
+      const int steps = it_steps[x];
+      const uint32_t idesc_qk = tc::instr_desc_bf16(kPfBQ, kPfBK / 2);
       const uint32_t idesc_pv = tc::instr_desc_bf16(kPfBQ, hd) | (1u << 16);   // B is MN-major
       const int k_steps = hd >> 4;
+      const uint32_t t_s = tmem + (uint32_t)x * kColTile + kColS;
+      const uint32_t t_p = tmem + (uint32_t)x * kColTile + kColP;
+      const uint32_t t_o = tmem + (uint32_t)x * kColTile + kColO;
+      const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + x * kPfBQ * 128);
+      const uint64_t kd0 = tc::smem_desc_k_sw128(smem + L.k);
+      const uint64_t vd0 = smem_desc_mn_sw128(smem + L.v, (uint32_t)(kPfBK * 128));
+      constexpr uint64_t kStage = (uint64_t)((kPfBK * 128) >> 4);    // a stage, in descriptor units
+      constexpr uint64_t kHalf = (uint64_t)((kPfBlk * 128) >> 4);    // 64 keys of it
       int ready = -1;                       // highest step whose keys and values have landed
       bool ok = tc::mbar_wait(q_full, 0u, abort);
       auto landed = [&](int j) {            // wait (once) for the stage of step j
@@ -557,45 +573,52 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         tc::tc_fence_after();
         return ok;
       };
-      auto scores = [&](int x, int j) {     // S_x = Q_x K_j^T
-        const int s = j % kPpStages;
-        for (int kk = 0; kk < k_steps; ++kk) {
-          const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + x * kPfBQ * 128) + 2 * kk;
-          const uint64_t kd = tc::smem_desc_k_sw128(smem + L.k + s * kPfBK * 128) + 2 * kk;
-          tc::umma_bf16(tmem + kColS + (uint32_t)x * kPfBK, qd, kd, idesc_qk, kk != 0);
-        }
-        tc::umma_commit(&s_full[x]);
-      };
-      // Both tiles' scores of a step are issued as early as their S tiles are free, so that the
-      // two tiles' threads work side by side.  (Taking strict turns — one tile exponentiating
-      // while the other folds and waits — was measured: 142 against 98 us at 8 x 2,048 tokens.
-      // A tile's step is a chain of latencies, not of special-function throughput, and two
-      // chains side by side hide more of each other than two in a row.)
-      auto product = [&](int x, int j) {     // O_blk_x = P_x V_j, once P_x of step j is there
-        ok = tc::mbar_wait(&p_full[x], (uint32_t)(j & 1), abort);
-        if (!ok) return;
-        tc::tc_fence_after();
-        const int s = j % kPpStages;
-        const uint64_t vd = smem_desc_mn_sw128(smem + L.v + s * kPfBK * 128,
-                                               (uint32_t)(kPfBK * 128));
+      auto scores = [&](int j, int h) {     // S_x[:, 64 h ..] = Q_x K_j[64 h ..]^T
+        const uint64_t kd = kd0 + (uint64_t)(j % kPpStages) * kStage + (uint64_t)h * kHalf;
 #pragma unroll
-        for (int kk = 0; kk < kPfBK / 16; ++kk) {
-          const uint64_t pd = tc::smem_desc_k_sw128(smem + L.p + x * kPBytes +
-                                                    (kk >> 2) * kPfBQ * 128) + 2 * (kk & 3);
-          tc::umma_bf16(tmem + kColO + (uint32_t)(x * 128 + (j & 1) * 64), pd,
-                        vd + (uint64_t)(kk * 128), idesc_pv, kk != 0);
-        }
-        tc::umma_commit(&o_full[2 * x + (j & 1)]);
+        for (int kk = 0; kk < 4; ++kk)
+          if (kk < k_steps)
+            tc::umma_bf16(t_s + (uint32_t)(h * kPfBlk), qd + 2 * kk, kd + 2 * kk, idesc_qk, kk != 0);
       };
-      if (ok && n_steps > 0 && landed(0))
-        for (int x = 0; x < n_mine; ++x) scores(x, 0);
-      for (int j = 0; j < n_steps && ok; ++j) {
-        for (int x = 0; x < n_mine && ok; ++x) {
-          if (j >= it_steps[x]) continue;
-          product(x, j);                     // (S_x has been read for the last time by then)
-          if (ok && j + 1 < it_steps[x] && landed(j + 1)) scores(x, j + 1);
+      auto product = [&](int j, int h) {    // O_x (+)= P_x[:, 64 h ..] V_j[64 h ..]
+        const uint64_t vd = vd0 + (uint64_t)(j % kPpStages) * kStage;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          const int kk = h * 4 + k4;
+          tc::umma_bf16_a_tmem(t_o, t_p + (uint32_t)(kk * 8), vd + (uint64_t)(kk * 128), idesc_pv,
+                               (j | kk) != 0);
         }
-        if (ok) tc::umma_commit(&kv_empty[j % kPpStages]);   // all products on this stage issued
+      };
+      if (ok && steps > 0 && landed(0)) {
+        scores(0, 0);
+        tc::umma_commit(&s_full[2 * x]);
+        scores(0, 1);
+        tc::umma_commit(&s_full[2 * x + 1]);
+      }
+      for (int j = 0; j < n_steps && ok; ++j) {
+        if (j < steps) {
+          // A step's keys go in two halves of 64.  When the tile's threads have written the P
+          // of a half, its product is issued and then the same half of the next step's
+          // scores (that half of S has been read for the last time); one commit tells the
+          // threads both that the scores are there and that this P has been read.  The
+          // threads meanwhile work on the other half and find the next scores waiting.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            ok = tc::mbar_wait(&p_full[2 * x + h], (uint32_t)(j & 1), abort);
+            if (!ok) break;
+            tc::tc_fence_after();
+            product(j, h);
+            if (j + 1 < steps && landed(j + 1)) scores(j + 1, h);
+            tc::umma_commit(&s_full[2 * x + h]);
+          }
+          if (!ok) break;
+          tc::umma_commit(&kv_empty[j % kPpStages]);         // this tile is done with the stage
+          if (j + 1 == steps) tc::umma_commit(&pv_done[x]);
+        } else if (landed(j)) {
+          // a tile with fewer steps (or none) has no use for the stage: it says so once the
+          // stage has been filled, which keeps its arrivals in step with the ring's turns
+          tc::mbar_arrive(&kv_empty[j % kPpStages]);
+        }
       }
     }
   } else {
@@ -607,45 +630,37 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     const int pos_first = start + it_q0[x];
     const bool row_valid = x < n_mine && row < it_rows[x];
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    const uint32_t s_addr = lane_addr + kColS + (uint32_t)x * kPfBK;
-    float o[64];
-#pragma unroll
-    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    const uint32_t s_addr = lane_addr + (uint32_t)x * kColTile + kColS;
+    const uint32_t p_addr = lane_addr + (uint32_t)x * kColTile + kColP;
+    const uint32_t o_addr = lane_addr + (uint32_t)x * kColTile + kColO;
     float m = -INFINITY, l = 0.f;
-    unsigned char* prow = smem + L.p + x * kPBytes + row * 128;
     bool ok = true;
-    auto fold = [&](int jj, float a) {       // o = o * a + (P V of step jj)
-      ok = tc::mbar_wait(&o_full[2 * x + (jj & 1)], (uint32_t)((jj >> 1) & 1), abort) && ok;
-      tc::tc_fence_after();
-      const float2 a2 = make_float2(a, a);
+    // O *= a for this thread's row (no product of the tile is in flight, see below).
+    auto rescale = [&](float a) {
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
         if (c0 < hd) {
           uint32_t r[32];
-          tc::tmem_load_32(lane_addr + kColO + (uint32_t)(x * 128 + (jj & 1) * 64 + c0), r);
+          tc::tmem_load_32(o_addr + (uint32_t)c0, r);
           tc::tmem_load_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float2 v = __ffma2_rn(make_float2(o[c0 + e], o[c0 + e + 1]), a2,
-                                        make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])));
-            o[c0 + e] = v.x;
-            o[c0 + e + 1] = v.y;
-          }
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * a);
+          tc::tmem_store_32(o_addr + (uint32_t)c0, r);
         }
       }
-      tc::tc_fence_before();
     };
-    float alpha_before = 0.f;
-    for (int j = 0; j < steps; ++j) {
-      ok = tc::mbar_wait(&s_full[x], (uint32_t)(j & 1), abort) && ok;
+    for (int hs = 0; hs < 2 * steps; ++hs) {
+      const int j = hs >> 1, h = hs & 1;
+      // the scores of this half are there, and the product that read the half's last P is done
+      ok = tc::mbar_wait(&s_full[2 * x + h], (uint32_t)(j & 1), abort) && ok;
       tc::tc_fence_after();
-      const int key0 = 2 * j * kPfBlk;
-      const bool masked = key0 + kPfBK - 1 > pos_first;     // the step reaches the diagonal
+      const int key0 = hs * kPfBlk;
+      const bool masked = key0 + kPfBlk - 1 > pos_first;     // the half reaches the diagonal
       // One pass over the scores: p = 2^(s * scale - ref) with `ref` the reference the row
-      // already has, the step's maximum found on the way.  As long as no score exceeds the
+      // already has, the half's maximum found on the way.  As long as no score exceeds the
       // reference by more than 2^8 the reference stays (p <= 256 is harmless in bfloat16 and
-      // in the 32-bit sums, and the output needs no rescaling: alpha = 1).  Otherwise, and in
-      // the first step, the warp finds the maximum first and goes over the scores again.
+      // in the 32-bit sums, and the output needs no rescaling: alpha = 1).  Otherwise, and at
+      // the very first keys, the warp finds the maximum first and goes over the scores again.
       float alpha = 1.0f, m_new = m;
       float2 sum2[2];
       float mx4[4];
@@ -678,30 +693,23 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], pp);
               packed[c >> 1] = pack2(pp.x, pp.y);
             }
-            // 32 keys = four 16-byte chunks of the row's 128-byte line of k-block c0 / 64
-            unsigned char* line = prow + (c0 >> 6) * kPfBQ * 128;
-#pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              const uint4 v4 = make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2],
-                                          packed[4 * ch + 3]);
-              const int at = ((c0 & 32) >> 3) + ch;
-              *reinterpret_cast<uint4*>(line + ((at ^ (row & 7)) << 4)) = v4;
-            }
+            tc::tmem_store_16(p_addr + (uint32_t)((h * kPfBlk + c0) >> 1), packed);
           }
         };
-        // (asking for the next 32 scores before these are worked on was measured and lost,
-        // 105 against 98 us at 8 x 2,048 tokens: it costs registers that spill)
-#pragma unroll
-        for (int c0 = 0; c0 < kPfBK; c0 += 32) {
-          uint32_t r[32];
-          tc::tmem_load_32(s_addr + (uint32_t)c0, r);
+        // (the second 32 are on their way while the first are worked on)
+        {
+          uint32_t r0[32], r1[32];
+          tc::tmem_load_32(s_addr + (uint32_t)(h * kPfBlk), r0);
           tc::tmem_load_wait();
-          chunk(c0, r);
+          tc::tmem_load_32(s_addr + (uint32_t)(h * kPfBlk + 32), r1);
+          chunk(0, r0);
+          tc::tmem_load_wait();
+          chunk(32, r1);
         }
         // the scale is positive, so the largest raw score is the largest scaled one
         return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       };
-      bool again = j == 0;
+      bool again = hs == 0;
       if (!again) {
         const float top = pass(true, m);
         again = __any_sync(0xffffffffu, top > m + 8.0f);
@@ -712,27 +720,43 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       if (again) {
         alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
         pass(true, m_new);
+        if (hs > 0) {
+          // O is scaled in place.  The product of the half before this one may still run:
+          // the commit that follows it is the one the other half's scores wait for next.
+          ok = tc::mbar_wait(&s_full[2 * x + (h ^ 1)], (uint32_t)((j + h) & 1), abort) && ok;
+          tc::tc_fence_after();
+          rescale(alpha);
+        }
       }
       const float2 s2 = __fadd2_rn(sum2[0], sum2[1]);
       l = l * alpha + (s2.x + s2.y);
       m = m_new;
-      tc::fence_proxy_async();                // generic-proxy writes -> visible to the MMA
-      tc::tc_fence_before();                  // and this step's reads of S are done
-      tc::mbar_arrive(&p_full[x]);
-      if (j > 0) fold(j - 1, alpha_before);
-      alpha_before = alpha;
+      tc::tmem_store_wait();                  // P (and O) are in tensor memory,
+      tc::tc_fence_before();                  // this half's reads of S are done
+      tc::mbar_arrive(&p_full[2 * x + h]);
     }
-    if (steps > 0) fold(steps - 1, alpha_before);
-    if (ok && row_valid) {
+    if (steps > 0) {
+      ok = tc::mbar_wait(&pv_done[x], 0u, abort) && ok;
+      tc::tc_fence_after();
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = out + (size_t)(tok0 + it_q0[x] + row) * ldo + (size_t)it_head[x] * hd;
 #pragma unroll
-      for (int d = 0; d < 64; d += 8) {
-        if (d < hd) {
-          float v[8];
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        if (c0 < hd) {
+          uint32_t r[32];
+          tc::tmem_load_32(o_addr + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          if (ok && row_valid) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = o[d + e] * inv;
-          store8(orow + d, v);
+            for (int d = 0; d < 32; d += 8) {
+              if (c0 + d < hd) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[d + e]) * inv;
+                store8(orow + c0 + d, v);
+              }
+            }
+          }
         }
       }
     }
@@ -799,7 +823,8 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
-  // Two query tiles per CTA where that still fills the chip: head sizes up to 64, no window.
+  // Two query tiles per CTA (a thread per row, P and O in tensor memory) where pairs still
+  // spread over the chip: head sizes up to 64, no window.
   const int group = nh / nkv;
   const long long n_qt = (max_new + kPfBQ - 1) / kPfBQ;
   const long long pairs = (n_qt * group + 1) / 2;
@@ -810,20 +835,19 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  // (2,048-token prompts, 9 heads on 3: 31 against 44 us for two prompts = 144 CTAs of pairs,
-  // 48 against 43 us for three = 216, 117 against 98 us for eight)
   const bool paired = g_pf_pairing != 0 && hd <= 64 && window == 0 && pairs <= 65535 &&
                       (g_pf_pairing > 0 || 5 * pairs * nkv * B >= 7LL * sm_count);
   if (paired) {
     const PpSmem P;
     static int configured_pair = 0;
-    if (P.total > configured_pair) {
+    if (!configured_pair) {
       e = cudaFuncSetAttribute(attn_prefill_pair_kernel,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, P.total);
       if (e != cudaSuccess) return (int)e;
-      configured_pair = P.total;
+      configured_pair = 1;
     }
     cfg.gridDim = dim3(nkv, B, (unsigned)pairs);
+    cfg.blockDim = dim3(kPpThreads);
     cfg.dynamicSmemBytes = P.total;
     count_variant(kVarPrefillAttnPair);
     e = cudaLaunchKernelEx(&cfg, attn_prefill_pair_kernel, map_q, map_k, map_v,

@@ -147,7 +147,7 @@ enum Variant : int {
   kVarTc64, kVarTc128, kVarTc256,   // tcgen05 product by tile width
   kVarTcSeveralTiles,       // ... whose persistent CTAs walk more than one tile
   kVarTc192,                // ... 192 columns wide
-  kVarPrefillAttnPair,      // tcgen05 prefill attention, two query tiles per CTA
+  kVarPrefillAttnPair,      // tcgen05 prefill attention, a thread per row, two query tiles per CTA
   kVarCount
 };
 void count_variant(int v);

@@ -586,9 +586,10 @@ def gemm_tc_qkv_rope(x, w_qkv, q_out, cos, sin, pairing: int, nh: int, nkv: int,
 
 
 def set_prefill_pairing(mode: int) -> int:
-    """(For tests that run both.)  The prefill attention with two query tiles per CTA: -1 where
-    the launcher sees fit (the default), 0 never, 1 wherever the kernel takes the shape.
-    Returns the old setting."""
+    """(For tests that run both.)  Which prefill attention kernel takes head sizes up to 64
+    without a window: -1 as the launcher sees fit (the default), 0 the kernel with two threads
+    per row, 1 the one with a thread per row and two query tiles per CTA wherever it takes
+    the shape.  Returns the old setting."""
     return int(lib().cretif_set_prefill_pairing(int(mode)))
 
 

@@ -568,11 +568,12 @@ PREFILL_CASES = [  # nh, nkv, hd, lens (cached + new), new tokens per sequence
 ]
 
 
-@pytest.fixture(params=[0, 1], ids=["one-tile-per-cta", "two-tiles-per-cta"])
+@pytest.fixture(params=[0, 1], ids=["two-threads-per-row", "thread-per-row-two-tiles"])
 def prefill_pairing(request, ops):
-    """The tensor-core prefill attention gives a CTA one tile of 128 queries, or two tiles that
-    share a key/value head (head sizes up to 64, no window); a launch chooses by its size.
-    Tests of that kernel run both ways."""
+    """The tensor-core prefill attention has a kernel with two threads per row of a tile of 128
+    queries (every head size, windows), and one with a thread per row that keeps P and O in
+    tensor memory and gives a CTA two tiles that share a key/value head (head sizes up to 64,
+    no window); a launch chooses by its shape.  Tests run both."""
     old = ops.set_prefill_pairing(request.param)
     yield request.param
     ops.set_prefill_pairing(old)
@@ -587,7 +588,7 @@ def prefill_pairing(request, ops):
 @pytest.mark.parametrize("window", [0, 100])
 def test_attn_prefill_tc(ops, prefill_pairing, nh, nkv, hd, lens, news, window):
     scale = 1.0 / math.sqrt(hd)
-    before = ops.variant_counts()["prefill_attn_pair"]
+    before = ops.variant_counts()
     cache = ToyCache(lens, nkv, hd, torch.bfloat16, seed=6)
     B = len(lens)
     assert ops.attn_prefill_supported(hd, 64)
@@ -604,8 +605,10 @@ def test_attn_prefill_tc(ops, prefill_pairing, nh, nkv, hd, lens, news, window):
                      64, B, max(news), fault)
     torch.cuda.synchronize()
     assert fault.item() == 0
-    took_pairs = ops.variant_counts()["prefill_attn_pair"] > before
-    assert took_pairs == (prefill_pairing == 1 and window == 0 and hd <= 64)
+    now = ops.variant_counts()
+    took = [k for k in ("prefill_attn", "prefill_attn_pair") if now[k] > before[k]]
+    rows = window == 0 and hd <= 64
+    assert took == [("prefill_attn", "prefill_attn_pair")[prefill_pairing if rows else 0]]
     for b, n in enumerate(lens):
         k, v = cache.keys(b, n)
         q = qkv[cu[b]:cu[b + 1], :nh * hd].double().cpu().reshape(news[b], nh, hd)

@@ -145,8 +145,9 @@ int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, 
 int cretif_wait_that_expires(unsigned int limit, unsigned int* fault, unsigned int* polls,
                              void* stream);
 
-// (For tests that run both.)  Two query tiles per CTA in cretif_attn_prefill_tc: -1 where the
-// launcher sees fit (default), 0 never, 1 wherever the kernel takes the shape.  Returns the old
+// (For tests that run all.)  Which kernel cretif_attn_prefill_tc gives head sizes up to 64
+// without a window: -1 as the launcher sees fit (default), 0 two threads per row, 1 a thread per
+// row and two query tiles per CTA, 2 a thread per row and one tile per CTA.  Returns the old
 // setting.
 int cretif_set_prefill_pairing(int mode);
 

@@ -430,20 +430,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 // exceeds it by 2^8 — so O needs no rescaling in almost every step; when the reference does
 // move, the row's thread reads O, scales it and writes it back before it hands over its P.
 // A tile's chain is then: scores -> exponentials -> next scores; the product runs beside it.
+//
+// With `split` the CTA's two slots work on ONE tile instead: slot 0 takes the tile's steps
+// 0, 2, 4, ... of 128 keys, slot 1 the steps 1, 3, 5, ..., each with a reference, a sum and an
+// output of its own, and slot 0's threads merge the two at the end.  That is for grids of too
+// few tiles to fill the chip as pairs (a lone prompt): as many CTAs as tiles, and the
+// heaviest tile, which decides the launch, takes half as long.
 // Head sizes up to 64, no sliding window; the launcher falls back to the kernel above
-// otherwise, and for grids too small to fill the chip with half as many CTAs.
-constexpr int kPpStages = 3;
+// otherwise.
+constexpr int kPpStages = 4;       // stages of K/V in shared memory (pairs use three of them)
 constexpr int kPpThreads = 352;   // producer, issuer of tile 0, 2 x 4 softmax warps, issuer of tile 1
 constexpr int kPpIssuer1 = 10;
 
 struct PpSmem {
-  int q, k, v, bars, total;
+  int q, k, v, xch, bars, total;
   __host__ __device__ PpSmem() {
     q = 0;                                   // [2][128 rows][128 B]
     k = q + 2 * kPfBQ * 128;
     v = k + kPpStages * kPfBK * 128;
-    bars = v + kPpStages * kPfBK * 128;
-    total = bars + 17 * 8 + 16 + 1024;       // 17 barriers, two words, alignment
+    xch = v + kPpStages * kPfBK * 128;       // [128 rows] reference and sum of slot 1 (split)
+    bars = xch + kPfBQ * 8;
+    total = bars + (2 * kPpStages + 12) * 8 + 16 + 1024;   // barriers, two words, alignment
   }
 };
 
@@ -454,7 +461,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                          int ldo, const int* __restrict__ table, int table_stride,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
-                         unsigned int* __restrict__ fault) {
+                         int split, unsigned int* __restrict__ fault) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -465,7 +472,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   uint64_t* s_full = q_full + 1;            // [tile][half of a step's keys]
   uint64_t* p_full = s_full + 4;            // [tile][half]
   uint64_t* pv_done = p_full + 4;           // [tile]: its last product has finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* xch_full = pv_done + 2;         // slot 1's references and sums are written (split)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch_full + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -476,23 +484,30 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   const int n_items = n_qt * group;          // (query tile, head of the group), tile-major
   // heavy pairs (late query tiles) of all sequences and key/value heads first
   const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
-  if (2 * pair >= n_items) return;
+  const int first = split ? pair : 2 * pair;
+  if (first >= n_items) return;
   const int start = seq_start[b];
   const int* tab = table + (size_t)seq_slot[b] * table_stride;
-  // the CTA's one or two items
+  // The CTA's one or two items, a slot each; split: one item in both slots.  A slot's step i
+  // is the ring's step i * stride + offset.
   int it_q0[2], it_head[2], it_rows[2], it_steps[2];
-  const int n_mine = min(2, n_items - 2 * pair);
+  const int n_mine = split ? 2 : min(2, n_items - first);
+  const int stride = split ? 2 : 1;
+  // split: the two slots are at ring steps g and g + 1 and ask for g + 2 and g + 3
+  const int n_stages = split ? kPpStages : kPpStages - 1;
+  int n_steps = 0;                           // steps of the ring of keys and values
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
-    const int idx = 2 * pair + (x < n_mine ? x : 0);
+    const int idx = first + (!split && x < n_mine ? x : 0);
     const int t = idx / group;
     it_q0[x] = t * kPfBQ;
     it_head[x] = kvh * group + (idx - t * group);
     it_rows[x] = min(kPfBQ, n_new - it_q0[x]);
     const int pos_last = start + it_q0[x] + it_rows[x] - 1;
-    it_steps[x] = x < n_mine ? pos_last / kPfBlk / 2 + 1 : 0;    // steps of two cache blocks
+    const int all = pos_last / kPfBlk / 2 + 1;                   // steps of two cache blocks
+    it_steps[x] = split ? (all - x + 1) / 2 : (x < n_mine ? all : 0);
+    if (x < n_mine) n_steps = max(n_steps, all);
   }
-  const int n_steps = max(it_steps[0], it_steps[1]);
   const int blk_hi = 2 * n_steps - 1;        // (blocks past a sequence's end are clamped below)
   const int blk_last = (start + n_new - 1) / kPfBlk;
   constexpr uint32_t kTmemCols = 512;
@@ -507,6 +522,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     tc::mbar_init(&pv_done[0], 1);
     tc::mbar_init(&pv_done[1], 1);
+    tc::mbar_init(xch_full, 128);
     *abort = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_descriptor(&map_q);
@@ -526,11 +542,12 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (warp == 0) {
     if (lane == 0) {
-      tc::mbar_expect_tx(q_full, (uint32_t)(n_mine * kPfBQ * 128));
-      for (int x = 0; x < n_mine; ++x)
+      const int n_q = split ? 1 : n_mine;
+      tc::mbar_expect_tx(q_full, (uint32_t)(n_q * kPfBQ * 128));
+      for (int x = 0; x < n_q; ++x)
         tc::tma_load_2d(smem + L.q + x * kPfBQ * 128, &map_q, it_head[x] * hd, tok0 + it_q0[x],
                         q_full);
-      for (int j = 0, s = 0, turn = 0; j < n_steps; ++j, s = s + 1 == kPpStages ? 0 : s + 1,
+      for (int j = 0, s = 0, turn = 0; j < n_steps; ++j, s = s + 1 == n_stages ? 0 : s + 1,
                turn += s == 0) {
         if (turn > 0 && !tc::mbar_wait(&kv_empty[s], (uint32_t)((turn - 1) & 1), abort)) break;
         tc::mbar_expect_tx(&kv_full[s], (uint32_t)(2 * kPfBK * 128));
@@ -558,7 +575,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t t_s = tmem + (uint32_t)x * kColTile + kColS;
       const uint32_t t_p = tmem + (uint32_t)x * kColTile + kColP;
       const uint32_t t_o = tmem + (uint32_t)x * kColTile + kColO;
-      const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + x * kPfBQ * 128);
+      const int offset = split ? x : 0;
+      const uint64_t qd = tc::smem_desc_k_sw128(smem + L.q + (split ? 0 : x) * kPfBQ * 128);
       const uint64_t kd0 = tc::smem_desc_k_sw128(smem + L.k);
       const uint64_t vd0 = smem_desc_mn_sw128(smem + L.v, (uint32_t)(kPfBK * 128));
       constexpr uint64_t kStage = (uint64_t)((kPfBK * 128) >> 4);    // a stage, in descriptor units
@@ -568,35 +586,36 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       auto landed = [&](int j) {            // wait (once) for the stage of step j
         while (ok && ready < j) {
           ++ready;
-          ok = tc::mbar_wait(&kv_full[ready % kPpStages], (uint32_t)((ready / kPpStages) & 1), abort);
+          ok = tc::mbar_wait(&kv_full[ready % n_stages], (uint32_t)((ready / n_stages) & 1), abort);
         }
         tc::tc_fence_after();
         return ok;
       };
-      auto scores = [&](int j, int h) {     // S_x[:, 64 h ..] = Q_x K_j[64 h ..]^T
-        const uint64_t kd = kd0 + (uint64_t)(j % kPpStages) * kStage + (uint64_t)h * kHalf;
+      auto scores = [&](int g, int h) {     // S_x[:, 64 h ..] = Q_x K_g[64 h ..]^T, g a ring step
+        const uint64_t kd = kd0 + (uint64_t)(g % n_stages) * kStage + (uint64_t)h * kHalf;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           if (kk < k_steps)
             tc::umma_bf16(t_s + (uint32_t)(h * kPfBlk), qd + 2 * kk, kd + 2 * kk, idesc_qk, kk != 0);
       };
-      auto product = [&](int j, int h) {    // O_x (+)= P_x[:, 64 h ..] V_j[64 h ..]
-        const uint64_t vd = vd0 + (uint64_t)(j % kPpStages) * kStage;
+      auto product = [&](int g, int i, int h) {    // O_x (+)= P_x[:, 64 h ..] V_g[64 h ..]
+        const uint64_t vd = vd0 + (uint64_t)(g % n_stages) * kStage;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           const int kk = h * 4 + k4;
           tc::umma_bf16_a_tmem(t_o, t_p + (uint32_t)(kk * 8), vd + (uint64_t)(kk * 128), idesc_pv,
-                               (j | kk) != 0);
+                               (i | kk) != 0);
         }
       };
-      if (ok && steps > 0 && landed(0)) {
-        scores(0, 0);
+      if (ok && steps > 0 && landed(offset)) {
+        scores(offset, 0);
         tc::umma_commit(&s_full[2 * x]);
-        scores(0, 1);
+        scores(offset, 1);
         tc::umma_commit(&s_full[2 * x + 1]);
       }
-      for (int j = 0; j < n_steps && ok; ++j) {
-        if (j < steps) {
+      for (int g = 0; g < n_steps && ok; ++g) {
+        const int j = (g - offset) / stride;       // the slot's own step, if the ring's is its
+        if (g >= offset && j * stride + offset == g && j < steps) {
           // A step's keys go in two halves of 64.  When the tile's threads have written the P
           // of a half, its product is issued and then the same half of the next step's
           // scores (that half of S has been read for the last time); one commit tells the
@@ -607,17 +626,18 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             ok = tc::mbar_wait(&p_full[2 * x + h], (uint32_t)(j & 1), abort);
             if (!ok) break;
             tc::tc_fence_after();
-            product(j, h);
-            if (j + 1 < steps && landed(j + 1)) scores(j + 1, h);
+            product(g, j, h);
+            if (j + 1 < steps && landed(g + stride)) scores(g + stride, h);
             tc::umma_commit(&s_full[2 * x + h]);
           }
           if (!ok) break;
-          tc::umma_commit(&kv_empty[j % kPpStages]);         // this tile is done with the stage
+          tc::umma_commit(&kv_empty[g % n_stages]);          // this slot is done with the stage
           if (j + 1 == steps) tc::umma_commit(&pv_done[x]);
-        } else if (landed(j)) {
-          // a tile with fewer steps (or none) has no use for the stage: it says so once the
-          // stage has been filled, which keeps its arrivals in step with the ring's turns
-          tc::mbar_arrive(&kv_empty[j % kPpStages]);
+        } else if (landed(g)) {
+          // a slot that has no use for the stage (the other's turn, or its tile has fewer
+          // steps) says so once the stage has been filled, which keeps its arrivals in step
+          // with the ring's turns
+          tc::mbar_arrive(&kv_empty[g % n_stages]);
         }
       }
     }
@@ -649,12 +669,13 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     };
+    const int offset = split ? x : 0;
     for (int hs = 0; hs < 2 * steps; ++hs) {
-      const int j = hs >> 1, h = hs & 1;
+      const int j = hs >> 1, h = hs & 1;       // the slot's own step and the half of its keys
       // the scores of this half are there, and the product that read the half's last P is done
       ok = tc::mbar_wait(&s_full[2 * x + h], (uint32_t)(j & 1), abort) && ok;
       tc::tc_fence_after();
-      const int key0 = hs * kPfBlk;
+      const int key0 = ((j * stride + offset) * 2 + h) * kPfBlk;
       const bool masked = key0 + kPfBlk - 1 > pos_first;     // the half reaches the diagonal
       // One pass over the scores: p = 2^(s * scale - ref) with `ref` the reference the row
       // already has, the half's maximum found on the way.  As long as no score exceeds the
@@ -735,10 +756,30 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       tc::tc_fence_before();                  // this half's reads of S are done
       tc::mbar_arrive(&p_full[2 * x + h]);
     }
-    if (steps > 0) {
+    if (split && x == 1) {
+      // the other slot's threads read this one's output from tensor memory; they need the
+      // reference and the sum that go with it
+      if (steps > 0) ok = tc::mbar_wait(&pv_done[1], 0u, abort) && ok;
+      reinterpret_cast<float2*>(smem + L.xch)[row] = make_float2(m, l);
+      tc::tc_fence_before();
+      tc::mbar_arrive(xch_full);
+    } else if (steps > 0) {
       ok = tc::mbar_wait(&pv_done[x], 0u, abort) && ok;
+      float w0 = 1.0f, w1 = 0.f;             // weights of the two slots' outputs (split)
+      if (split) {
+        ok = tc::mbar_wait(xch_full, 0u, abort) && ok;
+        const float2 other = reinterpret_cast<const float2*>(smem + L.xch)[row];
+        if (other.x != -INFINITY) {          // (slot 0 always has keys: its reference is finite)
+          const float mm = fmaxf(m, other.x);
+          w0 = fast_exp2(m - mm);
+          w1 = fast_exp2(other.x - mm);
+        }
+        l = l * w0 + other.y * w1;
+      }
       tc::tc_fence_after();
       const float inv = 1.0f / l;
+      w0 *= inv;
+      w1 *= inv;
       __nv_bfloat16* orow = out + (size_t)(tok0 + it_q0[x] + row) * ldo + (size_t)it_head[x] * hd;
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -746,13 +787,23 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           uint32_t r[32];
           tc::tmem_load_32(o_addr + (uint32_t)c0, r);
           tc::tmem_load_wait();
+          float v32[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v32[e] = __uint_as_float(r[e]) * w0;
+          if (split && __any_sync(0xffffffffu, w1 != 0.f)) {   // (a load all lanes take)
+            tc::tmem_load_32(o_addr + kColTile + (uint32_t)c0, r);
+            tc::tmem_load_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (w1 != 0.f) v32[e] = fmaf(__uint_as_float(r[e]), w1, v32[e]);
+          }
           if (ok && row_valid) {
 #pragma unroll
             for (int d = 0; d < 32; d += 8) {
               if (c0 + d < hd) {
                 float v[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[d + e]) * inv;
+                for (int e = 0; e < 8; ++e) v[e] = v32[d + e];
                 store8(orow + c0 + d, v);
               }
             }
@@ -776,12 +827,13 @@ using namespace cretif;
 
 // Tuning aid: a device buffer of 8 x 16 timestamps that the next launches fill (see the kernel).
 static unsigned long long* g_pf_stamps = nullptr;
-// Two query tiles per CTA: -1 where the launcher sees fit, 0 never, 1 wherever the kernel
-// takes the shape (for tests that run both).
+// Which kernel takes head sizes up to 64 without a window (for tests that run all): -1 as the
+// launcher sees fit, 0 the kernel with two threads per row, 1 a thread per row and two query
+// tiles per CTA, 2 a thread per row and one tile whose key steps the CTA's two slots share.
 static int g_pf_pairing = -1;
 extern "C" int cretif_set_prefill_pairing(int mode) {
   const int was = g_pf_pairing;
-  g_pf_pairing = mode < 0 ? -1 : (mode > 0 ? 1 : 0);
+  g_pf_pairing = mode < 0 ? -1 : (mode > 2 ? 2 : mode);
   return was;
 }
 #ifdef CRETIF_STAMPS
@@ -823,11 +875,12 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
-  // Two query tiles per CTA (a thread per row, P and O in tensor memory) where pairs still
-  // spread over the chip: head sizes up to 64, no window.
+  // The kernel with a thread per row (P and O in tensor memory) for head sizes up to 64 without
+  // a window: two query tiles per CTA where pairs still spread over the chip, else one tile
+  // per CTA with its key steps split between the CTA's two slots.
   const int group = nh / nkv;
   const long long n_qt = (max_new + kPfBQ - 1) / kPfBQ;
-  const long long pairs = (n_qt * group + 1) / 2;
+  const long long items = n_qt * group, pairs = (items + 1) / 2;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
@@ -835,9 +888,10 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const bool paired = g_pf_pairing != 0 && hd <= 64 && window == 0 && pairs <= 65535 &&
-                      (g_pf_pairing > 0 || 5 * pairs * nkv * B >= 7LL * sm_count);
-  if (paired) {
+  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535;
+  const bool paired = rows_ok && (g_pf_pairing == 1 ||
+                                  (g_pf_pairing < 0 && 5 * pairs * nkv * B >= 7LL * sm_count));
+  if (rows_ok) {
     const PpSmem P;
     static int configured_pair = 0;
     if (!configured_pair) {
@@ -846,13 +900,13 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
       if (e != cudaSuccess) return (int)e;
       configured_pair = 1;
     }
-    cfg.gridDim = dim3(nkv, B, (unsigned)pairs);
+    cfg.gridDim = dim3(nkv, B, (unsigned)(paired ? pairs : items));
     cfg.blockDim = dim3(kPpThreads);
     cfg.dynamicSmemBytes = P.total;
-    count_variant(kVarPrefillAttnPair);
+    count_variant(paired ? kVarPrefillAttnPair : kVarPrefillAttnSplit);
     e = cudaLaunchKernelEx(&cfg, attn_prefill_pair_kernel, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, fault);
+                           seq_slot, nh, nkv, hd, scale_log2, paired ? 0 : 1, fault);
     return e == cudaSuccess ? launch_status() : (int)e;
   }
   count_variant(kVarPrefillAttn);

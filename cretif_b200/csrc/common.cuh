@@ -148,6 +148,7 @@ enum Variant : int {
   kVarTcSeveralTiles,       // ... whose persistent CTAs walk more than one tile
   kVarTc192,                // ... 192 columns wide
   kVarPrefillAttnPair,      // tcgen05 prefill attention, a thread per row, two query tiles per CTA
+  kVarPrefillAttnSplit,     // ... one tile per CTA, its key steps split between two slots
   kVarCount
 };
 void count_variant(int v);

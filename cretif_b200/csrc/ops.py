@@ -49,7 +49,8 @@ def launch_count() -> int:
 
 _VARIANTS = ("fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4", "stream",
              "stream_row_groups", "decode_cluster", "decode_split", "prefill_attn", "tc64",
-             "tc128", "tc256", "tc_several_tiles", "tc192", "prefill_attn_pair")
+             "tc128", "tc256", "tc_several_tiles", "tc192", "prefill_attn_pair",
+             "prefill_attn_split")
 
 
 def variant_counts() -> dict:
@@ -586,10 +587,10 @@ def gemm_tc_qkv_rope(x, w_qkv, q_out, cos, sin, pairing: int, nh: int, nkv: int,
 
 
 def set_prefill_pairing(mode: int) -> int:
-    """(For tests that run both.)  Which prefill attention kernel takes head sizes up to 64
+    """(For tests that run all.)  Which prefill attention kernel takes head sizes up to 64
     without a window: -1 as the launcher sees fit (the default), 0 the kernel with two threads
-    per row, 1 the one with a thread per row and two query tiles per CTA wherever it takes
-    the shape.  Returns the old setting."""
+    per row, 1 a thread per row and two query tiles per CTA, 2 a thread per row and one tile
+    per CTA whose key steps two groups of warps share.  Returns the old setting."""
     return int(lib().cretif_set_prefill_pairing(int(mode)))
 
 

@@ -11,7 +11,8 @@
 The last test checks, from the kernels' own launch counts, that every variant bench.py's
 numbers come from (row groups, shared norm prologue, streaming ring, the cluster merge
 of the decode attention, the persistent tensor-core product, the tensor-core prefill
-attention with one and with two query tiles per CTA) ran under one of these comparisons.
+attention with a CTA's two groups of warps on one query tile and on two) ran under one of
+these comparisons.
 """
 import numpy as np
 import pytest
@@ -219,6 +220,6 @@ def test_every_path_the_benchmark_times_was_compared():
     now = ops.variant_counts()
     ran = {k for k, v in now.items() if v > _counts_at_start.get(k, 0)}
     needed = {"fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4",
-              "stream", "stream_row_groups", "decode_cluster", "prefill_attn",
+              "stream", "stream_row_groups", "decode_cluster", "prefill_attn_split",
               "prefill_attn_pair", "tc64", "tc128", "tc192", "tc_several_tiles"}
     assert needed <= ran, sorted(needed - ran)

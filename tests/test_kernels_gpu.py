@@ -568,12 +568,14 @@ PREFILL_CASES = [  # nh, nkv, hd, lens (cached + new), new tokens per sequence
 ]
 
 
-@pytest.fixture(params=[0, 1], ids=["two-threads-per-row", "thread-per-row-two-tiles"])
+@pytest.fixture(params=[0, 1, 2], ids=["two-threads-per-row", "thread-per-row-two-tiles",
+                                       "thread-per-row-split-keys"])
 def prefill_pairing(request, ops):
     """The tensor-core prefill attention has a kernel with two threads per row of a tile of 128
     queries (every head size, windows), and one with a thread per row that keeps P and O in
-    tensor memory and gives a CTA two tiles that share a key/value head (head sizes up to 64,
-    no window); a launch chooses by its shape.  Tests run both."""
+    tensor memory (head sizes up to 64, no window); that one gives a CTA two tiles that share
+    a key/value head, or one tile whose key steps its two groups of warps take in turns and
+    merge at the end.  A launch chooses by its shape; tests run all three."""
     old = ops.set_prefill_pairing(request.param)
     yield request.param
     ops.set_prefill_pairing(old)
@@ -606,9 +608,10 @@ def test_attn_prefill_tc(ops, prefill_pairing, nh, nkv, hd, lens, news, window):
     torch.cuda.synchronize()
     assert fault.item() == 0
     now = ops.variant_counts()
-    took = [k for k in ("prefill_attn", "prefill_attn_pair") if now[k] > before[k]]
+    names = ("prefill_attn", "prefill_attn_pair", "prefill_attn_split")
+    took = [k for k in names if now[k] > before[k]]
     rows = window == 0 and hd <= 64
-    assert took == [("prefill_attn", "prefill_attn_pair")[prefill_pairing if rows else 0]]
+    assert took == [names[prefill_pairing if rows else 0]]
     for b, n in enumerate(lens):
         k, v = cache.keys(b, n)
         q = qkv[cu[b]:cu[b + 1], :nh * hd].double().cpu().reshape(news[b], nh, hd)

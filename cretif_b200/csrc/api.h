@@ -58,6 +58,10 @@ int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N
 // chooses per launch.  Returns the old setting.
 int cretif_set_tc_epilogue_warps(int n);
 
+// (For tests that run both.)  Adding into a float32 matrix through TMA (wide tiles, eight
+// epilogue warps): on by default.  Returns the old setting.
+int cretif_set_tc_bulk_add(int on);
+
 // The same product with fused epilogues (see gemm_tc.cu): SiLU·mul for the stacked gate|up
 // matrix whose rows are interleaved in blocks of 64 (I % 64 == 0), and rotary + cache write for
 // the stacked q|k|v matrix (head_dim 64 or 128, rotary over the whole head).

@@ -149,6 +149,7 @@ enum Variant : int {
   kVarTc192,                // ... 192 columns wide
   kVarPrefillAttnPair,      // tcgen05 prefill attention, a thread per row, two query tiles per CTA
   kVarPrefillAttnSplit,     // ... one tile per CTA, its key steps split between two slots
+  kVarTcBulkAdd,            // tcgen05 product added into a float32 matrix through TMA
   kVarCount
 };
 void count_variant(int v);

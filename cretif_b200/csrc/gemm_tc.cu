@@ -45,8 +45,12 @@ struct TcSmem {
   static constexpr int kATile = kTcBM * kTcBK * 2;
   static constexpr int kBTile = BN * kTcBK * 2;
   static constexpr int kStage = kATile + kBTile;
-  static constexpr int total(int stages) {     // barriers behind the stages, + align slack
-    return stages * kStage + (2 * kTcMaxStages + 4) * 8 + 16 + 1024;
+  // Staging for the epilogue that adds its tile into a float32 matrix through TMA: each of
+  // the two groups of four warps has two slabs of 128 rows x 32 columns.
+  // (The SiLU epilogue stores its tile the same way: two slabs of 128 rows x 64 bfloat16.)
+  static constexpr int kSlab = kTcBM * 128;
+  static constexpr int total(int stages, int slabs = 0) {   // stages, staging, barriers, align slack
+    return stages * kStage + slabs * kSlab + (2 * kTcMaxStages + 4) * 8 + 16 + 1024;
   }
   // Tensor memory is handed out in powers of two columns; the two accumulators lie at
   // columns 0 and BN of the allocation.
@@ -57,6 +61,10 @@ struct TcSmem {
       stages = num_kb < kTcMaxStages ? (num_kb < 3 ? 3 : num_kb) : kTcMaxStages;
       while (stages > 3 && total(stages) > 200 * 1024) --stages;
     }
+    return stages;
+  }
+  static int stages_with_staging(int stages, int slabs) {
+    while (stages > 2 && total(stages, slabs) > 227 * 1024) --stages;
     return stages;
   }
 };
@@ -72,6 +80,7 @@ enum TcEpilogue : int { kTcStore = 0, kTcSilu = 1, kTcRope = 2 };
 
 struct TcEpi {
   void* C; int ldc, accumulate;                            // store
+  int bulk;        // through TMA (map_c): the float32 add of kTcStore, the store of kTcSilu
   __nv_bfloat16* act; int I;                               // silu
   __nv_bfloat16* Q; int ldq;                               // rope
   const float* cos_t; const float* sin_t;
@@ -89,7 +98,8 @@ __device__ __forceinline__ float round_bf16(float x) {
 template <int BN, int EPI, typename TC, int EW>
 __global__ void __launch_bounds__(tc_threads(EW))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const TcEpi ep, int M, int N, int K, unsigned int* __restrict__ fault,
+               const __grid_constant__ CUtensorMap map_c, const TcEpi ep, int M, int N, int K,
+               unsigned int* __restrict__ fault,
                int kTcStages, unsigned long long* stamps, int n_n_tiles, int n_tiles) {
   // Tuning aid: with a buffer given, lane 0 of each warp of the first CTA notes the time at
   // which it passes the phases of its first tile: [warp][8] nanoseconds.
@@ -108,7 +118,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TcSmem<BN>;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kTcStages * L::kStage);
+  constexpr bool kBulk = EPI == kTcStore && sizeof(TC) == 4 && EW == 8 && BN >= 192;
+  constexpr bool kBulkSilu = EPI == kTcSilu && EW == 8 && BN == 256;
+  constexpr int kSlabs = kBulk ? 4 : (kBulkSilu ? 2 : 0);
+  unsigned char* staging = smem + kTcStages * L::kStage;
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (kSlabs && ep.bulk ? kSlabs * L::kSlab : 0));
   uint64_t* empty = full + kTcMaxStages;
   uint64_t* acc_full = empty + kTcMaxStages;       // two accumulators in tensor memory
   uint64_t* acc_empty = acc_full + 2;
@@ -223,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     stamp(2);
     Tile t = first;
     bool alive = true;
+    uint32_t slabs = 0;                      // slabs this group has handed to TMA so far
     for (int i = 0; i < my_tiles; ++i, next(t)) {
       const int buf = i & 1;
       const int m0 = t.mt * kTcBM, n0 = t.nt * BN;
@@ -287,7 +302,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc::tc_fence_after();
       if (i == 0) stamp(3);
       const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
-      if (ok && EPI == kTcStore) {
+      if (kBulk && ep.bulk) {
+        // The tile is added into the float32 matrix by TMA: a row per thread would touch 32
+        // different lines with every load and store, and the old values would pass through
+        // the SM at all.  Each group of four warps (128 rows, half of the columns) writes a
+        // slab of 32 columns into shared memory in the 128-byte swizzle (eight 16-byte stores
+        // a thread, conflict-free), one thread hands it to the copy engine, which adds it in
+        // L2 and clips it at the matrix's edges; two slabs a group, so that one is filled
+        // while the other drains.
+        unsigned char* mine = staging + chalf * 2 * L::kSlab;
+        const bool elected = ((warp - 2) & 3) == 0 && lane == 0;
+        const int row = quad * 32 + lane;
+#pragma unroll 1
+        for (int c0 = c_first; c0 < c_first + kCols; c0 += 32, ++slabs) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          if (elected) tc::bulk_wait_group_read<1>();       // the slab used two slabs ago is free
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
+          unsigned char* slab = mine + (slabs & 1) * L::kSlab;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(slab + row * 128 + ((j ^ (row & 7)) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          tc::fence_proxy_async();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
+          if (elected) {                   // (a group for every slab, or the count above is off)
+            if (ok && n0 + c0 < N) tc::tma_reduce_add_2d(&map_c, slab, n0 + c0, m0);
+            tc::bulk_commit_group();
+          }
+        }
+      } else if (ok && EPI == kTcStore) {
 #pragma unroll 1
         for (int c0 = c_first; c0 < c_first + kCols; c0 += 32) {
           uint32_t r[32];
@@ -330,7 +375,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
-      if (ok && EPI == kTcSilu) {
+      if (kBulkSilu && ep.bulk) {
+        // act = silu(gate) * up leaves through shared memory and TMA as well: the two groups
+        // fill the halves of a slab of 128 rows x 64 columns (a thread's 32 values are four
+        // 16-byte pieces of its row's 128-byte line), one thread hands it over.
+        const bool elected = warp == 2 && lane == 0;
+        const int row = quad * 32 + lane;
+#pragma unroll 1
+        for (int pair = 0; pair < BN / 128; ++pair, ++slabs) {
+          const int col0 = (n0 >> 1) + pair * 64;
+          const int c0 = chalf * 32;
+          uint32_t g[32], u[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + c0), g);
+          tc::tmem_load_32(lane_acc + (uint32_t)(pair * 128 + 64 + c0), u);
+          tc::tmem_load_wait();
+          if (elected) tc::bulk_wait_group_read<1>();
+          asm volatile("bar.sync 3, 256;" ::: "memory");
+          unsigned char* slab = staging + (slabs & 1) * L::kSlab;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const float g0 = round_bf16(__uint_as_float(g[j + e]));
+              const float g1 = round_bf16(__uint_as_float(g[j + e + 1]));
+              const float u0 = round_bf16(__uint_as_float(u[j + e]));
+              const float u1 = round_bf16(__uint_as_float(u[j + e + 1]));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_bf16_path(g0) * u0,
+                                                        silu_bf16_path(g1) * u1);
+              w4[e >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            const int piece = chalf * 4 + (j >> 3);
+            *reinterpret_cast<uint4*>(slab + row * 128 + ((piece ^ (row & 7)) << 4)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+          tc::fence_proxy_async();
+          asm volatile("bar.sync 3, 256;" ::: "memory");
+          if (elected) {
+            if (ok && col0 < ep.I) tc::tma_store_2d(&map_c, slab, col0, m0);
+            tc::bulk_commit_group();
+          }
+        }
+      } else if (ok && EPI == kTcSilu) {
         // every 128 tile columns are 64 gate columns and the 64 up columns that belong to
         // them: act[:, n0/2 + 64 pair ..]
 #pragma unroll 1
@@ -469,6 +555,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc::tc_fence_before();
       tc::mbar_arrive(&acc_empty[buf]);        // this accumulator may be overwritten
     }
+    if (kSlabs && ep.bulk && ((warp - 2) & 3) == 0 && lane == 0) tc::bulk_wait_all();
   }
   stamp(4);
   if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
@@ -569,6 +656,9 @@ int make_tile_map_bf16(CUtensorMap* map, const void* base, int rows, int cols, i
 static unsigned long long* g_tc_stamps = nullptr;
 // Epilogue warps: 0 chooses per launch, 4 or 8 force (for tests that run both).
 static int g_tc_epilogue_warps = 0;
+// Epilogues through shared memory and TMA (the float32 add, the SiLU store) where the kernel
+// can: 1 (default), 0 never (for tests that run both).
+static int g_tc_bulk_add = 1;
 
 // Registers of a thread of the kernel, for the residency estimate (once per instantiation).
 template <int BN, int EPI, typename TC, int EW>
@@ -585,7 +675,8 @@ static int tc_regs_per_thread() {
 template <int BN, int EPI, typename TC, int EW>
 static cudaError_t launch_tc_kernel(const cudaLaunchConfig_t& cfg, int smem,
                                     const CUtensorMap& map_a, const CUtensorMap& map_w,
-                                    const TcEpi& ep, int M, int N, int K, unsigned int* fault,
+                                    const CUtensorMap& map_c, const TcEpi& ep, int M, int N, int K,
+                                    unsigned int* fault,
                                     int stages, unsigned long long* stamps, int n_n_tiles,
                                     int tiles) {
   static int configured = 0;
@@ -595,14 +686,15 @@ static cudaError_t launch_tc_kernel(const cudaLaunchConfig_t& cfg, int smem,
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC, EW>, map_a, map_w, ep, M, N, K, fault,
-                            stages, stamps, n_n_tiles, tiles);
+  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC, EW>, map_a, map_w, map_c, ep, M, N, K,
+                            fault, stages, stamps, n_n_tiles, tiles);
 }
 
 template <int BN, int EPI, typename TC>
-static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N, int K, int lda,
+static int launch_tc(const void* A, const void* W, const TcEpi& ep_in, int M, int N, int K, int lda,
                      int ldw, unsigned int* fault, cudaStream_t st) {
-  CUtensorMap map_a, map_w;
+  TcEpi ep = ep_in;
+  CUtensorMap map_a, map_w, map_c = {};
   if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
   if (make_tile_map_bf16(&map_w, W, N, K, ldw, BN)) return kBadArgument;
   static int sm_count = 0;
@@ -615,8 +707,8 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   const int n_n_tiles = (N + BN - 1) / BN;
   const long long tiles = (long long)n_n_tiles * ((M + kTcBM - 1) / kTcBM);
   if (tiles > 0x7fffffffLL) return kBadArgument;
-  const int stages = TcSmem<BN>::stages_for(tiles, (K + kTcBK - 1) / kTcBK, sm_count);
-  const int smem = TcSmem<BN>::total(stages);
+  int stages = TcSmem<BN>::stages_for(tiles, (K + kTcBK - 1) / kTcBK, sm_count);
+  int smem = TcSmem<BN>::total(stages);
   // Persistent CTAs: as many as fit the chip at once (by shared memory and by the 512 columns
   // of tensor memory, of which a CTA holds two accumulators), each walking its share of tiles.
   // Eight epilogue warps where CTAs walk several tiles: a tile's epilogue (a read-modify-write
@@ -640,6 +732,23 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   int epi_warps = g_tc_epilogue_warps;
   if (epi_warps != 4 && epi_warps != 8)
     epi_warps = tiles > 2LL * residents(4) * sm_count && K <= 4096 ? 8 : 4;
+  // The float32 add through TMA (eight epilogue warps, wide tiles) needs room for its slabs.
+  ep.bulk = 0;
+  if (EPI == kTcStore && sizeof(TC) == 4 && ep.accumulate && epi_warps == 8 && BN >= 192 &&
+      g_tc_bulk_add && ep.ldc % 4 == 0 && ((uintptr_t)ep.C & 15) == 0 &&
+      make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true) == 0) {
+    ep.bulk = 1;
+    stages = TcSmem<BN>::stages_with_staging(stages, 4);
+    smem = TcSmem<BN>::total(stages, 4);
+    count_variant(kVarTcBulkAdd);
+  }
+  if (EPI == kTcSilu && epi_warps == 8 && BN == 256 && g_tc_bulk_add &&
+      make_box_map(&map_c, ep.act, M, ep.I, ep.I, kTcBM, 64, true, false) == 0) {
+    ep.bulk = 1;
+    stages = TcSmem<BN>::stages_with_staging(stages, 2);
+    smem = TcSmem<BN>::total(stages, 2);
+    count_variant(kVarTcBulkAdd);
+  }
   const int per_sm = residents(epi_warps);
   const long long resident = (long long)per_sm * sm_count;
   const dim3 grid((unsigned)(tiles < resident ? tiles : resident));
@@ -656,10 +765,12 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep, int M, int N
   count_variant(BN == 64 ? kVarTc64 : BN == 128 ? kVarTc128 : BN == 192 ? kVarTc192 : kVarTc256);
   if (tiles > resident) count_variant(kVarTcSeveralTiles);
   const cudaError_t e =
-      epi_warps == 8 ? launch_tc_kernel<BN, EPI, TC, 8>(cfg, smem, map_a, map_w, ep, M, N, K, fault,
-                                                        stages, g_tc_stamps, n_n_tiles, (int)tiles)
-                     : launch_tc_kernel<BN, EPI, TC, 4>(cfg, smem, map_a, map_w, ep, M, N, K, fault,
-                                                        stages, g_tc_stamps, n_n_tiles, (int)tiles);
+      epi_warps == 8 ? launch_tc_kernel<BN, EPI, TC, 8>(cfg, smem, map_a, map_w, map_c, ep, M, N, K,
+                                                        fault, stages, g_tc_stamps, n_n_tiles,
+                                                        (int)tiles)
+                     : launch_tc_kernel<BN, EPI, TC, 4>(cfg, smem, map_a, map_w, map_c, ep, M, N, K,
+                                                        fault, stages, g_tc_stamps, n_n_tiles,
+                                                        (int)tiles);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 
@@ -671,6 +782,12 @@ static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, 
 }  // namespace cretif
 
 using namespace cretif;
+
+extern "C" int cretif_set_tc_bulk_add(int on) {
+  const int was = g_tc_bulk_add;
+  g_tc_bulk_add = on ? 1 : 0;
+  return was;
+}
 
 extern "C" int cretif_set_tc_epilogue_warps(int n) {
   const int was = g_tc_epilogue_warps;

@@ -50,7 +50,7 @@ def launch_count() -> int:
 _VARIANTS = ("fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4", "stream",
              "stream_row_groups", "decode_cluster", "decode_split", "prefill_attn", "tc64",
              "tc128", "tc256", "tc_several_tiles", "tc192", "prefill_attn_pair",
-             "prefill_attn_split")
+             "prefill_attn_split", "tc_bulk_add")
 
 
 def variant_counts() -> dict:
@@ -584,6 +584,12 @@ def gemm_tc_qkv_rope(x, w_qkv, q_out, cos, sin, pairing: int, nh: int, nkv: int,
         _p(tok_pos), _p(tok_seq), _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc),
         block_tokens, int(write_cache), M, K, _rows(x, "x"), _rows(w_qkv, "w_qkv"),
         _p(fault_word(x.device)), _stream()), "gemm_tc_qkv_rope")
+
+
+def set_tc_bulk_add(on: bool) -> bool:
+    """(For tests that run both.)  Whether the tensor-core product adds into a float32 matrix
+    through TMA where it can (the default).  Returns the old setting."""
+    return bool(lib().cretif_set_tc_bulk_add(1 if on else 0))
 
 
 def set_prefill_pairing(mode: int) -> int:

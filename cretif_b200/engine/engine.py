@@ -129,7 +129,7 @@ class Engine:
         # ones are dropped.  Indices, slots and positions are read from a fixed device buffer
         # that is refreshed before each replay, so a captured step serves any sequences.
         self.step_graphs = step_graphs and self.model.graph_safe
-        self.graph_max_tokens = 8192
+        self.graph_max_tokens = 32768                # a captured step pins its activations
         self.graph_max_logit_bytes = 128 << 20       # a captured step pins its logits
         self.max_step_graphs = 16
         self._graphs = collections.OrderedDict()

@@ -119,11 +119,24 @@ def test_gemm_tc(ops, tc_epilogue, M, N, K, bn):
     torch.cuda.synchronize()
     assert fault.item() == 0
     close(c, want, 1e-5)
-    base = rnd(M, ldc, seed=3)[:, :N]
-    c2 = torch.empty((M, ldc), device=DEV)[:, :N]
-    c2.copy_(base)
-    ops.gemm_tc(x, w, c2, accumulate=True, bn=bn)
-    close(c2, base.double() + want, 1e-5)
+    # added into a float32 matrix: by the epilogue's threads, and (wide tiles, eight epilogue
+    # warps, a row pitch of whole 16 bytes) through TMA, which clips the tile at both edges;
+    # what lies beside the matrix in its rows' padding stays as it is
+    base = rnd(M, ldc, seed=3)
+    for bulk in (False, True):
+        old = ops.set_tc_bulk_add(bulk)
+        before = ops.variant_counts()["tc_bulk_add"]
+        full = base.clone()
+        c2 = full[:, :N]
+        ops.gemm_tc(x, w, c2, accumulate=True, bn=bn)
+        ops.set_tc_bulk_add(old)
+        close(c2, base[:, :N].double() + want, 1e-5)
+        assert torch.equal(full[:, N:], base[:, N:])
+        took = ops.variant_counts()["tc_bulk_add"] > before
+        if bn in (192, 256):
+            assert took == (bulk and tc_epilogue == 8 and ldc % 4 == 0)
+        else:
+            assert not took or bulk
     cb = torch.empty((M, ldc), device=DEV, dtype=torch.bfloat16)[:, :N]
     ops.gemm_tc(x, w, cb, bn=bn)
     close(cb, want, 5e-3)
@@ -319,15 +332,18 @@ def test_gemm_tc_silu(ops, tc_epilogue, M, I, K):
     gate = rnd(I, K, dtype=torch.bfloat16, seed=1, scale=0.3)
     up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
     w = _interleave(gate, up)
-    act = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
     fault = ops.fault_word(DEV)
     fault.zero_()
-    ops.gemm_tc_silu(x, w, act)
-    torch.cuda.synchronize()
-    assert fault.item() == 0
     g = (x.double() @ gate.double().T).to(torch.bfloat16).double()
     u = (x.double() @ up.double().T).to(torch.bfloat16).double()
-    close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
+    for bulk in (False, True):       # stored by the epilogue's threads, and through TMA
+        old = ops.set_tc_bulk_add(bulk)
+        act = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_tc_silu(x, w, act)
+        ops.set_tc_bulk_add(old)
+        torch.cuda.synchronize()
+        assert fault.item() == 0
+        close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
     # the few-token kernel reads the same interleaved matrix
     h, nw = rnd(8, K), rnd(K, seed=3) * 0.1 + 1
     a2 = torch.empty(8, I, device=DEV, dtype=torch.bfloat16)

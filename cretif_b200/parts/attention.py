@@ -91,7 +91,9 @@ class Attention(Part):
     def cache_request(self):
         return KVRequest(self.nkv, self.hd, self.window)
 
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, into=None):
+        """``into``: a float32 matrix that the output is added to (the residual stream) instead
+        of being returned."""
         from .linear import plain_forced, skinny_max_rows
         kv = cache.kv
         rot = getattr(self.position, "rotary_table", None)
@@ -119,11 +121,22 @@ class Attention(Part):
                                        ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k,
                                        kv.v, kv.block_tokens, True, ctx.fault)
             self.attend(qkv, o, ctx, kv)
+        if into is not None:
+            linear(o, self.w_o, out=into, accumulate=True)
+            return None
         return linear(o, self.w_o, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx, cache) -> bool:
-        """Few tokens, bfloat16: norm + q|k|v + rotary + cache write in one kernel, attention,
-        then the output projection added into ``h``.  False if the step does not qualify."""
+        """bfloat16.  Few tokens: norm + q|k|v + rotary + cache write in one kernel, attention,
+        then the output projection added into ``h``.  Many tokens: the same through the norm's
+        kernel and the tensor-core products.  False if the step does not qualify."""
+        if (ctx.T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not _force_plain
+                and h.dtype == torch.float32 and h.is_contiguous()):
+            # many tokens: the norm's own kernel, then the products; the last one adds its
+            # float32 accumulators into the residual stream, so that no delta is written, read
+            # again and added by the next norm
+            self.forward(norm.forward(h, None), ctx, cache, into=h)
+            return True
         rms = getattr(norm, "rms_params", None)
         rot = getattr(self.position, "rotary_table", None)
         if (_force_plain or not fused_steps_enabled() or self.dtype != torch.bfloat16

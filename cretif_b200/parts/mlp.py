@@ -50,7 +50,9 @@ class GatedMLP(Part):
             self.w_gate_up = self._matrix(torch.cat([gate, up], dim=0))
         self.w_down = self._matrix(tensors["down"])
 
-    def forward(self, x, ctx):
+    def forward(self, x, ctx, into=None):
+        """``into``: a float32 matrix that the output is added to (the residual stream) instead
+        of being returned."""
         T = x.shape[0]
         act = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
         if (self.gu_block == 64 and T > SKINNY_ROWS() and not plain_forced()
@@ -59,13 +61,22 @@ class GatedMLP(Part):
         else:
             gu = linear(x, self.w_gate_up)                            # [T, 2 I]
             ops.silu_mul(gu, act, self.gu_block)
+        if into is not None:
+            linear(act, self.w_down, out=into, accumulate=True)
+            return None
         return linear(act, self.w_down, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx) -> bool:
-        """Few tokens, bfloat16: norm + gate|up + SiLU·mul in one kernel, then the down
-        projection added into ``h``.  False if the step does not qualify."""
+        """bfloat16.  Few tokens: norm + gate|up + SiLU·mul in one kernel, then the down
+        projection added into ``h``.  Many tokens: the same through the norm's kernel and the
+        tensor-core products.  False if the step does not qualify."""
         from .attention import FUSED_MAX_TOKENS, fused_steps_enabled
         T = h.shape[0]
+        if (T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not plain_forced()
+                and h.dtype == torch.float32 and h.is_contiguous()):
+            # many tokens: the down projection adds its accumulators into the residual stream
+            self.forward(norm.forward(h, None), ctx, into=h)
+            return True
         rms = getattr(norm, "rms_params", None)
         if (not fused_steps_enabled() or self.dtype != torch.bfloat16 or T > FUSED_MAX_TOKENS
                 or rms is None

@@ -171,6 +171,28 @@ def test_batches_of_unequal_prompts_then_decoding_past_2048(wide_model, wide_eng
     assert eng.cache.stats()["slots_live"] == 0
 
 
+def test_a_repeated_step_of_16384_tokens_is_replayed_as_a_graph(wide_model, wide_engines):
+    """Eight prompts of 2,048 tokens in one step, three times with the same tokens in other
+    slots: the first runs eagerly, the second is captured, the third is the graph's replay;
+    all three give the same logits, and those of the first prompt are the plain model's."""
+    eng = wide_engines("bfloat16", 40 * 2112)
+    rng = np.random.default_rng(16384)
+    prompts = [rng.integers(0, 1000, size=2048).tolist() for _ in range(8)]
+    key = (tuple(2048 for _ in prompts), "last", 0)
+    runs = []
+    for i in range(3):
+        spare = [eng.alloc_slot() for _ in range(i)]       # so that the slots differ each time
+        slots = [eng.alloc_slot() for _ in prompts]
+        runs.append(eng.step(list(zip(slots, prompts)), "last").cpu().numpy())
+        assert (key in eng._graphs) == (i >= 1)
+        for s in slots + spare:
+            eng.free_slot(s)
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    want = _plain(wide_model, prompts[0], "bfloat16")[-1]
+    assert rel_err(runs[2][0], want) <= TOL["bfloat16"]
+    eng.cache.check()
+
+
 @pytest.mark.parametrize("batch", [16, 33, 64])
 def test_decode_batches_through_the_step_function(wide_model, wide_engines, batch):
     """Short unequal prompts, four of them long enough that the decode attention is planned

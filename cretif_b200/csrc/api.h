@@ -62,6 +62,11 @@ int cretif_set_tc_epilogue_warps(int n);
 // epilogue warps): on by default.  Returns the old setting.
 int cretif_set_tc_bulk_add(int on);
 
+// (For tests that run both.)  Two CTAs on a tile (cta_group::2) for the float32 add and the
+// SiLU product: -1 where the launcher sees fit (default), 0 never, 1 wherever the kernel takes
+// the product.  Returns the old setting.
+int cretif_set_tc_pair(int mode);
+
 // The same product with fused epilogues (see gemm_tc.cu): SiLU·mul for the stacked gate|up
 // matrix whose rows are interleaved in blocks of 64 (I % 64 == 0), and rotary + cache write for
 // the stacked q|k|v matrix (head_dim 64 or 128, rotary over the whole head).

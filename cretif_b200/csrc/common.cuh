@@ -150,6 +150,7 @@ enum Variant : int {
   kVarPrefillAttnPair,      // tcgen05 prefill attention, a thread per row, two query tiles per CTA
   kVarPrefillAttnSplit,     // ... one tile per CTA, its key steps split between two slots
   kVarTcBulkAdd,            // tcgen05 product added into a float32 matrix through TMA
+  kVarTcPair,               // tcgen05 product with two CTAs on a tile (cta_group::2)
   kVarCount
 };
 void count_variant(int v);

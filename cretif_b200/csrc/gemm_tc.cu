@@ -568,6 +568,223 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   stamp(5);
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Two CTAs on one tile of 256 rows (cta_group::2).
+//
+// With a tile of its own a CTA pulls (128 + BN) x 64 x 2 bytes through its SM's port to L2 per
+// k-block of 4 x BN / 2 cycles of products: 96 bytes a cycle at BN = 256, more for narrower
+// tiles, and the port gives some 70 (the widest product here stops at 0.76 of the tensor
+// peak, gate|up at 0.65).  Here the CTAs of a cluster of two share a tile: each loads its
+// 128 rows of A and its 128 of the 256 rows of W, CTA 0 issues one product of M = 256 for
+// both, and each ends up with its 128 rows of the accumulator in its own tensor memory: 64
+// bytes a cycle per SM.  The loads of both CTAs are counted on CTA 0's barriers; its commits
+// arrive on the barriers of both.  Epilogues: the float32 add and the SiLU store through
+// shared-memory slabs and TMA, as above.
+constexpr int kTpThreads = 320;         // producer, issuer, eight epilogue warps
+template <int kTpBN>                    // the tile's width: 256, or 192 for widths like 576 and 960
+struct TpSmem {
+  static constexpr int kATile = kTcBM * kTcBK * 2;       // this CTA's 128 rows of A
+  static constexpr int kBTile = (kTpBN / 2) * kTcBK * 2; // its half of the tile's rows of W
+  static constexpr int kStage = kATile + kBTile;
+  static constexpr int kSlab = kTcBM * 128;
+  static constexpr int total(int stages, int slabs) {
+    return stages * kStage + slabs * kSlab + (2 * kTcMaxStages + 4) * 8 + 16 + 1024;
+  }
+};
+
+template <int kTpBN, int EPI>
+__global__ void __launch_bounds__(kTpThreads)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_c, const TcEpi ep, int M, int N, int K,
+                    unsigned int* __restrict__ fault, int n_stages, int n_n_tiles, int n_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using L = TpSmem<kTpBN>;
+  constexpr int kSlabs = EPI == kTcStore ? 4 : 2;
+  unsigned char* staging = smem + n_stages * L::kStage;
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + kSlabs * L::kSlab);   // used in CTA 0
+  uint64_t* empty = full + kTcMaxStages;
+  uint64_t* acc_full = empty + kTcMaxStages;
+  uint64_t* acc_empty = acc_full + 2;                                          // used in CTA 0
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_rank();
+  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+  const int num_kb = (K + kTcBK - 1) / kTcBK;
+  const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 2 * 8);       // a warp of either CTA at a time
+    }
+    *abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_descriptor(&map_a);
+    tc::tma_prefetch_descriptor(&map_w);
+    tc::tma_prefetch_descriptor(&map_c);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc_pair(tmem_slot, 512);
+    tc::tmem_relinquish_pair();
+  }
+  tc::tc_fence_before();
+  tc::cluster_sync_all();                 // both CTAs' barriers exist before either touches them
+  tc::tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0 && my_tiles > 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      int s = 0, turn = 0;
+      bool ok = true;
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int tile = pair + i * n_pairs;
+        const int mt = tile / n_n_tiles, nt = tile - mt * n_n_tiles;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (turn > 0 && !tc::mbar_wait(&empty[s], (uint32_t)((turn - 1) & 1), abort)) {
+            ok = false;
+            break;
+          }
+          unsigned char* stage = smem + s * L::kStage;
+          if (rank == 0) tc::mbar_expect_tx(&full[s], 2u * L::kStage);    // both CTAs' bytes
+          const uint32_t bar = tc::cluster_addr(&full[s], 0);
+          tc::tma_load_2d_pair(stage, &map_a, kb * kTcBK, mt * 2 * kTcBM + (int)rank * kTcBM, bar);
+          tc::tma_load_2d_pair(stage + L::kATile, &map_w, kb * kTcBK,
+                               nt * kTpBN + (int)rank * (kTpBN / 2), bar);
+          if (++s == n_stages) { s = 0; ++turn; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = tc::instr_desc_bf16(2 * kTcBM, kTpBN);
+      bool ok = true;
+      int s = 0, turn = 0;
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        const int buf = i & 1;
+        if (i >= 2) ok = tc::mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) - 1) & 1), abort);
+        if (!ok) break;
+        tc::tc_fence_after();
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = tc::mbar_wait(&full[s], (uint32_t)(turn & 1), abort);
+          if (!ok) break;
+          tc::tc_fence_after();
+          unsigned char* stage = smem + s * L::kStage;
+          const uint64_t a_desc = tc::smem_desc_k_sw128(stage);
+          const uint64_t b_desc = tc::smem_desc_k_sw128(stage + L::kATile);
+#pragma unroll
+          for (int k = 0; k < kTcBK / 16; ++k)
+            tc::umma_bf16_pair(tmem_acc + (uint32_t)(buf * kTpBN), a_desc + 2 * k, b_desc + 2 * k,
+                               idesc, (kb | k) != 0);
+          tc::umma_commit_pair(&empty[s], 3);          // frees the stage in both CTAs
+          if (++s == n_stages) { s = 0; ++turn; }
+        }
+        if (ok) tc::umma_commit_pair(&acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): a thread takes one of this CTA's 128 rows and half of the
+    // tile's columns; see the bulk epilogues of gemm_tc_kernel
+    const int quad = warp & 3, chalf = (warp - 2) >> 2;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    bool alive = true;
+    uint32_t slabs = 0;
+    const uint32_t acc_empty_leader[2] = {tc::cluster_addr(&acc_empty[0], 0),
+                                          tc::cluster_addr(&acc_empty[1], 0)};
+    const int row = quad * 32 + lane;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int buf = i & 1;
+      const int tile = pair + i * n_pairs;
+      const int mt = tile / n_n_tiles, nt = tile - mt * n_n_tiles;
+      const int m0 = mt * 2 * kTcBM + (int)rank * kTcBM, n0 = nt * kTpBN;
+      alive = tc::mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1), abort) && alive;
+      const bool ok = alive;
+      tc::tc_fence_after();
+      const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * kTpBN) + ((uint32_t)(quad * 32) << 16);
+      if (EPI == kTcStore) {
+        unsigned char* mine = staging + chalf * 2 * L::kSlab;
+        const bool elected = ((warp - 2) & 3) == 0 && lane == 0;
+#pragma unroll 1
+        for (int c0 = chalf * (kTpBN / 2); c0 < (chalf + 1) * (kTpBN / 2); c0 += 32, ++slabs) {
+          uint32_t r[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)c0, r);
+          tc::tmem_load_wait();
+          if (elected) tc::bulk_wait_group_read<1>();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
+          unsigned char* slab = mine + (slabs & 1) * L::kSlab;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(slab + row * 128 + ((j ^ (row & 7)) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          tc::fence_proxy_async();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
+          if (elected) {
+            if (ok && n0 + c0 < N) tc::tma_reduce_add_2d(&map_c, slab, n0 + c0, m0);
+            tc::bulk_commit_group();
+          }
+        }
+      } else {
+        const bool elected = warp == 2 && lane == 0;
+#pragma unroll 1
+        for (int pr = 0; pr < kTpBN / 128; ++pr, ++slabs) {
+          const int col0 = (n0 >> 1) + pr * 64;
+          const int c0 = chalf * 32;
+          uint32_t g[32], u[32];
+          tc::tmem_load_32(lane_acc + (uint32_t)(pr * 128 + c0), g);
+          tc::tmem_load_32(lane_acc + (uint32_t)(pr * 128 + 64 + c0), u);
+          tc::tmem_load_wait();
+          if (elected) tc::bulk_wait_group_read<1>();
+          asm volatile("bar.sync 3, 256;" ::: "memory");
+          unsigned char* slab = staging + (slabs & 1) * L::kSlab;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const float g0 = round_bf16(__uint_as_float(g[j + e]));
+              const float g1 = round_bf16(__uint_as_float(g[j + e + 1]));
+              const float u0 = round_bf16(__uint_as_float(u[j + e]));
+              const float u1 = round_bf16(__uint_as_float(u[j + e + 1]));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_bf16_path(g0) * u0,
+                                                        silu_bf16_path(g1) * u1);
+              w4[e >> 1] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            const int piece = chalf * 4 + (j >> 3);
+            *reinterpret_cast<uint4*>(slab + row * 128 + ((piece ^ (row & 7)) << 4)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+          tc::fence_proxy_async();
+          asm volatile("bar.sync 3, 256;" ::: "memory");
+          if (elected) {
+            if (ok && col0 < ep.I) tc::tma_store_2d(&map_c, slab, col0, m0);
+            tc::bulk_commit_group();
+          }
+        }
+      }
+      // this CTA's half of the accumulator may be overwritten: CTA 0's issuer is told
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(acc_empty_leader[buf]);
+    }
+    if (((EPI == kTcStore && ((warp - 2) & 3) == 0) || (EPI != kTcStore && warp == 2)) && lane == 0)
+      tc::bulk_wait_all();
+  }
+  if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
+  tc::tc_fence_before();
+  tc::cluster_sync_all();                 // no commit is on its way to a CTA that has left
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc_pair(tmem_acc, 512);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -659,6 +876,68 @@ static int g_tc_epilogue_warps = 0;
 // Epilogues through shared memory and TMA (the float32 add, the SiLU store) where the kernel
 // can: 1 (default), 0 never (for tests that run both).
 static int g_tc_bulk_add = 1;
+
+// Two CTAs on one tile where the launch is large enough: -1 (default), 0 never, 1 wherever
+// the kernel takes the product (for tests that run both).
+static int g_tc_pair = -1;
+
+// Measured at 16,384 rows (single-CTA tiles against pairs, us): 3072 x 576 47 / 55, 576 x 1536
+// 33 / 33, 5120 x 960 120 / 115, 960 x 2560 80 / 77, 2048 x 2048 123 / 112, 16384 x 2048 829 / 743,
+// 2048 x 8192 442 / 417: pairs pay once a tile's products outlast what two CTAs spend on
+// telling each other.
+static bool pair_pays(int N, int K) { return (long long)N * K >= (2LL << 20); }
+
+template <int kTpBN, int EPI>
+static int launch_tc_pair(const void* A, const void* W, TcEpi ep, int M, int N, int K, int lda,
+                          int ldw, unsigned int* fault, cudaStream_t st) {
+  CUtensorMap map_a, map_w, map_c;
+  if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
+  if (make_tile_map_bf16(&map_w, W, N, K, ldw, kTpBN / 2)) return kBadArgument;
+  if (EPI == kTcStore ? make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true)
+                      : make_box_map(&map_c, ep.act, M, ep.I, ep.I, kTcBM, 64, true, false))
+    return kBadArgument;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int n_n_tiles = (N + kTpBN - 1) / kTpBN;
+  const long long tiles = (long long)n_n_tiles * ((M + 2 * kTcBM - 1) / (2 * kTcBM));
+  if (tiles > 0x7fffffffLL) return kBadArgument;
+  constexpr int kSlabs = EPI == kTcStore ? 4 : 2;
+  int stages = kTcMaxStages;
+  while (stages > 2 && TpSmem<kTpBN>::total(stages, kSlabs) > 227 * 1024) --stages;
+  const int smem = TpSmem<kTpBN>::total(stages, kSlabs);
+  static int configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<kTpBN, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  const long long pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kTpThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled();
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  ep.bulk = 1;
+  count_variant(kVarTcPair);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<kTpBN, EPI>, map_a, map_w, map_c, ep, M,
+                                           N, K, fault, stages, n_n_tiles, (int)tiles);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
 
 // Registers of a thread of the kernel, for the residency estimate (once per instantiation).
 template <int BN, int EPI, typename TC, int EW>
@@ -783,6 +1062,12 @@ static bool tc_operands_ok(const void* A, const void* W, int M, int K, int lda, 
 
 using namespace cretif;
 
+extern "C" int cretif_set_tc_pair(int mode) {
+  const int was = g_tc_pair;
+  g_tc_pair = mode < 0 ? -1 : (mode > 0 ? 1 : 0);
+  return was;
+}
+
 extern "C" int cretif_set_tc_bulk_add(int on) {
   const int was = g_tc_bulk_add;
   g_tc_bulk_add = on ? 1 : 0;
@@ -820,6 +1105,14 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
   }
   TcEpi ep = {};
   ep.C = C; ep.ldc = ldc; ep.accumulate = accumulate;
+  // The float32 add of a large product: two CTAs a tile (see gemm_tc_pair_kernel), as wide as
+  // the single-CTA tile would be.
+  if (c_dt == kF32 && accumulate && g_tc_pair != 0 && g_tc_bulk_add && (bn == 256 || bn == 192) &&
+      N % bn == 0 && ldc % 4 == 0 &&
+      (g_tc_pair > 0 || ((long long)((M + 255) / 256) * (N / bn) >= 2 * 74 && pair_pays(N, K)))) {
+    return bn == 256 ? launch_tc_pair<256, kTcStore>(A, W, ep, M, N, K, lda, ldw, fault, st)
+                     : launch_tc_pair<192, kTcStore>(A, W, ep, M, N, K, lda, ldw, fault, st);
+  }
 #define CRETIF_TC(BN)                                                                         \
   (c_dt == kBF16 ? launch_tc<BN, kTcStore, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, \
                                                           st)                                 \
@@ -847,6 +1140,9 @@ extern "C" int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, in
   // wide tiles (two gate|up pairs, one CTA per SM) once there are four waves of them for the
   // whole chip; with fewer, the last wave's empty seats cost more than the wide tile saves
   const long long wide_tiles = (long long)((2 * I + 255) / 256) * ((M + kTcBM - 1) / kTcBM);
+  if (g_tc_pair != 0 && g_tc_bulk_add && (2 * I) % 256 == 0 &&
+      (g_tc_pair > 0 || (wide_tiles >= 4 * 148 && pair_pays(2 * I, K))))
+    return launch_tc_pair<256, kTcSilu>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault, (cudaStream_t)stream);
   if (wide_tiles >= 4 * 148)
     return launch_tc<256, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
                                                   (cudaStream_t)stream);

@@ -50,7 +50,7 @@ def launch_count() -> int:
 _VARIANTS = ("fused_registers", "fused_row_groups", "fused_cluster2", "fused_cluster4", "stream",
              "stream_row_groups", "decode_cluster", "decode_split", "prefill_attn", "tc64",
              "tc128", "tc256", "tc_several_tiles", "tc192", "prefill_attn_pair",
-             "prefill_attn_split", "tc_bulk_add")
+             "prefill_attn_split", "tc_bulk_add", "tc_pair")
 
 
 def variant_counts() -> dict:
@@ -584,6 +584,13 @@ def gemm_tc_qkv_rope(x, w_qkv, q_out, cos, sin, pairing: int, nh: int, nkv: int,
         _p(tok_pos), _p(tok_seq), _p(seq_slot), _p(table), table.stride(0), _p(kc), _p(vc),
         block_tokens, int(write_cache), M, K, _rows(x, "x"), _rows(w_qkv, "w_qkv"),
         _p(fault_word(x.device)), _stream()), "gemm_tc_qkv_rope")
+
+
+def set_tc_pair(mode: int) -> int:
+    """(For tests that run both.)  The tensor-core product with two CTAs on a tile: -1 where
+    the launcher sees fit (the default), 0 never, 1 wherever the kernel takes the product.
+    Returns the old setting."""
+    return int(lib().cretif_set_tc_pair(int(mode)))
 
 
 def set_tc_bulk_add(on: bool) -> bool:

@@ -143,6 +143,51 @@ def test_gemm_tc(ops, tc_epilogue, M, N, K, bn):
     assert fault.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(256, 256, 64, 256), (1000, 512, 136, 256), (300, 576, 72, 192),
+                                      (130, 960, 200, 192), (2100, 2048, 264, 256)])
+def test_gemm_tc_with_two_ctas_on_a_tile(ops, M, N, K, bn):
+    """The float32 add with a cluster of two CTAs on each tile of 256 rows (cta_group::2)
+    against float64, tails in M and K, and the same numbers as the single-CTA kernel."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    base = rnd(M, N, seed=3)
+    want = base.double() + x.double() @ w.double().T
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    got = {}
+    for mode in (0, 1):
+        old = ops.set_tc_pair(mode)
+        before = ops.variant_counts()["tc_pair"]
+        c = base.clone()
+        ops.gemm_tc(x, w, c, accumulate=True, bn=bn)
+        ops.set_tc_pair(old)
+        torch.cuda.synchronize()
+        assert (ops.variant_counts()["tc_pair"] > before) == (mode == 1)
+        close(c, want, 1e-5)
+        got[mode] = c
+    assert fault.item() == 0
+    assert torch.equal(got[0], got[1])
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (2200, 4224, 72), (300, 1536, 576)])
+def test_gemm_tc_silu_with_two_ctas_on_a_tile(ops, M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16)
+    gate = rnd(I, K, dtype=torch.bfloat16, seed=1, scale=0.3)
+    up = rnd(I, K, dtype=torch.bfloat16, seed=2, scale=0.3)
+    w = _interleave(gate, up)
+    g = (x.double() @ gate.double().T).to(torch.bfloat16).double()
+    u = (x.double() @ up.double().T).to(torch.bfloat16).double()
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    old = ops.set_tc_pair(1)
+    before = ops.variant_counts()["tc_pair"]
+    act = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc_silu(x, w, act)
+    ops.set_tc_pair(old)
+    torch.cuda.synchronize()
+    assert ops.variant_counts()["tc_pair"] > before and fault.item() == 0
+    close(act, g / (1 + torch.exp(-g)) * u, 1e-2)
+
+
 # ------------------------------------------------------------------ fused decode projections
 @pytest.fixture(params=[(1 << 20, 1 << 40, 4), (1 << 20, 1 << 40, 1), (64, 0, 4)],
                 ids=["registers", "registers-no-cluster", "streamed"])

@@ -47,3 +47,30 @@ def test_larger_layer_sizes(folders, name, dtype, tol):
     for got, want in zip(outs, wants):
         assert rel_err(got, want) <= tol
     eng.cache.check()
+
+
+def test_a_large_step_at_360m_sizes_takes_the_two_cta_products(folders):
+    """Four prompts of 2,048 tokens in one step at SmolLM2-360M layer sizes: enough tiles and
+    a long enough K that gate|up and the down projection run with two CTAs on a tile
+    (cta_group::2).  The last positions of every prompt and every 97th of the first against the
+    plain model rounded alike."""
+    from cretif_b200.csrc import ops
+    from cretif_b200.engine import Engine
+    d, (cfg, w) = folders["360m"]
+    eng = Engine(d, dtype="bfloat16", max_tokens=4 * 2112)
+    rng = np.random.default_rng(360)
+    prompts = [rng.integers(0, 1000, size=2048).tolist() for _ in range(4)]
+    rows = [sorted(set(range(0, 2048, 97)) | {2047})] + [[2047]] * 3
+    before = ops.variant_counts()["tc_pair"]
+    slots = [eng.alloc_slot() for _ in prompts]
+    got = eng.step(list(zip(slots, prompts)), rows).cpu().numpy()
+    for s_ in slots:
+        eng.free_slot(s_)
+    assert ops.variant_counts()["tc_pair"] >= before + 4          # two layers, two products each
+    first = pl.forward(cfg, w, prompts[0], storage=torch.bfloat16).numpy()
+    n0 = len(rows[0])
+    assert rel_err(got[:n0], first[rows[0]]) <= 2e-2
+    for b in (1, 2, 3):
+        want = pl.forward(cfg, w, prompts[b], storage=torch.bfloat16).numpy()[-1]
+        assert rel_err(got[n0 + b - 1], want) <= 2e-2
+    eng.cache.check()

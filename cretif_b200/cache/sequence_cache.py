@@ -230,8 +230,11 @@ class SequenceCache:
         for g in self._kv_groups:
             g.flush()
 
-    def reserve(self, slot: int, total_len: int) -> None:
-        """Map blocks for ``total_len`` positions now, so later steps change no table."""
+    def reserve(self, slot: int, total_len: int, flush: bool = True) -> None:
+        """Map blocks for ``total_len`` positions now, so later steps change no table.
+        ``flush=False`` leaves the device's copy of the tables for a later call (another
+        ``reserve`` or ``begin_step``) to bring up to date: a batch reserves all its slots and
+        copies once."""
         if not self.slots.is_live(slot):
             raise CacheError(f"slot {slot} is not in use")
         if total_len > self.max_len:
@@ -248,8 +251,9 @@ class SequenceCache:
             for g, old in olds:
                 g.shrink_to(slot, old)
             raise
-        for g in self._kv_groups:
-            g.flush()
+        if flush:
+            for g in self._kv_groups:
+                g.flush()
 
     # -- views -----------------------------------------------------------------
     def kv_view(self, cache_id: int) -> KVView:

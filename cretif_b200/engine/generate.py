@@ -247,10 +247,10 @@ class EngineBackend:
                            for _ in range(self.depth + 2)]
         self._host_at = 0
         try:
-            for n in reserve_lens:
+            for i, n in enumerate(reserve_lens):
                 s = eng.alloc_slot()
                 self.slots.append(s)
-                eng.cache.reserve(s, n)
+                eng.cache.reserve(s, n, flush=i + 1 == len(reserve_lens))   # one copy for all
         except Exception:
             self.end_batch()
             raise

@@ -65,14 +65,23 @@ class _PinnedRing:
     """Page-locked staging buffers for the small host-to-device copies of a step, reused in
     turn; a buffer is taken again only after the copy that last read it has finished."""
 
-    def __init__(self, n: int = 8):
-        self.bufs = [None] * n
-        self.events = [None] * n
+    def __init__(self, n: int = 8, n_large: int = 2, large: int = 1 << 14):
+        # the last `n_large` buffers take the copies of more than `large` elements (a prompt
+        # step's indices): page-locking megabytes costs milliseconds, and such steps do not
+        # run ahead of one another, so two buffers serve them
+        self.bufs = [None] * (n + n_large)
+        self.events = [None] * (n + n_large)
+        self.n, self.n_large, self.large = n, n_large, large
         self.at = 0
+        self.at_large = 0
 
     def copy_to(self, dst: torch.Tensor, src: np.ndarray) -> None:
-        i = self.at
-        self.at = (i + 1) % len(self.bufs)
+        if src.size > self.large:
+            i = self.n + self.at_large
+            self.at_large = (self.at_large + 1) % self.n_large
+        else:
+            i = self.at
+            self.at = (i + 1) % self.n
         if self.events[i] is not None:
             self.events[i].synchronize()
         buf = self.bufs[i]

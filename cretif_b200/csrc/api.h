@@ -58,8 +58,8 @@ int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N
 // chooses per launch.  Returns the old setting.
 int cretif_set_tc_epilogue_warps(int n);
 
-// (For tests that run both.)  Adding into a float32 matrix through TMA (wide tiles, eight
-// epilogue warps): on by default.  Returns the old setting.
+// (For tests that run both.)  Adding into a float32 matrix, and storing the SiLU product,
+// through shared memory and TMA: on by default.  Returns the old setting.
 int cretif_set_tc_bulk_add(int on);
 
 // (For tests that run both.)  Two CTAs on a tile (cta_group::2) for the float32 add and the

@@ -118,9 +118,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TcSmem<BN>;
-  constexpr bool kBulk = EPI == kTcStore && sizeof(TC) == 4 && EW == 8 && BN >= 192;
+  constexpr bool kBulk = EPI == kTcStore && sizeof(TC) == 4;
   constexpr bool kBulkSilu = EPI == kTcSilu && EW == 8 && BN == 256;
-  constexpr int kSlabs = kBulk ? 4 : (kBulkSilu ? 2 : 0);
+  constexpr int kSlabs = kBulk ? EW / 2 : (kBulkSilu ? 2 : 0);     // two a group of four warps
   unsigned char* staging = smem + kTcStages * L::kStage;
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + (kSlabs && ep.bulk ? kSlabs * L::kSlab : 0));
   uint64_t* empty = full + kTcMaxStages;
@@ -1011,14 +1011,17 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep_in, int M, in
   int epi_warps = g_tc_epilogue_warps;
   if (epi_warps != 4 && epi_warps != 8)
     epi_warps = tiles > 2LL * residents(4) * sm_count && K <= 4096 ? 8 : 4;
-  // The float32 add through TMA (eight epilogue warps, wide tiles) needs room for its slabs.
+  // The float32 add through TMA needs room for its slabs (two a group of four epilogue
+  // warps).  Measured against the add by the epilogue's threads, us: 4,096 x 576 x 576 24.4 ->
+  // 11.4, x 1,536 29.6 -> 20.6; 2,048 x 576 x 1,536 13.7 -> 12.0; 2,048 x 960 x 2,560 22.6 -> 17.2;
+  // 2,048 x 2,048 x 2,048 28.2 -> 26.1; with K = 8,192 the stages it takes away cost more than
+  // it saves (69.6 -> 94.2).
   ep.bulk = 0;
-  if (EPI == kTcStore && sizeof(TC) == 4 && ep.accumulate && epi_warps == 8 && BN >= 192 &&
-      g_tc_bulk_add && ep.ldc % 4 == 0 && ((uintptr_t)ep.C & 15) == 0 &&
+  if (EPI == kTcStore && sizeof(TC) == 4 && ep.accumulate && K <= 4096 && g_tc_bulk_add && ep.ldc % 4 == 0 && ((uintptr_t)ep.C & 15) == 0 &&
       make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true) == 0) {
     ep.bulk = 1;
-    stages = TcSmem<BN>::stages_with_staging(stages, 4);
-    smem = TcSmem<BN>::total(stages, 4);
+    stages = TcSmem<BN>::stages_with_staging(stages, epi_warps / 2);
+    smem = TcSmem<BN>::total(stages, epi_warps / 2);
     count_variant(kVarTcBulkAdd);
   }
   if (EPI == kTcSilu && epi_warps == 8 && BN == 256 && g_tc_bulk_add &&
